@@ -1,0 +1,193 @@
+/*
+ * kascade_b200 — C ABI of the B200 (sm_100a) Kascade sparse-attention kernels.
+ *
+ * One shared library, libkascade_b200.so, replaces the seven per-kernel shared objects the
+ * reference builds at strategy construction (strategies/EfficientKascadeStrategy.py:22-70), each of
+ * which exports `init`, `call`, `get_last_error`
+ * (kernels/flash_attention/kascade_prefill_cu_kernels/dynamic_alllen_reuse_cp_async_ts32_dim128_gsize4_heads32_groups8_rolling.cu:249-319).
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer unless the comment says "host"; fp16 data is IEEE binary16;
+ *  - strides are in ELEMENTS, the head dimension D is contiguous and must be 128;
+ *  - query heads per KV head (H / G) must be 4, the prefill query tile is 32 queries — the one
+ *    shape the reference compiles (README.md:74, file names `ts32_dim128_gsize4`);
+ *  - every call is asynchronous on `stream` (a cudaStream_t passed as void*), allocates nothing,
+ *    copies nothing between host and device and never synchronises; the caller owns all memory,
+ *    including the workspaces whose sizes the *_workspace_bytes functions return;
+ *  - return value 0 = launched, non-zero = rejected (nothing launched); the reason is returned by
+ *    kb200_last_error() for the calling thread.
+ *  - logits are kept in the log2 domain like the reference's kernels
+ *    (kernels/flash_attention/recompute_kascade_gqa_prefill.py:266-272):
+ *    lse2 = log2(sum_j exp2(s_j * scale * log2 e)).
+ */
+#ifndef KASCADE_B200_H_
+#define KASCADE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KB200_HEAD_DIM 128
+#define KB200_GROUP_SIZE 4
+#define KB200_TILE 32
+
+/* ---- library ---------------------------------------------------------------------------------- */
+
+/* Replaces `init()` of every reference kernel library (…_rolling.cu:249-258): selects nothing,
+ * allocates nothing; raises the dynamic shared-memory limits of the kernels on `device` and checks
+ * that the device is an sm_100 part.  Must be called once per device before any other call. */
+int kb200_init(int device);
+
+/* Replaces `get_last_error()` (…_rolling.cu:245-247).  Thread-local, never NULL. */
+const char* kb200_last_error(void);
+
+/* ABI version of this header. */
+int kb200_abi_version(void);
+
+/* ---- Top-k selection (replaces the torch.topk call sites,
+ *      strategies/EfficientKascadeStrategy.py:82,90,111) ---------------------------------------- */
+
+/* Exact Top-k of each row of a fp32 score matrix by radix select.
+ *   scores      [rows, row_stride]      only the first n_valid[r] entries of row r are candidates
+ *   n_valid     [rows] int32            (NULL: every row has n_cols candidates)
+ *   k_row       [rows] int32            budget of row r (NULL: k_max for every row)
+ *   out_idx     [rows, idx_stride] int32  receives min(k_row[r], n_valid[r]) indices in ASCENDING
+ *                                       index order; entries beyond that count are left untouched
+ *   out_count   [rows] int32            receives that count
+ * Ties at the k-th score are resolved towards the lowest index.  NaNs are not supported. */
+int kb200_topk_select(const float* scores, int64_t row_stride, int n_cols, const int32_t* n_valid,
+                      const int32_t* k_row, int k_max, int32_t* out_idx, int64_t idx_stride,
+                      int32_t* out_count, int64_t rows, void* stream);
+
+/* ---- paged decode (replaces kernels/flash_decoding/reuse_kascade_gqa_decode.py:50-134 and
+ *      recompute_kascade_gqa_decode.py:49-315; the reference has no paged variant, README.md:135;
+ *      the closest signature is reuse_kascade_gqa_decode_with_kvcache.py:160-171) --------------- */
+
+/* Address of the 128-element row of token `pos` of sequence `b`, KV head `g`:
+ *   page = block_table ? block_table[b * block_table_stride + pos / page_size] : pos / page_size
+ *   base + b * stride_batch + page * stride_page + (pos % page_size) * stride_token + g * stride_head
+ * vLLM-style paged cache [num_pages, page_size, G, D]: stride_batch = 0.  Contiguous HF cache
+ * [B, G, L, D]: block_table = NULL, stride_batch = G*L*D, stride_page = page_size*D,
+ * stride_token = D, stride_head = L*D. */
+typedef struct kb200_kv_layout {
+  const void* k;              /* fp16 */
+  const void* v;              /* fp16, may be NULL where a call says so */
+  int64_t stride_batch;
+  int64_t stride_page;
+  int64_t stride_token;
+  int64_t stride_head;
+  const int32_t* block_table; /* [B, block_table_stride] or NULL */
+  int32_t block_table_stride;
+  int32_t page_size;          /* power of two, >= 1 */
+} kb200_kv_layout;
+
+/* Workspace for kb200_decode_sparse_paged / kb200_decode_anchor_paged (split-K partials). */
+size_t kb200_decode_workspace_bytes(int batch, int num_q_heads, int num_splits);
+/* Number of splits the library would choose (num_splits = 0) for this problem. */
+int kb200_decode_default_splits(int batch, int num_kv_heads, int max_keys);
+
+/* Sparse (reuse-layer) decode: attention of one query token per sequence over the key rows
+ * listed in topk_idx.   (K8 + K9 of the reference: reuse_kascade_gqa_decode.py:50-200)
+ *   q           [B, H, D] fp16, strides q_stride_b / q_stride_h
+ *   topk_idx    [B, G, idx_stride_g…] int32 logical token positions; row of KV head g of
+ *               sequence b starts at topk_idx + b*idx_stride_b + g*idx_stride_g
+ *   topk_count  [B, G] int32 number of valid entries per row (NULL: k_max everywhere)
+ *   head_map    [G] int32: KV head g reads the index row of KV head head_map[g] (NULL: identity)
+ *   out         [B, H, D] fp16 contiguous
+ *   lse2_out    [B, H] fp32 or NULL
+ * Rows with zero valid keys produce zeros. */
+int kb200_decode_sparse_paged(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                              const kb200_kv_layout* kv, const int32_t* topk_idx,
+                              int64_t idx_stride_b, int64_t idx_stride_g,
+                              const int32_t* topk_count, int k_max, const int32_t* head_map,
+                              float softmax_scale, void* out, float* lse2_out, void* workspace,
+                              size_t workspace_bytes, int batch, int num_q_heads, int num_kv_heads,
+                              int num_splits, void* stream);
+
+/* Anchor-layer decode: dense pass over all seq_lens[b] cached keys.  Writes the scaled base-2
+ * logits of every (head, key), the per-head lse2, optionally the dense output, and the pooled
+ * post-softmax score  pooled[b,g,j] = sum_{h in group g} exp2(logit[b,h,j] - lse2[b,h])
+ * that kb200_topk_select consumes.  (K5 + K6 + K7: recompute_kascade_gqa_decode.py:49-315)
+ *   seq_lens    [B] int32
+ *   logits      [B, H, logit_stride] fp32 scratch (logit_stride >= max seq len)
+ *   pooled      [B, G, logit_stride] fp32
+ *   out         [B, H, D] fp16 or NULL (NULL: K only — anchor layers > 0 read no V)
+ *   lse2_out    [B, H] fp32 (required) */
+int kb200_decode_anchor_paged(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                              const kb200_kv_layout* kv, const int32_t* seq_lens, int max_seq_len,
+                              float softmax_scale, float* logits, float* pooled,
+                              int64_t logit_stride, void* out, float* lse2_out, void* workspace,
+                              size_t workspace_bytes, int batch, int num_q_heads, int num_kv_heads,
+                              int num_splits, void* stream);
+
+/* ---- tile prefill (replaces kernels/flash_attention/recompute_kascade_gqa_prefill.py:191-312 and
+ *      reuse_kascade_gqa_prefill.py:146-198) --------------------------------------------------- */
+
+/* Token-major activations: element (b, token, head, d) at
+ *   base + b*stride_b + token*stride_t + head*stride_h + d. */
+typedef struct kb200_act_layout {
+  const void* ptr; /* fp16 */
+  int64_t stride_b;
+  int64_t stride_t;
+  int64_t stride_h;
+} kb200_act_layout;
+
+/* Dense causal attention of a whole prompt, one CTA per (32-query tile, KV head, batch).
+ *   out   [B, L, H, D] fp16 contiguous, or NULL for the lse-only pass (then v is not read)
+ *   lse2  [B, L, H] fp32, or NULL
+ * (K1 `prefill` and K2 `compute_scores`: recompute_kascade_gqa_prefill.py:224-312) */
+int kb200_prefill_dense(const kb200_act_layout* q, const kb200_act_layout* k,
+                        const kb200_act_layout* v, float softmax_scale, void* out, float* lse2,
+                        int batch, int seq_len, int num_q_heads, int num_kv_heads, void* stream);
+
+/* Tile-pooled post-softmax scores of an anchor layer:
+ *   pooled[b,g,t,j] = sum_{32 queries i of tile t} sum_{4 heads h of group g}
+ *                     exp2(q_ih . k_j * scale * log2 e - lse2[b,i,h])      for j < 32*t
+ * Entries j >= 32*t of a row are not written (kb200_topk_select is given n_valid = 32*t).
+ *   pooled  [B, G, T, row_stride] fp32, T = ceil(L/32), row_stride >= L rounded up to 128
+ * (K3 `aggregate`: recompute_kascade_gqa_prefill.py:171-222 and
+ *  dynamic_alllen_aggregate_cp_async_ts32_dim128_gsize4_heads32_groups8.cu) */
+int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_act_layout* k,
+                              const float* lse2, float softmax_scale, float* pooled,
+                              int64_t row_stride, int batch, int seq_len, int num_q_heads,
+                              int num_kv_heads, void* stream);
+
+/* Sparse tile attention of a reuse layer (or of an anchor layer > 0 over its own fresh rows):
+ * query i of tile t attends to the keys tile_idx[b, head_map[g], t, 0:tile_count[…]] (all
+ * strictly before the tile) and to the keys 32*t .. i of its own tile.
+ *   tile_idx    [B, G, T, idx_stride] int32, ascending or any order, no duplicates
+ *   tile_count  [B, G, T] int32
+ *   head_map    [G] int32 or NULL (identity)
+ *   out         [B, L, H, D] fp16 contiguous;  lse2 [B, L, H] fp32 or NULL
+ * (K4 `main_kernel`: reuse_kascade_gqa_prefill.py:146-198 and the two
+ *  dynamic_alllen_reuse_cp_async_ts32_dim128_gsize4_heads32_groups8[_rolling].cu) */
+int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_layout* k,
+                         const kb200_act_layout* v, const int32_t* tile_idx, int64_t idx_stride,
+                         const int32_t* tile_count, const int32_t* head_map, float softmax_scale,
+                         void* out, float* lse2, int batch, int seq_len, int num_q_heads,
+                         int num_kv_heads, void* stream);
+
+/* Per-tile budgets of an anchor prefill layer, written on the device for kb200_topk_select:
+ *   n_valid[b,g,t] = 32*t,
+ *   k_row[b,g,t]   = rolling ? min(k_max, max(128, floor(pct * 32*t / 100))) : k_max
+ * (strategies/KascadeStrategy.py:127-139). */
+int kb200_prefill_budgets(int32_t* n_valid, int32_t* k_row, int batch, int num_kv_heads,
+                          int num_tiles, int k_max, float pct, int rolling, void* stream);
+
+/* ---- diagnostics ----------------------------------------------------------------------------- */
+
+/* Runs four 128x128x128 fp16 products through the tensor-core paths the prefill kernels rely on
+ * (A/B from shared memory K-major; B MN-major; A from tensor memory) and writes the fp32 results:
+ *   a, b [128,128] fp16 row-major;  out [4, 128, 128] fp32
+ *   out[0] = a . b^T   out[1] = a . b   out[2] = a . b^T (A via tensor memory)   out[3] = a . b (A via tensor memory)
+ *   status [4] int32: 0 ok, non-zero = a bounded wait gave up.
+ * No counterpart in the reference. */
+int kb200_selftest_umma(const void* a, const void* b, float* out, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KASCADE_B200_H_ */

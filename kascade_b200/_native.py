@@ -1,0 +1,251 @@
+"""ctypes binding of libkascade_b200.so (the C ABI declared in include/kascade_b200.h).
+
+The library is loaded from this package directory.  There is no fallback: if the shared object is
+missing or a call is rejected, a ``KascadeNativeError`` is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libkascade_b200.so")
+
+HEAD_DIM = 128
+GROUP_SIZE = 4
+TILE = 32
+
+EXPORTS = [
+    "kb200_init", "kb200_last_error", "kb200_abi_version", "kb200_topk_select",
+    "kb200_decode_workspace_bytes", "kb200_decode_default_splits", "kb200_decode_sparse_paged",
+    "kb200_decode_anchor_paged", "kb200_prefill_dense", "kb200_prefill_pool_scores",
+    "kb200_prefill_sparse", "kb200_prefill_budgets", "kb200_selftest_umma",
+]
+
+
+class KascadeNativeError(RuntimeError):
+    pass
+
+
+class KvLayout(C.Structure):
+    _fields_ = [("k", C.c_void_p), ("v", C.c_void_p), ("stride_batch", C.c_int64),
+                ("stride_page", C.c_int64), ("stride_token", C.c_int64), ("stride_head", C.c_int64),
+                ("block_table", C.c_void_p), ("block_table_stride", C.c_int32),
+                ("page_size", C.c_int32)]
+
+
+class ActLayout(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_t", C.c_int64),
+                ("stride_h", C.c_int64)]
+
+
+_lib = None
+_inited = set()
+
+
+def load() -> C.CDLL:
+    """dlopen the library (no CUDA call is made)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise KascadeNativeError(
+                f"{LIB_PATH} is missing: build it with `python -m kascade_b200.build` "
+                "(there is no fallback implementation)")
+        lib = C.CDLL(LIB_PATH)
+        lib.kb200_last_error.restype = C.c_char_p
+        lib.kb200_decode_workspace_bytes.restype = C.c_size_t
+        lib.kb200_decode_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
+        lib.kb200_decode_default_splits.argtypes = [C.c_int, C.c_int, C.c_int]
+        lib.kb200_init.argtypes = [C.c_int]
+        vp, i64, i32, f32 = C.c_void_p, C.c_int64, C.c_int, C.c_float
+        lib.kb200_topk_select.argtypes = [vp, i64, i32, vp, vp, i32, vp, i64, vp, i64, vp]
+        lib.kb200_decode_sparse_paged.argtypes = [vp, i64, i64, C.POINTER(KvLayout), vp, i64, i64, vp,
+                                                  i32, vp, f32, vp, vp, vp, C.c_size_t, i32, i32, i32,
+                                                  i32, vp]
+        lib.kb200_decode_anchor_paged.argtypes = [vp, i64, i64, C.POINTER(KvLayout), vp, i32, f32, vp,
+                                                  vp, i64, vp, vp, vp, C.c_size_t, i32, i32, i32, i32,
+                                                  vp]
+        AL = C.POINTER(ActLayout)
+        lib.kb200_prefill_dense.argtypes = [AL, AL, AL, f32, vp, vp, i32, i32, i32, i32, vp]
+        lib.kb200_prefill_pool_scores.argtypes = [AL, AL, vp, f32, vp, i64, i32, i32, i32, i32, vp]
+        lib.kb200_prefill_sparse.argtypes = [AL, AL, AL, vp, i64, vp, vp, f32, vp, vp, i32, i32, i32,
+                                             i32, vp]
+        lib.kb200_prefill_budgets.argtypes = [vp, vp, i32, i32, i32, i32, f32, i32, vp]
+        lib.kb200_selftest_umma.argtypes = [vp, vp, vp, vp, vp]
+        _lib = lib
+    return _lib
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise KascadeNativeError(f"{what}: {load().kb200_last_error().decode()}")
+
+
+def init(device: Optional[int] = None) -> C.CDLL:
+    lib = load()
+    if not torch.cuda.is_available():
+        raise KascadeNativeError("kascade_b200 needs a CUDA device (sm_100a); none is visible")
+    dev = torch.cuda.current_device() if device is None else int(device)
+    if dev not in _inited:
+        _check(lib.kb200_init(dev), "kb200_init")
+        _inited.add(dev)
+    return lib
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _want(t: torch.Tensor, dtype, name: str):
+    if t.dtype != dtype or not t.is_cuda:
+        raise KascadeNativeError(f"{name}: expected a CUDA {dtype} tensor, got {t.dtype} on {t.device}")
+
+
+# ------------------------------------------------------------------------------------------------
+def topk_select(scores: torch.Tensor, n_valid: Optional[torch.Tensor], k_row: Optional[torch.Tensor],
+                k_max: int, out_idx: torch.Tensor, out_count: Optional[torch.Tensor], n_cols: Optional[int] = None):
+    """scores [..., row_stride] fp32 (last dim contiguous, rows equally spaced), out_idx [..., idx_stride]."""
+    lib = init(scores.device.index)
+    _want(scores, torch.float32, "scores")
+    _want(out_idx, torch.int32, "out_idx")
+    rows = scores.numel() // scores.shape[-1]
+    assert scores.is_contiguous() and out_idx.is_contiguous()
+    _check(lib.kb200_topk_select(_ptr(scores), scores.shape[-1], scores.shape[-1] if n_cols is None else n_cols,
+                                 _ptr(n_valid), _ptr(k_row), k_max, _ptr(out_idx), out_idx.shape[-1],
+                                 _ptr(out_count), rows, _stream()), "kb200_topk_select")
+
+
+def prefill_budgets(n_valid, k_row, batch, groups, tiles, k_max, pct, rolling):
+    lib = init(n_valid.device.index)
+    _check(lib.kb200_prefill_budgets(_ptr(n_valid), _ptr(k_row), batch, groups, tiles, k_max, float(pct),
+                                     int(bool(rolling)), _stream()), "kb200_prefill_budgets")
+
+
+def kv_layout_paged(k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], block_table: torch.Tensor) -> KvLayout:
+    """vLLM-style cache [num_pages, page_size, G, D] and block table [B, max_pages] int32."""
+    _want(k_cache, torch.float16, "k_cache")
+    assert k_cache.dim() == 4 and k_cache.stride(3) == 1
+    assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
+    if v_cache is not None:
+        assert v_cache.shape == k_cache.shape and v_cache.stride() == k_cache.stride()
+    return KvLayout(k_cache.data_ptr(), 0 if v_cache is None else v_cache.data_ptr(), 0, k_cache.stride(0),
+                    k_cache.stride(1), k_cache.stride(2), block_table.data_ptr(), block_table.stride(0),
+                    k_cache.shape[1])
+
+
+def kv_layout_contiguous(k: torch.Tensor, v: Optional[torch.Tensor], page_size: int = 16) -> KvLayout:
+    """HF cache view [B, G, L, D] (any batch / head / token strides, D contiguous)."""
+    _want(k, torch.float16, "k")
+    assert k.dim() == 4 and k.stride(3) == 1
+    if v is not None:
+        assert v.shape == k.shape and v.stride() == k.stride()
+    return KvLayout(k.data_ptr(), 0 if v is None else v.data_ptr(), k.stride(0), k.stride(2) * page_size,
+                    k.stride(2), k.stride(1), 0, 0, page_size)
+
+
+def decode_workspace(batch: int, heads: int, splits: int, device) -> torch.Tensor:
+    n = load().kb200_decode_workspace_bytes(batch, heads, splits)
+    return torch.empty(max(n, 16), dtype=torch.uint8, device=device)
+
+
+def decode_default_splits(batch: int, groups: int, max_keys: int) -> int:
+    init()
+    return load().kb200_decode_default_splits(batch, groups, max_keys)
+
+
+def decode_sparse_paged(q, kv: KvLayout, topk_idx, topk_count, k_max, head_map, scale, out, lse2=None,
+                        workspace=None, num_splits=0):
+    """q [B,H,D] fp16; topk_idx [B,G,kstride] int32; out [B,H,D] fp16 contiguous."""
+    lib = init(q.device.index)
+    _want(q, torch.float16, "q")
+    _want(out, torch.float16, "out")
+    _want(topk_idx, torch.int32, "topk_idx")
+    B, H, D = q.shape
+    G = topk_idx.shape[1]
+    assert D == HEAD_DIM and q.stride(2) == 1 and out.is_contiguous() and topk_idx.stride(2) == 1
+    _check(lib.kb200_decode_sparse_paged(
+        _ptr(q), q.stride(0), q.stride(1), C.byref(kv), _ptr(topk_idx), topk_idx.stride(0), topk_idx.stride(1),
+        _ptr(topk_count), k_max, _ptr(head_map), float(scale), _ptr(out), _ptr(lse2), _ptr(workspace),
+        0 if workspace is None else workspace.numel() * workspace.element_size(), B, H, G, num_splits, _stream()),
+        "kb200_decode_sparse_paged")
+
+
+def decode_anchor_paged(q, kv: KvLayout, seq_lens, max_seq_len, scale, logits, pooled, out, lse2,
+                        workspace=None, num_splits=0):
+    """q [B,H,D]; logits [B,H,stride] fp32; pooled [B,G,stride] fp32; out [B,H,D] fp16 or None."""
+    lib = init(q.device.index)
+    _want(q, torch.float16, "q")
+    _want(logits, torch.float32, "logits")
+    _want(pooled, torch.float32, "pooled")
+    B, H, D = q.shape
+    G = pooled.shape[1]
+    assert logits.is_contiguous() and pooled.is_contiguous() and logits.shape[-1] == pooled.shape[-1]
+    _check(lib.kb200_decode_anchor_paged(
+        _ptr(q), q.stride(0), q.stride(1), C.byref(kv), _ptr(seq_lens), max_seq_len, float(scale), _ptr(logits),
+        _ptr(pooled), logits.shape[-1], _ptr(out), _ptr(lse2), _ptr(workspace),
+        0 if workspace is None else workspace.numel() * workspace.element_size(), B, H, G, num_splits, _stream()),
+        "kb200_decode_anchor_paged")
+
+
+def act_layout(x: torch.Tensor) -> ActLayout:
+    """x indexed [B, L, heads, D] (any strides, D contiguous)."""
+    _want(x, torch.float16, "activation")
+    assert x.dim() == 4 and x.stride(3) == 1 and x.shape[3] == HEAD_DIM
+    return ActLayout(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2))
+
+
+def prefill_dense(q, k, v, scale, out, lse2):
+    """q [B,L,H,D], k/v [B,L,G,D] (views allowed); out [B,L,H,D] fp16 contiguous or None; lse2 [B,L,H] fp32 or None."""
+    lib = init(q.device.index)
+    B, L, H, _ = q.shape
+    G = k.shape[2]
+    ql, kl = act_layout(q), act_layout(k)
+    vl = act_layout(v) if v is not None else ActLayout(0, 0, 0, 0)
+    if out is not None:
+        _want(out, torch.float16, "out")
+        assert out.is_contiguous()
+    _check(lib.kb200_prefill_dense(C.byref(ql), C.byref(kl), C.byref(vl), float(scale), _ptr(out), _ptr(lse2),
+                                   B, L, H, G, _stream()), "kb200_prefill_dense")
+
+
+def prefill_pool_scores(q, k, lse2, scale, pooled):
+    """pooled [B,G,T,row_stride] fp32 contiguous."""
+    lib = init(q.device.index)
+    B, L, H, _ = q.shape
+    G = k.shape[2]
+    ql, kl = act_layout(q), act_layout(k)
+    _want(pooled, torch.float32, "pooled")
+    _want(lse2, torch.float32, "lse2")
+    assert pooled.is_contiguous() and lse2.is_contiguous()
+    _check(lib.kb200_prefill_pool_scores(C.byref(ql), C.byref(kl), _ptr(lse2), float(scale), _ptr(pooled),
+                                         pooled.shape[-1], B, L, H, G, _stream()), "kb200_prefill_pool_scores")
+
+
+def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=None):
+    """tile_idx [B,G,T,kstride] int32, tile_count [B,G,T] int32, out [B,L,H,D] fp16 contiguous."""
+    lib = init(q.device.index)
+    B, L, H, _ = q.shape
+    G = k.shape[2]
+    ql, kl, vl = act_layout(q), act_layout(k), act_layout(v)
+    _want(tile_idx, torch.int32, "tile_idx")
+    _want(tile_count, torch.int32, "tile_count")
+    _want(out, torch.float16, "out")
+    assert tile_idx.is_contiguous() and tile_count.is_contiguous() and out.is_contiguous()
+    _check(lib.kb200_prefill_sparse(C.byref(ql), C.byref(kl), C.byref(vl), _ptr(tile_idx), tile_idx.shape[-1],
+                                    _ptr(tile_count), _ptr(head_map), float(scale), _ptr(out), _ptr(lse2), B, L, H,
+                                    G, _stream()), "kb200_prefill_sparse")
+
+
+def selftest_umma(a: torch.Tensor, b: torch.Tensor):
+    lib = init(a.device.index)
+    out = torch.zeros(4, 128, 128, dtype=torch.float32, device=a.device)
+    status = torch.full((4,), -1, dtype=torch.int32, device=a.device)
+    _check(lib.kb200_selftest_umma(_ptr(a), _ptr(b), _ptr(out), _ptr(status), _stream()), "kb200_selftest_umma")
+    return out, status
