@@ -47,14 +47,22 @@ const char* kb200_last_error(void);
 /* ABI version of this header. */
 int kb200_abi_version(void);
 
+/* Every device-side wait of the tensor-core kernels is bounded; a kernel that gives up records a
+ * non-zero code in a device status word, releases what it holds and returns.  This call copies
+ * that word to *host_out (host pointer) and clears it.  It synchronises the device, so call it at
+ * a point where the caller synchronises anyway.  0 = no kernel gave up.  No counterpart in the
+ * reference (its kernels spin without a limit). */
+int kb200_read_status(int* host_out);
+
 /* ---- Top-k selection (replaces the torch.topk call sites,
  *      strategies/EfficientKascadeStrategy.py:82,90,111) ---------------------------------------- */
 
 /* Exact Top-k of each row of a fp32 score matrix by radix select.
  *   scores      [rows, row_stride]      only the first n_valid[r] entries of row r are candidates
  *   n_valid     [rows] int32            (NULL: every row has n_cols candidates)
- *   k_row       [rows] int32            budget of row r (NULL: k_max for every row)
- *   out_idx     [rows, idx_stride] int32  receives min(k_row[r], n_valid[r]) indices in ASCENDING
+ *   k_row       [rows] int32            budget of row r, capped at k_max (NULL: k_max for every row)
+ *   out_idx     [rows, idx_stride] int32, idx_stride >= k_max; receives min(k_row[r], k_max,
+ *                                       n_valid[r]) indices in ASCENDING
  *                                       index order; entries beyond that count are left untouched
  *   out_count   [rows] int32            receives that count
  * Ties at the k-th score are resolved towards the lowest index.  NaNs are not supported. */

@@ -22,7 +22,7 @@ EXPORTS = [
     "kb200_init", "kb200_last_error", "kb200_abi_version", "kb200_topk_select",
     "kb200_decode_workspace_bytes", "kb200_decode_default_splits", "kb200_decode_sparse_paged",
     "kb200_decode_anchor_paged", "kb200_prefill_dense", "kb200_prefill_pool_scores",
-    "kb200_prefill_sparse", "kb200_prefill_budgets", "kb200_selftest_umma",
+    "kb200_prefill_sparse", "kb200_prefill_budgets", "kb200_selftest_umma", "kb200_read_status",
 ]
 
 
@@ -93,6 +93,13 @@ def init(device: Optional[int] = None) -> C.CDLL:
         _check(lib.kb200_init(dev), "kb200_init")
         _inited.add(dev)
     return lib
+
+
+def read_status() -> int:
+    """Device status word (0 = every kernel ran to completion); synchronises the device."""
+    out = C.c_int(0)
+    _check(init().kb200_read_status(C.byref(out)), "kb200_read_status")
+    return out.value
 
 
 def _stream() -> C.c_void_p:

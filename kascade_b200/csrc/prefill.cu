@@ -1,3 +1,511 @@
-// placeholder until the tile-prefill kernels land
+// Tile prefill kernels on the sm_100a tensor-core path (tcgen05.mma, accumulators in tensor memory).
+//
+// One CTA owns one query tile: 32 consecutive queries x the 4 query heads of one KV head = 128
+// rows (row = 4 * query_in_tile + head), the M dimension of every MMA.  Keys arrive in blocks of
+// 128 rows.  The same kernel body serves four modes:
+//
+//   kDenseAttn  causal attention over keys 0 .. last query of the tile; writes O and lse2
+//               (replaces `prefill`, kernels/flash_attention/recompute_kascade_gqa_prefill.py:224-274)
+//   kDenseLse   the same without V: lse2 only
+//               (replaces `compute_scores`, recompute_kascade_gqa_prefill.py:276-312)
+//   kSparse     keys = the tile's selected index row followed by the tile's own keys
+//               (replaces `main_kernel`, kernels/flash_attention/reuse_kascade_gqa_prefill.py:146-198)
+//   kPool       S^T = K_block . Q_tile^T so that tensor-memory lanes are keys; each reducer thread
+//               sums exp2(s * scale2 - lse2[row]) over the 128 rows of the tile for its key
+//               (replaces `aggregate`, recompute_kascade_gqa_prefill.py:171-222)
+//
+// Warp roles (288 threads): warps 0-3 softmax / reducer (one thread per tensor-memory lane),
+// warps 4-7 producers (cp.async 16-byte chunks, 16 lanes per 256-byte row, written in the
+// 128-byte-swizzled operand layout of umma.cuh), warp 8 issues the MMAs from one thread.
+// Hand-offs are mbarriers; every wait is bounded (umma::mbar_wait) and a kernel that gives up
+// records a code in the device status word, drains its copies, frees its tensor memory and returns.
+//
+// Tensor memory (512 columns): S0 [0,128), S1 [128,256), O [256,384).  P (fp16) overwrites the
+// first 64 columns of the S buffer it was computed from and is the A operand of the P.V product.
 #include "common.cuh"
-namespace kb200 { int init_prefill() { return 0; } }
+#include "umma.cuh"
+
+namespace kb200 {
+
+enum PrefillMode { kDenseAttn = 0, kDenseLse = 1, kSparse = 2, kPool = 3 };
+
+constexpr int kPfThreads = 288;
+constexpr int kStageBytes = 128 * kD * 2;     // one 128-row operand tile (32 KB)
+constexpr int kNK = 3, kNV = 3;               // ring depths
+
+__device__ int g_status_word = 0;
+
+struct PrefillParams {
+  const __half* q; int64_t q_sb, q_st, q_sh;
+  const __half* k; int64_t k_sb, k_st, k_sh;
+  const __half* v; int64_t v_sb, v_st, v_sh;
+  const int32_t* tile_idx; int64_t idx_stride;
+  const int32_t* tile_count;
+  const int32_t* head_map;
+  float scale2;
+  __half* out;
+  float* lse2;
+  const float* lse2_in;
+  float* pooled; int64_t pooled_stride;
+  int B, L, H, G, T;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const PrefillParams p) {
+  using namespace umma;
+  constexpr bool HAS_V = MODE == kDenseAttn || MODE == kSparse;
+  constexpr bool POOL = MODE == kPool;
+  constexpr bool GATHER = MODE == kSparse;
+  constexpr int GROUPS_PER_BLOCK = HAS_V ? 2 : 1;     // cp.async groups committed per key block
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_q, bar_kfull[kNK], bar_kempty[kNK], bar_vfull[kNV], bar_vempty[kNV];
+  __shared__ uint64_t bar_sfull[2], bar_pready[2], bar_odone;
+  __shared__ uint32_t tmem_sh;
+  __shared__ int give_up;
+  __shared__ float lse_s[128];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t = (int)gridDim.x - 1 - (int)blockIdx.x;   // long tiles first
+  const int g = blockIdx.y, b = blockIdx.z;
+  const int tile_start = t * kTile;
+  const int rows_valid = min(kTile, p.L - tile_start);
+
+  int count = 0, total;
+  const int32_t* idx_row = nullptr;
+  if (GATHER) {
+    const int src_g = p.head_map ? p.head_map[g] : g;
+    const int64_t r = ((int64_t)b * p.G + src_g) * p.T + t;
+    count = p.tile_count[r];
+    count = max(0, min(count, (int)min((int64_t)tile_start, p.idx_stride)));
+    idx_row = p.tile_idx + r * p.idx_stride;
+    total = count + rows_valid;
+  } else if (POOL) {
+    total = tile_start;
+  } else {
+    total = tile_start + rows_valid;
+  }
+  const int nb = (total + 127) >> 7;
+  if (nb == 0) return;                                   // pool pass of tile 0: no earlier keys
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t q_s = smem_addr(smem);
+  const uint32_t k_s = q_s + kStageBytes;
+  const uint32_t v_s = k_s + kNK * kStageBytes;
+
+  if (tid == 0) {
+    mbar_init(&bar_q, 128);
+    for (int i = 0; i < kNK; ++i) { mbar_init(&bar_kfull[i], 128); mbar_init(&bar_kempty[i], 1); }
+    for (int i = 0; i < kNV; ++i) { mbar_init(&bar_vfull[i], 128); mbar_init(&bar_vempty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar_sfull[i], 1); mbar_init(&bar_pready[i], 128); }
+    mbar_init(&bar_odone, 1);
+    mbar_fence_init();
+    give_up = 0;
+  }
+  if (warp == 8) {
+    tmem_alloc(&tmem_sh, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_sh;
+  const uint32_t t_s0 = tmem, t_o = tmem + 256;
+
+  if (warp >= 4 && warp < 8) {
+    // ================================ producers ================================================
+    const int pw = warp - 4, ptid = tid - 128;
+    const __half* qb = p.q + (int64_t)b * p.q_sb;
+#pragma unroll 4
+    for (int it = 0; it < 16; ++it) {
+      const int id = it * 128 + ptid, row = id >> 4, c = id & 15;
+      const int tok = tile_start + (row >> 2), head = g * kHg + (row & 3);
+      const uint32_t dst = q_s + tile_off(row, c, 128);
+      if (tok < p.L) {
+        cp16(dst, qb + (int64_t)tok * p.q_st + (int64_t)head * p.q_sh + c * 8);
+      } else {
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(dst), "r"(0u));
+      }
+    }
+    cp_commit();
+    const __half* kb = p.k + (int64_t)b * p.k_sb + (int64_t)g * p.k_sh;
+    const __half* vb = HAS_V ? p.v + (int64_t)b * p.v_sb + (int64_t)g * p.v_sh : nullptr;
+    bool ok = true;
+    for (int j = 0; j < nb && ok; ++j) {
+      const int s = j * 128 + pw * 32 + lane;
+      int key;
+      if (GATHER) key = s < count ? __ldg(idx_row + s) : tile_start + (s - count);
+      else key = s;
+      if (s >= total) key = 0;
+      key = max(0, min(key, p.L - 1));
+      const int64_t offk = (int64_t)key * p.k_st;
+      const int64_t offv = HAS_V ? (int64_t)key * p.v_st : 0;
+      ok = mbar_wait(&bar_kempty[j % kNK], ((j / kNK) & 1) ^ 1, &give_up, 11);
+      if (!ok) break;
+      {
+        const uint32_t dst = k_s + (j % kNK) * kStageBytes;
+        const int c = lane & 15;
+#pragma unroll 4
+        for (int it = 0; it < 16; ++it) {
+          const int rw = it * 2 + (lane >> 4);
+          const int64_t o = __shfl_sync(0xFFFFFFFFu, offk, rw);
+          cp16(dst + tile_off(pw * 32 + rw, c, 128), kb + o + c * 8);
+        }
+        cp_commit();
+      }
+      if (HAS_V) {
+        ok = mbar_wait(&bar_vempty[j % kNV], ((j / kNV) & 1) ^ 1, &give_up, 12);
+        if (!ok) break;
+        const uint32_t dst = v_s + (j % kNV) * kStageBytes;
+        const int c = lane & 15;
+#pragma unroll 4
+        for (int it = 0; it < 16; ++it) {
+          const int rw = it * 2 + (lane >> 4);
+          const int64_t o = __shfl_sync(0xFFFFFFFFu, offv, rw);
+          cp16(dst + tile_off(pw * 32 + rw, c, 128), vb + o + c * 8);
+        }
+        cp_commit();
+      }
+      // everything older than this block's groups has landed: publish it to the async proxy
+      cp_wait<GROUPS_PER_BLOCK>();
+      fence_proxy_async_smem();
+      if (j == 0) {
+        mbar_arrive(&bar_q);
+      } else {
+        mbar_arrive(&bar_kfull[(j - 1) % kNK]);
+        if (HAS_V) mbar_arrive(&bar_vfull[(j - 1) % kNV]);
+      }
+    }
+    cp_wait<0>();
+    fence_proxy_async_smem();
+    if (ok) {
+      mbar_arrive(&bar_kfull[(nb - 1) % kNK]);
+      if (HAS_V) mbar_arrive(&bar_vfull[(nb - 1) % kNV]);
+    }
+  } else if (warp == 8) {
+    // ================================ MMA issuer ===============================================
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
+      bool ok = mbar_wait(&bar_q, 0, &give_up, 21);
+      auto issue_qk = [&](int j) -> bool {
+        if (!mbar_wait(&bar_kfull[j % kNK], (j / kNK) & 1, &give_up, 22)) return false;
+        tc_fence_after();
+        const uint32_t ks_addr = k_s + (j % kNK) * kStageBytes;
+        const uint32_t d = t_s0 + (j & 1) * 128;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t off = (ks >> 2) * (kStageBytes / 2) + (ks & 3) * 32;
+          const uint64_t dq = desc_kmajor(q_s + off), dk = desc_kmajor(ks_addr + off);
+          if (POOL) mma_ss(d, dk, dq, idesc_qk, ks > 0);     // S^T: lanes = keys
+          else mma_ss(d, dq, dk, idesc_qk, ks > 0);          // S: lanes = (query, head) rows
+        }
+        mma_commit(&bar_kempty[j % kNK]);
+        mma_commit(&bar_sfull[j & 1]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < nb && ok; ++j) {
+        if (j + 1 < nb) {
+          if (!HAS_V && j >= 1) {
+            ok = mbar_wait(&bar_pready[(j - 1) & 1], ((j - 1) >> 1) & 1, &give_up, 23);
+            if (!ok) break;
+          }
+          ok = issue_qk(j + 1);
+          if (!ok) break;
+        }
+        if (HAS_V) {
+          ok = mbar_wait(&bar_pready[j & 1], (j >> 1) & 1, &give_up, 24);
+          if (!ok) break;
+          ok = mbar_wait(&bar_vfull[j % kNV], (j / kNV) & 1, &give_up, 25);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t vs_addr = v_s + (j % kNV) * kStageBytes;
+          const uint32_t a = t_s0 + (j & 1) * 128;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            mma_ts(t_o, a + ks * 8, desc_mnmajor(vs_addr + ks * 2048, kStageBytes / 2), idesc_pv,
+                   (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          mma_commit(&bar_vempty[j % kNV]);
+          mma_commit(&bar_odone);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (!POOL) {
+    // ================================ softmax (one thread per row) =============================
+    const int row = tid, q_local = row >> 2;
+    const int tok = tile_start + q_local;
+    const int off = GATHER ? count : tile_start;      // slot - off = key position inside the tile
+    const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nb; ++j) {
+      ok = mbar_wait(&bar_sfull[j & 1], (j >> 1) & 1, &give_up, 31);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t ts = t_s0 + (j & 1) * 128 + lane_sel;
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int part = 0; part < 4; ++part) tmem_ld32(ts + part * 32, sr[part]);
+      tmem_wait_ld();
+      const bool need_mask = (j * 128 + 127 - off) > 0;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int part = 0; part < 4; ++part) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(sr[part][i]) * p.scale2;
+          if (need_mask && (j * 128 + part * 32 + i - off) > q_local) x = -INFINITY;
+          sr[part][i] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = ex2(m_run - m_new);
+      float sum = 0.f;
+      if (HAS_V) {
+        uint32_t pr[32];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int c = half * 64 + i * 2;
+            float p0 = ex2(__uint_as_float(sr[c >> 5][c & 31]) - m_new);
+            float p1 = ex2(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]) - m_new);
+            sum += p0 + p1;
+            pr[i] = pack2(p0, p1);
+          }
+          tmem_st32(ts + half * 32, pr);
+        }
+      } else {
+#pragma unroll
+        for (int part = 0; part < 4; ++part)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sum += ex2(__uint_as_float(sr[part][i]) - m_new);
+      }
+      l_run = l_run * alpha + sum;
+      m_run = m_new;
+      if (HAS_V && j > 0) {
+        ok = mbar_wait(&bar_odone, (j - 1) & 1, &give_up, 32);
+        if (!ok) break;
+        tc_fence_after();
+        if (!__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
+#pragma unroll 1
+          for (int part = 0; part < 4; ++part) {
+            uint32_t orr[32];
+            tmem_ld32(t_o + lane_sel + part * 32, orr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+            tmem_st32(t_o + lane_sel + part * 32, orr);
+          }
+        }
+      }
+      if (HAS_V) tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar_pready[j & 1]);
+    }
+    // ---- epilogue --------------------------------------------------------------------------
+    if (ok && HAS_V) {
+      ok = mbar_wait(&bar_odone, (nb - 1) & 1, &give_up, 33);
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.0f / l_run;
+        __half* orow = p.out + (((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)) * kD;
+#pragma unroll 1
+        for (int part = 0; part < 4; ++part) {
+          uint32_t orr[32];
+          tmem_ld32(t_o + lane_sel + part * 32, orr);
+          tmem_wait_ld();
+          if (tok < p.L) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 w;
+              w.x = pack2(__uint_as_float(orr[i * 8 + 0]) * inv, __uint_as_float(orr[i * 8 + 1]) * inv);
+              w.y = pack2(__uint_as_float(orr[i * 8 + 2]) * inv, __uint_as_float(orr[i * 8 + 3]) * inv);
+              w.z = pack2(__uint_as_float(orr[i * 8 + 4]) * inv, __uint_as_float(orr[i * 8 + 5]) * inv);
+              w.w = pack2(__uint_as_float(orr[i * 8 + 6]) * inv, __uint_as_float(orr[i * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + part * 32 + i * 8) = w;
+            }
+          }
+        }
+      }
+    }
+    if (ok && p.lse2 && tok < p.L)
+      p.lse2[((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)] = m_run + log2f(l_run);
+  } else {
+    // ================================ pooled-score reducer (one thread per key) ================
+    {
+      const int tok = tile_start + (tid >> 2);
+      lse_s[tid] = tok < p.L ? p.lse2_in[((int64_t)b * p.L + tok) * p.H + g * kHg + (tid & 3)] : INFINITY;
+    }
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+    float* prow = p.pooled + (((int64_t)b * p.G + g) * p.T + t) * p.pooled_stride;
+    for (int j = 0; j < nb; ++j) {
+      if (!mbar_wait(&bar_sfull[j & 1], (j >> 1) & 1, &give_up, 41)) break;
+      tc_fence_after();
+      const uint32_t ts = t_s0 + (j & 1) * 128 + lane_sel;
+      float acc = 0.f;
+#pragma unroll 1
+      for (int part = 0; part < 4; ++part) {
+        uint32_t sr[32];
+        tmem_ld32(ts + part * 32, sr);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc += ex2(fmaf(__uint_as_float(sr[i]), p.scale2, -lse_s[part * 32 + i]));
+      }
+      tc_fence_before();
+      mbar_arrive(&bar_pready[j & 1]);
+      const int key = j * 128 + tid;
+      if (key < tile_start) prow[key] = acc;
+    }
+  }
+
+  // ---- teardown: every role ends up here, also after a wait that gave up ----------------------
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 8) tmem_dealloc(tmem, 512);
+  if (tid == 0 && give_up != 0) atomicCAS(&g_status_word, 0, give_up);
+}
+
+constexpr int kSmemAttn = 1024 + kStageBytes * (1 + kNK + kNV);
+constexpr int kSmemNoV = 1024 + kStageBytes * (1 + kNK);
+
+int init_prefill() {
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kDenseAttn>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn));
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kSparse>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn));
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kDenseLse>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemNoV));
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kPool>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemNoV));
+  return 0;
+}
+
+static int fill_act(const kb200_act_layout* a, const __half** ptr, int64_t* sb, int64_t* st, int64_t* sh,
+                    const char* what) {
+  KB_REQUIRE(a && a->ptr, "prefill: %s is null", what);
+  KB_REQUIRE((reinterpret_cast<uintptr_t>(a->ptr) & 15) == 0 && a->stride_b % 8 == 0 && a->stride_t % 8 == 0 &&
+                 a->stride_h % 8 == 0,
+             "prefill: %s must be 16-byte aligned with strides that are multiples of 8 elements", what);
+  *ptr = static_cast<const __half*>(a->ptr);
+  *sb = a->stride_b;
+  *st = a->stride_t;
+  *sh = a->stride_h;
+  return 0;
+}
+
+static int check_shape(int batch, int seq_len, int H, int G) {
+  KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
+  KB_REQUIRE(batch >= 0 && seq_len >= 0, "prefill: negative size");
+  KB_REQUIRE(G > 0 && H == G * kHg,
+             "prefill: %d query heads / %d KV heads; exactly %d query heads per KV head are supported", H, G, kHg);
+  KB_REQUIRE(batch <= 65535 && G <= 65535, "prefill: batch and KV heads must fit a grid dimension");
+  return 0;
+}
+
+}  // namespace kb200
+
+extern "C" int kb200_read_status(int* host_out) {
+  using namespace kb200;
+  KB_REQUIRE(host_out, "read_status: null pointer");
+  int zero = 0;
+  KB_CUDA(cudaMemcpyFromSymbol(host_out, g_status_word, sizeof(int)));
+  KB_CUDA(cudaMemcpyToSymbol(g_status_word, &zero, sizeof(int)));
+  return 0;
+}
+
+extern "C" int kb200_prefill_dense(const kb200_act_layout* q, const kb200_act_layout* k,
+                                   const kb200_act_layout* v, float softmax_scale, void* out, float* lse2,
+                                   int batch, int seq_len, int num_q_heads, int num_kv_heads, void* stream) {
+  using namespace kb200;
+  if (check_shape(batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
+  KB_REQUIRE(out || lse2, "prefill_dense: nothing to compute (out and lse2 are both null)");
+  if (batch == 0 || seq_len == 0) return 0;
+  PrefillParams p{};
+  if (fill_act(q, &p.q, &p.q_sb, &p.q_st, &p.q_sh, "q") != 0) return -1;
+  if (fill_act(k, &p.k, &p.k_sb, &p.k_st, &p.k_sh, "k") != 0) return -1;
+  if (out && fill_act(v, &p.v, &p.v_sb, &p.v_st, &p.v_sh, "v") != 0) return -1;
+  KB_REQUIRE(!out || (reinterpret_cast<uintptr_t>(out) & 15) == 0, "prefill_dense: out must be 16-byte aligned");
+  p.scale2 = softmax_scale * kLog2e;
+  p.out = static_cast<__half*>(out);
+  p.lse2 = lse2;
+  p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
+  dim3 grid(p.T, num_kv_heads, batch);
+  if (out) tile_prefill_kernel<kDenseAttn><<<grid, kPfThreads, kSmemAttn, (cudaStream_t)stream>>>(p);
+  else tile_prefill_kernel<kDenseLse><<<grid, kPfThreads, kSmemNoV, (cudaStream_t)stream>>>(p);
+  KB_CHECK_LAUNCH("tile_prefill_kernel<dense>");
+  return 0;
+}
+
+extern "C" int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_act_layout* k,
+                                         const float* lse2, float softmax_scale, float* pooled,
+                                         int64_t row_stride, int batch, int seq_len, int num_q_heads,
+                                         int num_kv_heads, void* stream) {
+  using namespace kb200;
+  if (check_shape(batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
+  KB_REQUIRE(lse2 && pooled, "prefill_pool_scores: null pointer");
+  KB_REQUIRE(row_stride >= seq_len, "prefill_pool_scores: row_stride (%lld) smaller than seq_len (%d)",
+             (long long)row_stride, seq_len);
+  if (batch == 0 || seq_len == 0) return 0;
+  PrefillParams p{};
+  if (fill_act(q, &p.q, &p.q_sb, &p.q_st, &p.q_sh, "q") != 0) return -1;
+  if (fill_act(k, &p.k, &p.k_sb, &p.k_st, &p.k_sh, "k") != 0) return -1;
+  p.scale2 = softmax_scale * kLog2e;
+  p.lse2_in = lse2;
+  p.pooled = pooled;
+  p.pooled_stride = row_stride;
+  p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
+  dim3 grid(p.T, num_kv_heads, batch);
+  tile_prefill_kernel<kPool><<<grid, kPfThreads, kSmemNoV, (cudaStream_t)stream>>>(p);
+  KB_CHECK_LAUNCH("tile_prefill_kernel<pool>");
+  return 0;
+}
+
+extern "C" int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_layout* k,
+                                    const kb200_act_layout* v, const int32_t* tile_idx, int64_t idx_stride,
+                                    const int32_t* tile_count, const int32_t* head_map, float softmax_scale,
+                                    void* out, float* lse2, int batch, int seq_len, int num_q_heads,
+                                    int num_kv_heads, void* stream) {
+  using namespace kb200;
+  if (check_shape(batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
+  KB_REQUIRE(tile_idx && tile_count && out, "prefill_sparse: null pointer");
+  KB_REQUIRE(idx_stride >= 0, "prefill_sparse: negative idx_stride");
+  KB_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15) == 0, "prefill_sparse: out must be 16-byte aligned");
+  if (batch == 0 || seq_len == 0) return 0;
+  PrefillParams p{};
+  if (fill_act(q, &p.q, &p.q_sb, &p.q_st, &p.q_sh, "q") != 0) return -1;
+  if (fill_act(k, &p.k, &p.k_sb, &p.k_st, &p.k_sh, "k") != 0) return -1;
+  if (fill_act(v, &p.v, &p.v_sb, &p.v_st, &p.v_sh, "v") != 0) return -1;
+  p.tile_idx = tile_idx;
+  p.idx_stride = idx_stride;
+  p.tile_count = tile_count;
+  p.head_map = head_map;
+  p.scale2 = softmax_scale * kLog2e;
+  p.out = static_cast<__half*>(out);
+  p.lse2 = lse2;
+  p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
+  dim3 grid(p.T, num_kv_heads, batch);
+  tile_prefill_kernel<kSparse><<<grid, kPfThreads, kSmemAttn, (cudaStream_t)stream>>>(p);
+  KB_CHECK_LAUNCH("tile_prefill_kernel<sparse>");
+  return 0;
+}

@@ -38,7 +38,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     int n = n_valid ? n_valid[row] : n_cols;
     n = max(0, min(n, n_cols));
-    int k = k_row ? k_row[row] : k_max;
+    int k = k_row ? min(k_row[row], k_max) : k_max;
     k = max(0, min(k, n));
     int32_t* out = out_idx + row * idx_stride;
     if (tid == 0 && out_count) out_count[row] = k;
@@ -179,8 +179,8 @@ extern "C" int kb200_topk_select(const float* scores, int64_t row_stride, int n_
              (long long)row_stride);
   KB_REQUIRE(row_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(scores) & 15) == 0,
              "topk_select: rows must be 16-byte aligned (row_stride %% 4 == 0)");
-  KB_REQUIRE(idx_stride >= (int64_t)k_max || k_row != nullptr,
-             "topk_select: idx_stride (%lld) smaller than k_max (%d)", (long long)idx_stride, k_max);
+  KB_REQUIRE(idx_stride >= (int64_t)k_max, "topk_select: idx_stride (%lld) smaller than k_max (%d)",
+             (long long)idx_stride, k_max);
   if (rows == 0) return 0;
   int64_t grid = rows < (int64_t)sm_count() * 64 ? rows : (int64_t)sm_count() * 64;
   topk_select_kernel<<<(unsigned)grid, kTopkThreads, 0, (cudaStream_t)stream>>>(

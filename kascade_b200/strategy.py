@@ -1,0 +1,263 @@
+"""Host side of the Kascade hot path: the ``efficient_kascade`` attention strategy.
+
+Mirrors the plugin interface of the reference (strategies/Strategy.py:8-27,
+strategies/EfficientKascadeStrategy.py:16-168): same constructor arguments, the same
+``attention_forward(module, query, key, value, attention_mask, scaling, dropout, **kw)`` hook that
+HF attention modules call once per layer in layer order, the same ``register_attention`` into the
+HF registries and the same ``.npy`` head-mapping lookup (strategies/KascadeStrategy.py:174-183).
+All arithmetic runs in libkascade_b200.so through :mod:`kascade_b200._native`; PyTorch only owns
+device memory and the stream.
+
+Selection semantics follow the reference's PyTorch ``KascadeStrategy`` (the parity oracle):
+budget ``min(max(128, int(k/100*Lk)), Lk) - tile_size`` (strategies/KascadeStrategy.py:127-129),
+rolling prefill budgets ``max(128, k*tile_start//100)`` (:134-139), keys at or after a tile's
+first query are never candidates (:83), layer 0 dense (:99).  Index rows are stored per query tile
+([B, G, T, k], as in strategies/EfficientKascadeStrategy.py:82-84) in ascending key order with an
+explicit count per row.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _native as nat
+
+__all__ = ["Strategy", "EfficientKascadeStrategy", "topk_budget"]
+
+
+def topk_budget(pct: float, lk: int, tile_size: int) -> int:
+    """strategies/KascadeStrategy.py:127-129."""
+    k = min(max(128, int((pct / 100) * lk)), lk)
+    if tile_size > 1:
+        k -= tile_size
+    return k
+
+
+class Strategy:
+    """strategies/Strategy.py:8-27: a named attention function that registers itself."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self.register_attention()
+
+    def register_attention(self):
+        pass
+
+    def attention_forward(self, module, query, key, value, attention_mask, scaling, dropout=0.0, **kwargs):
+        pass
+
+
+class EfficientKascadeStrategy(Strategy):
+    """Drop-in for the reference's ``EfficientKascadeStrategy``.
+
+    Extra keyword arguments (not in the reference) are keyword-only: ``head_mapping`` passes the
+    ``[num_layers][G]`` table directly instead of reading the ``.npy`` file, ``register`` skips the
+    HF registration (for use without transformers)."""
+
+    def __init__(self, recompute_layers: List[int], model_name: str, k=1, tile_size=1, rolling_prefill=False,
+                 block_size=12288, *, head_mapping: Optional[Sequence[Sequence[int]]] = None,
+                 register: bool = True):
+        if recompute_layers is None:
+            raise ValueError("recompute_layers cannot be None for EfficientKascadeStrategy")
+        if not (0 <= k <= 100):
+            raise AssertionError(f"Invalid k: {k}. It should be between 0 and 100%.")
+        if tile_size != nat.TILE:
+            # the reference only ships kernels for tile_size 32 (README.md:74)
+            raise ValueError(f"tile_size must be {nat.TILE}, got {tile_size}")
+        self.k = k
+        self.tile_size = tile_size
+        self.rolling_prefill = rolling_prefill
+        self._block_size = block_size          # accepted for signature parity; the kernels tile on their own
+        self.recompute_layers = list(recompute_layers)
+        self._heads, self._groups, self._dim = 32, 8, nat.HEAD_DIM
+        self._head_mapping = [list(map(int, r)) for r in head_mapping] if head_mapping is not None \
+            else self.get_head_mapping(model_name)
+        self._register = register
+        # cross-layer state written by anchor layers (strategies/KascadeStrategy.py:95,133)
+        self._tile_idx: Optional[torch.Tensor] = None       # prefill [B,G,T,k]
+        self._tile_count: Optional[torch.Tensor] = None     # prefill [B,G,T]
+        self._dec_idx: Optional[torch.Tensor] = None        # decode  [B,G,k]
+        self._dec_count: Optional[torch.Tensor] = None      # decode  [B,G]
+        self._dec_kmax = 0
+        self._map_dev: Dict[tuple, torch.Tensor] = {}
+        self._buf: Dict[str, torch.Tensor] = {}
+        super().__init__("efficient_kascade")
+
+    # ------------------------------------------------------------------------------------------
+    def get_head_mapping(self, model_name: str):
+        """strategies/KascadeStrategy.py:174-183 (path relative to the working directory)."""
+        try:
+            base = model_name.split("/")[-1]
+            path = f"./results/head_mappings/{base}_layers_{'_'.join(map(str, self.recompute_layers))}.npy"
+            return np.load(path).tolist()
+        except Exception:
+            raise ValueError(f"Head mapping file not found for model {model_name} with layers {self.recompute_layers}.")
+
+    def register_attention(self):
+        """strategies/EfficientKascadeStrategy.py:163-168."""
+        if not getattr(self, "_register", True):
+            return
+        from transformers.masking_utils import ALL_MASK_ATTENTION_FUNCTIONS
+        from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+
+        def _fwd(module, query, key, value, attention_mask, scaling, dropout=0.0, **kwargs):
+            return self.attention_forward(module, query, key, value, attention_mask, scaling, dropout=dropout, **kwargs)
+
+        ALL_MASK_ATTENTION_FUNCTIONS.register(self.name, ALL_MASK_ATTENTION_FUNCTIONS["sdpa"])
+        ALL_ATTENTION_FUNCTIONS.register(self.name, _fwd)
+
+    def is_anchor(self, layer_idx: int) -> bool:
+        return layer_idx == 0 or layer_idx in self.recompute_layers
+
+    # ------------------------------------------------------------------------------------------
+    def _scratch(self, name: str, shape, dtype, device) -> torch.Tensor:
+        """Grow-only cache of device buffers, so steady-state calls allocate nothing."""
+        n = int(math.prod(shape))
+        buf = self._buf.get(name)
+        if buf is None or buf.numel() < n or buf.dtype != dtype or buf.device != device:
+            buf = torch.empty(max(n, 1), dtype=dtype, device=device)
+            self._buf[name] = buf
+        return buf[:n].view(*shape)
+
+    def _mapping(self, layer_idx: int, device) -> torch.Tensor:
+        key = (layer_idx, device)
+        m = self._map_dev.get(key)
+        if m is None:
+            m = torch.tensor(self._head_mapping[layer_idx], dtype=torch.int32, device=device)
+            self._map_dev[key] = m
+        return m
+
+    @staticmethod
+    def _token_major(x: torch.Tensor) -> torch.Tensor:
+        """[B, heads, L, D] -> a [B, L, heads, D] view with D contiguous and 16-byte aligned strides."""
+        y = x.transpose(1, 2)
+        if y.stride(3) != 1 or any(s % 8 for s in y.stride()[:3]) or y.data_ptr() % 16:
+            y = y.contiguous()
+        return y
+
+    # ------------------------------------------------------------------------------------------
+    def attention_forward(self, module, query, key, value, attention_mask, scaling, dropout=0.0, **kwargs):
+        """query [B,H,Lq,D], key/value [B,G,Lk,D] -> (out [B,Lq,H,D], None).
+
+        Like the reference (strategies/EfficientKascadeStrategy.py:126-161) the mask is not read:
+        prompts are causal and unpadded, a decode step attends to the whole cache."""
+        if query.dtype != torch.float16:
+            raise nat.KascadeNativeError(f"efficient_kascade computes in fp16; got {query.dtype}")
+        B, H, Lq, D = query.shape
+        G, Lk = key.shape[1], key.shape[2]
+        layer = int(module.layer_idx)
+        if Lq == 1:
+            kv = nat.kv_layout_contiguous(*self._cache_views(key, value))
+            seq_lens = self._scratch("seq_lens_full", (B,), torch.int32, query.device)
+            seq_lens.fill_(Lk)
+            dense = Lk <= 128                      # strategies/EfficientKascadeStrategy.py:137-140
+            out = self._decode(layer, query[:, :, 0], kv, seq_lens, Lk, scaling, G, dense_only=dense)
+            return out.unsqueeze(1), None
+        if Lq != Lk:
+            raise NotImplementedError("prefill expects the whole prompt (Lq == Lk); chunked prefill is not supported")
+        q, k, v = self._token_major(query), self._token_major(key), self._token_major(value)
+        if Lk <= 128:
+            out = torch.empty(B, Lq, H, D, dtype=torch.float16, device=query.device)
+            nat.prefill_dense(q, k, v, scaling, out, None)
+            return out, None
+        return self._prefill(layer, q, k, v, scaling), None
+
+    @staticmethod
+    def _cache_views(key, value):
+        if key.stride(3) != 1 or any(s % 8 for s in key.stride()[:3]) or key.stride() != value.stride():
+            key, value = key.contiguous(), value.contiguous()
+        return key, value
+
+    # -- prefill -----------------------------------------------------------------------------------
+    def _prefill(self, layer: int, q, k, v, scaling) -> torch.Tensor:
+        B, L, H, D = q.shape
+        G = k.shape[2]
+        dev = q.device
+        T = -(-L // self.tile_size)
+        out = torch.empty(B, L, H, D, dtype=torch.float16, device=dev)
+        if self.is_anchor(layer):
+            kk = topk_budget(self.k, L, self.tile_size)
+            lse2 = self._scratch("lse2", (B, L, H), torch.float32, dev)
+            nat.prefill_dense(q, k, v if layer == 0 else None, scaling, out if layer == 0 else None, lse2)
+            stride = -(-L // 128) * 128
+            pooled = self._scratch("pooled", (B, G, T, stride), torch.float32, dev)
+            nat.prefill_pool_scores(q, k, lse2, scaling, pooled)
+            n_valid = self._scratch("n_valid", (B, G, T), torch.int32, dev)
+            k_row = self._scratch("k_row", (B, G, T), torch.int32, dev)
+            nat.prefill_budgets(n_valid, k_row, B, G, T, kk, self.k, self.rolling_prefill and L > 128)
+            self._tile_idx = self._scratch("tile_idx", (B, G, T, max(kk, 1)), torch.int32, dev)
+            self._tile_count = self._scratch("tile_count", (B, G, T), torch.int32, dev)
+            nat.topk_select(pooled, n_valid, k_row, kk, self._tile_idx, self._tile_count, n_cols=L)
+            if layer == 0:
+                return out
+            head_map = None
+        else:
+            if self._tile_idx is None:
+                raise RuntimeError("reuse layer called before any anchor layer")
+            head_map = self._mapping(layer, dev)
+        nat.prefill_sparse(q, k, v, self._tile_idx, self._tile_count, head_map, scaling, out)
+        return out
+
+    # -- decode ------------------------------------------------------------------------------------
+    def _decode_budgets(self, seq_lens: torch.Tensor, max_len: int):
+        """Per-sequence key budgets on the device (no sync): the reference formula for a cache of
+        seq_lens[b] keys; sequences of at most 128 keys attend to everything."""
+        lens = seq_lens.to(torch.float64)
+        kk = torch.clamp(torch.floor((self.k / 100) * lens), min=128.0)
+        kk = torch.minimum(kk, lens) - self.tile_size
+        kk = torch.where(lens <= 128, lens, kk).to(torch.int32)
+        kmax = max_len if max_len <= 128 else topk_budget(self.k, max_len, self.tile_size)
+        return kk, max(kmax, 1)
+
+    def _decode(self, layer: int, q, kv, seq_lens, max_len: int, scaling, G: int, dense_only=False) -> torch.Tensor:
+        B, H, D = q.shape
+        dev = q.device
+        if q.stride(2) != 1 or q.stride(0) % 2 or q.stride(1) % 2:
+            q = q.contiguous()
+        out = torch.empty(B, H, D, dtype=torch.float16, device=dev)
+        splits_a = nat.decode_default_splits(B, G, max_len)
+        if dense_only or self.is_anchor(layer):
+            stride = -(-max_len // 4) * 4
+            logits = self._scratch("dec_logits", (B, H, stride), torch.float32, dev)
+            pooled = self._scratch("dec_pooled", (B, G, stride), torch.float32, dev)
+            lse2 = self._scratch("dec_lse2", (B, H), torch.float32, dev)
+            ws = self._scratch("dec_ws", (nat.load().kb200_decode_workspace_bytes(B, H, splits_a),), torch.uint8, dev)
+            want_out = dense_only or layer == 0
+            nat.decode_anchor_paged(q, kv, seq_lens, max_len, scaling, logits, pooled, out if want_out else None,
+                                    lse2, ws, splits_a)
+            if dense_only:
+                return out
+            k_row, kmax = self._decode_budgets(seq_lens, max_len)
+            self._dec_kmax = kmax
+            self._dec_idx = self._scratch("dec_idx", (B, G, kmax), torch.int32, dev)
+            self._dec_count = self._scratch("dec_count", (B, G), torch.int32, dev)
+            n_valid = seq_lens.view(B, 1).expand(B, G).contiguous()
+            k_rows = k_row.view(B, 1).expand(B, G).contiguous()
+            nat.topk_select(pooled, n_valid, k_rows, kmax, self._dec_idx, self._dec_count, n_cols=max_len)
+            if layer == 0:
+                return out
+            head_map = None
+        else:
+            if self._dec_idx is None:
+                raise RuntimeError("reuse layer called before any anchor layer")
+            head_map = self._mapping(layer, dev)
+        kmax = self._dec_kmax
+        splits = nat.decode_default_splits(B, G, kmax)
+        ws = self._scratch("dec_ws_s", (nat.load().kb200_decode_workspace_bytes(B, H, splits),), torch.uint8, dev)
+        nat.decode_sparse_paged(q, kv, self._dec_idx, self._dec_count, kmax, head_map, scaling, out, None, ws, splits)
+        return out
+
+    def paged_decode_forward(self, layer_idx: int, query, key_cache, value_cache, block_table, seq_lens, scaling,
+                             max_seq_len: Optional[int] = None) -> torch.Tensor:
+        """Paged-attention backend entry: query [B,H,D] fp16, key/value cache
+        [num_pages, page_size, G, D] fp16, block_table [B, max_pages] int32, seq_lens [B] int32
+        -> out [B,H,D] fp16.  The reference has no paged kernel (README.md:135); the nearest
+        signature is kernels/flash_decoding/reuse_kascade_gqa_decode_with_kvcache.py:160-171."""
+        if max_seq_len is None:
+            max_seq_len = int(seq_lens.max().item())
+        kv = nat.kv_layout_paged(key_cache, value_cache, block_table)
+        return self._decode(int(layer_idx), query, kv, seq_lens, int(max_seq_len), scaling, key_cache.shape[2])
