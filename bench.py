@@ -1,0 +1,445 @@
+#!/usr/bin/env python
+"""Benchmark of the Kascade sparse-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (N = 1): the Llama-3.1-8B-shaped prefill attention stack at 32 768 tokens —
+32 layers, anchors {0,2,8,13,14}, batch 1, 32 query / 8 KV heads, head_dim 128, fp16, tile 32,
+Top-k 10 %, rolling prefill, seeded synthetic Q/K/V with heavy-hitter keys.  One "step" is one
+pass of all 32 attention layers through ``EfficientKascadeStrategy.attention_forward``.
+The same JSON line also carries the paged sparse-decode configuration (batch 64, context 32 768,
+16-token pages) under "decode", dense attention on the same GPU under "dense", the roofline of the
+dominant kernel and the CPU baseline (the oracle port on the host cores).
+
+With N > 1 (launched by torch.distributed.run) the KV heads of every layer are sharded over the
+ranks (strong scaling); the anchors' index rows are all-gathered over NCCL because a reuse head may
+map to an anchor head of another shard, per-head outputs are all-gathered at the end of each layer.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode attn µs/step & prefill attn ms @32k, 10% top-k, vs dense on B200"
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops_sustained"], "tflops_burst": p["bf16_tflops"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "tflops_burst": 1590.0, "source": "fallback"}
+
+
+class _Module:
+    def __init__(self, layer_idx, groups=4):
+        self.layer_idx = layer_idx
+        self.num_key_value_groups = groups
+        self.training = False
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def _time_cuda(fn, reps: int):
+    """Mean milliseconds of fn() over reps back-to-back calls, CUDA events on the current stream."""
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    s.record()
+    for i in range(reps):
+        fn(i)
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / reps
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the oracle port (oracle/kascade_oracle.py) on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_prefill_sample(seq_len: int):
+    """Times one anchor-0, one reuse and one anchor>0 layer of the oracle at `seq_len`, fp32, and
+    extrapolates the 32-layer stack at 32 768 tokens by the L^2 work ratio."""
+    from oracle.kascade_oracle import KascadeOracle
+    from kascade_b200.workloads import PrefillWorkload
+    wl = PrefillWorkload(seq_len=seq_len, layers=3, anchors=(0, 2))
+    orc = KascadeOracle(recompute_layers=(0, 2), head_mapping=wl.head_mapping(), k=10, tile_size=32,
+                        rolling_prefill=True, row_block=512)
+    times = []
+    for layer in range(3):
+        q, k, v = wl.layer_inputs(layer, "cpu")
+        q, k, v = (x.float().transpose(1, 2).contiguous() for x in (q, k, v))
+        t0 = time.perf_counter()
+        orc.attention_forward(layer, q, k, v, 128 ** -0.5)
+        times.append(time.perf_counter() - t0)
+    scale = (32768 / seq_len) ** 2
+    stack_ms = (times[0] + 4 * times[2] + 27 * times[1]) * scale * 1e3
+    return stack_ms, times
+
+
+def run_reference(args, rank):
+    """--impl reference: the reference's CPU implementation of the path (the oracle port — the Python
+    reference itself cannot travel to the GPU box) on all host threads, same metric and unit."""
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    L = 2048
+    for _ in range(args.warmup):
+        cpu_prefill_sample(L)
+    t0 = time.perf_counter()
+    vals = [cpu_prefill_sample(L)[0] for _ in range(args.steps)]
+    wall = (time.perf_counter() - t0) / max(args.steps, 1)
+    value = sum(vals) / len(vals)
+    sample = (f"oracle port, fp32, {cores} threads: 3 layers (anchor 0, reuse, anchor>0) at L={L}, stack of 32 layers "
+              f"at 32768 extrapolated by (32768/{L})^2 and 1/27/4 layer weights")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "ms", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall * 1e3, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "llama31_8b_prefill_attention_stack_32k", "layers": 32, "seq_len": 32768,
+                       "topk_pct": 10, "tile": 32, "rolling": True},
+            "cpu_baseline": {"value": value, "unit": "ms", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seq-len", type=int, default=32768, help="prefill length (default: the benchmark's 32768)")
+    ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-dense", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+    from kascade_b200 import EfficientKascadeStrategy, _native as nat
+    from kascade_b200.workloads import DecodeWorkload, PrefillWorkload
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = _peaks()
+
+    # ---------------- prefill stack (headline) -----------------------------------------------------
+    wl = PrefillWorkload(seq_len=args.seq_len)
+    assert wl.G % world == 0, "KV heads must divide over the ranks"
+    gpr = wl.G // world
+    my_heads = list(range(rank * gpr, (rank + 1) * gpr))
+    strat = EfficientKascadeStrategy(list(wl.anchors), "synthetic/llama31-8b-shape", k=wl.pct, tile_size=wl.tile,
+                                     rolling_prefill=wl.rolling, head_mapping=wl.head_mapping(), register=False,
+                                     shard=(rank, world) if world > 1 else None)
+    inputs = [wl.layer_inputs(l, dev, my_heads if world > 1 else None) for l in range(wl.layers)]
+    scaling = wl.D ** -0.5
+    mods = [_Module(l) for l in range(wl.layers)]
+    result = {}
+
+    def step(_i=0):
+        out = None
+        for l in range(wl.layers):
+            q, k, v = inputs[l]
+            out, _ = strat.attention_forward(mods[l], q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), None, scaling)
+        if world > 1:
+            strat.wait_gathers()
+        result["out"] = out
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    n0 = nat.launch_count
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(args.steps):
+        step()
+    e.record()
+    torch.cuda.synchronize()
+    launches = (nat.launch_count - n0) // max(args.steps, 1)
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop()
+    ms = torch.tensor([s.elapsed_time(e) / args.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = float(ms.item())
+    status = nat.read_status()
+
+    # ---------------- per-kernel timing and the roofline of the dominant kernel ------------------
+    kernels = {}
+    roof = None
+    if world == 1:
+        B, L, H, G, D = wl.B, wl.seq_len, wl.H, wl.G, wl.D
+        T = -(-L // 32)
+        out = torch.empty(B, L, H, D, dtype=torch.float16, device=dev)
+        lse = torch.empty(B, L, H, dtype=torch.float32, device=dev)
+        pooled = strat._buf["pooled"][: B * G * T * (-(-L // 128) * 128)].view(B, G, T, -1)
+        nl = len(inputs)
+        reps = 4
+        kernels["prefill_dense_attn"] = (_time_cuda(lambda i: nat.prefill_dense(*inputs[i % nl], scaling, out, lse), reps),
+                                         wl.flops_dense(), 1)
+        kernels["prefill_dense_lse"] = (_time_cuda(lambda i: nat.prefill_dense(inputs[i % nl][0], inputs[i % nl][1], None,
+                                                                               scaling, None, lse), reps),
+                                        wl.flops_qk_causal(), 4)
+        kernels["prefill_pool_scores"] = (_time_cuda(lambda i: nat.prefill_pool_scores(inputs[i % nl][0], inputs[i % nl][1],
+                                                                                       lse, scaling, pooled), reps),
+                                          wl.flops_qk_causal(), 5)
+        nv, kr = strat._buf["n_valid"][: B * G * T].view(B, G, T), strat._buf["k_row"][: B * G * T].view(B, G, T)
+        kk = strat._tile_idx.shape[-1]
+        kernels["topk_select"] = (_time_cuda(lambda i: nat.topk_select(pooled, nv, kr, kk, strat._tile_idx,
+                                                                       strat._tile_count, n_cols=L), reps), 0.0, 5)
+        kernels["prefill_sparse"] = (_time_cuda(lambda i: nat.prefill_sparse(*inputs[i % nl], strat._tile_idx,
+                                                                             strat._tile_count, None, scaling, out), reps),
+                                     wl.flops_sparse(), 31)
+        share = {k: v[0] * v[2] for k, v in kernels.items()}
+        top = max(share, key=share.get)
+        t_ms, flops, _n = kernels[top]
+        achieved = flops / (t_ms * 1e-3) / 1e12
+        roof = {"kernel": "tile_prefill_kernel<%s>" % top, "bound": "tensor", "achieved": achieved,
+                "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"], "traffic": None,
+                "peak_source": peaks["source"] + " (sustained bf16 GEMM)",
+                "per_kernel_ms": {k: round(v[0], 4) for k, v in kernels.items()},
+                "per_kernel_tflops": {k: round(v[1] / (v[0] * 1e-3) / 1e12, 1) for k, v in kernels.items() if v[1]},
+                "launches_per_step": {k: v[2] for k, v in kernels.items()}}
+
+    # ---------------- end to end through the plugin call with host buffers ------------------------
+    e2e = None
+    if not args.skip_e2e:
+        n_host = min(4, wl.layers)
+        host = [tuple(x.cpu().pin_memory() for x in inputs[l]) for l in range(n_host)]
+        host_out = torch.empty(inputs[0][0].shape, dtype=torch.float16).pin_memory()
+        dq, dk, dv = (torch.empty_like(x) for x in inputs[0])
+        h2d = sum(x.numel() * 2 for x in inputs[0]) * wl.layers
+        d2h = host_out.numel() * 2 * wl.layers
+
+        def e2e_step(_i=0):
+            for l in range(wl.layers):
+                hq, hk, hv = host[l % n_host]
+                dq.copy_(hq, non_blocking=True)
+                dk.copy_(hk, non_blocking=True)
+                dv.copy_(hv, non_blocking=True)
+                o, _ = strat.attention_forward(mods[l], dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2), None, scaling)
+                host_out.copy_(o, non_blocking=True)
+
+        e2e_step()
+        if world > 1:
+            dist.barrier()
+        t = torch.tensor([_time_cuda(e2e_step, max(1, min(args.steps, 2)))], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e = {"value": float(t.item()), "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "note": f"{n_host} distinct pinned host layers cycled over {wl.layers} layers; copies serialised with compute"}
+        del host, host_out, dq, dk, dv
+
+    # ---------------- dense attention on the same GPU ----------------------------------------------
+    dense = None
+    if world == 1 and not args.skip_dense:
+        out = torch.empty(wl.B, wl.seq_len, wl.H, wl.D, dtype=torch.float16, device=dev)
+        t_own = _time_cuda(lambda i: nat.prefill_dense(*inputs[i % len(inputs)], scaling, out, None), 3)
+        dense = {"own_kernel_ms_per_layer": t_own, "own_kernel_ms_stack": t_own * wl.layers,
+                 "own_tflops": wl.flops_dense() / (t_own * 1e-3) / 1e12}
+        try:
+            import torch.nn.functional as F
+
+            def sdpa(i):
+                q, k, v = inputs[i % len(inputs)]
+                F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
+                                               enable_gqa=True)
+            sdpa(0)
+            t_lib = _time_cuda(sdpa, 3)
+            dense.update({"torch_sdpa_ms_per_layer": t_lib, "torch_sdpa_ms_stack": t_lib * wl.layers})
+        except Exception as ex:                                      # library comparator only
+            dense["torch_sdpa_error"] = str(ex)[:120]
+        dense["speedup_vs_own_dense"] = dense["own_kernel_ms_stack"] / ms_step
+    del inputs
+    strat._buf.clear()
+    torch.cuda.empty_cache()
+
+    # ---------------- paged sparse decode (batch 64, context 32768) -------------------------------
+    decode = None
+    if not args.skip_decode:
+        dw = DecodeWorkload()
+        assert dw.batch % world == 0
+        dw.batch //= world                                            # batch-sharded across ranks
+        dstrat = EfficientKascadeStrategy(list(dw.anchors), "synthetic/llama31-8b-shape", k=dw.pct, tile_size=32,
+                                          rolling_prefill=True, head_mapping=dw.head_mapping(), register=False)
+        caches = [dw.make_cache(i, dev) for i in range(dw.distinct_caches)]
+        qs = [dw.query(l, dev) for l in range(dw.layers)]
+        seq_lens = torch.full((dw.batch,), dw.context, dtype=torch.int32, device=dev)
+        dout = {}
+
+        def dstep(_i=0):
+            for l in range(dw.layers):
+                kc, vc, bt = caches[l % len(caches)]
+                dout["o"] = dstrat.paged_decode_forward(l, qs[l], kc, vc, bt, seq_lens, scaling, dw.context)
+
+        for _ in range(args.warmup):
+            dstep()
+        if world > 1:
+            dist.barrier()
+        n0 = nat.launch_count
+        t = torch.tensor([_time_cuda(dstep, args.steps)], device=dev)
+        dl = (nat.launch_count - n0) // max(args.steps, 1)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us_step = float(t.item()) * 1e3
+        # reuse-layer kernel alone (the dominant decode kernel by launches: 27 of 32 layers)
+        kc, vc, bt = caches[0]
+        kv = nat.kv_layout_paged(kc, vc, bt)
+        o = torch.empty(dw.batch, dw.H, dw.D, dtype=torch.float16, device=dev)
+        kmax = dstrat._dec_kmax
+        splits = nat.decode_default_splits(dw.batch, dw.G, kmax)
+        ws = nat.decode_workspace(dw.batch, dw.H, splits, dev)
+
+        def reuse(i):
+            kc, vc, bt = caches[i % len(caches)]
+            nat.decode_sparse_paged(qs[i % len(qs)], nat.kv_layout_paged(kc, vc, bt), dstrat._dec_idx, dstrat._dec_count,
+                                    kmax, None, scaling, o, None, ws, splits)
+        reuse(0)
+        t_reuse = _time_cuda(reuse, 20) * 1e3
+        # dense decode of all layers with the library's own dense pass, for the "vs dense" figure
+        stride = -(-dw.context // 4) * 4
+        logits = torch.empty(dw.batch, dw.H, stride, dtype=torch.float32, device=dev)
+        pooled = torch.empty(dw.batch, dw.G, stride, dtype=torch.float32, device=dev)
+        lse2 = torch.empty(dw.batch, dw.H, dtype=torch.float32, device=dev)
+        sa = nat.decode_default_splits(dw.batch, dw.G, dw.context)
+        wsa = nat.decode_workspace(dw.batch, dw.H, sa, dev)
+
+        def dense_dec(i):
+            kc, vc, bt = caches[i % len(caches)]
+            nat.decode_anchor_paged(qs[i % len(qs)], nat.kv_layout_paged(kc, vc, bt), seq_lens, dw.context, scaling, logits,
+                                    pooled, o, lse2, wsa, sa)
+        dense_dec(0)
+        t_dense = _time_cuda(dense_dec, 8) * 1e3
+        gbs_reuse = dw.bytes_reuse() / (t_reuse * 1e-6) / 1e9
+        decode = {"us_per_step": us_step, "layers": dw.layers, "batch_per_gpu": dw.batch, "context": dw.context,
+                  "page": dw.page, "topk": dw.budget(), "distinct_layer_caches": dw.distinct_caches,
+                  "gpu_launches": dl,
+                  "algorithmic_gb_per_step": dw.bytes_step() / 1e9,
+                  "achieved_gbs_step": dw.bytes_step() / (us_step * 1e-6) / 1e9,
+                  "frac_step": dw.bytes_step() / (us_step * 1e-6) / 1e9 / peaks["hbm_gbs"],
+                  "reuse_layer_us": t_reuse,
+                  "roofline": {"kernel": "decode_attn_kernel<sparse>", "bound": "hbm", "achieved": gbs_reuse,
+                               "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs_reuse / peaks["hbm_gbs"],
+                               "traffic": None, "peak_source": peaks["source"]},
+                  "dense_layer_us": t_dense, "dense_us_per_step": t_dense * dw.layers,
+                  "dense_layer_gbs": 2 * dw.bytes_dense_k() / (t_dense * 1e-6) / 1e9,
+                  "speedup_vs_dense": t_dense * dw.layers / us_step}
+        del caches, logits, pooled
+        torch.cuda.empty_cache()
+    status |= nat.read_status()
+
+    # ---------------- CPU baseline (rank 0, N = 1) --------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        L = 4096
+        stack_ms, times = cpu_prefill_sample(L)
+        cpu = {"value": stack_ms, "unit": "ms", "cores": torch.get_num_threads(), "kind": "port",
+               "sample": (f"oracle port fp32: anchor-0 {times[0]:.1f}s, reuse {times[1]:.1f}s, anchor>0 {times[2]:.1f}s at "
+                          f"L={L}; 32-layer stack at 32768 extrapolated by (32768/{L})^2 with 1/27/4 layer weights")}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": {"workload": "llama31_8b_prefill_attention_stack_32k" if args.seq_len == 32768
+                           else f"llama31_8b_prefill_attention_stack_{args.seq_len}",
+                           "layers": wl.layers, "anchors": list(wl.anchors), "seq_len": wl.seq_len, "batch": wl.B,
+                           "q_heads": wl.H, "kv_heads": wl.G, "head_dim": wl.D, "topk_pct": wl.pct, "tile": wl.tile,
+                           "rolling": wl.rolling, "parallelism": f"kv-head shard x{world}",
+                           "cache_policy": "inputs larger than L2 (402 MB per layer, 32 distinct layers)"},
+                "algorithmic_tflop_per_step": wl.flops_stack() / 1e12,
+                "achieved_tflops": wl.flops_stack() / (ms_step * 1e-3) / 1e12,
+                "gpu_launches": launches, "device_status": status, "clocks": clocks}
+        if roof:
+            line["roofline"] = roof
+        if cpu:
+            line["cpu_baseline"] = cpu
+        if e2e:
+            line["e2e"] = e2e
+        if dense:
+            line["dense"] = dense
+        if decode:
+            line["decode"] = decode
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

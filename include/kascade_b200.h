@@ -166,9 +166,12 @@ int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_act_layout*
 /* Sparse tile attention of a reuse layer (or of an anchor layer > 0 over its own fresh rows):
  * query i of tile t attends to the keys tile_idx[b, head_map[g], t, 0:tile_count[…]] (all
  * strictly before the tile) and to the keys 32*t .. i of its own tile.
- *   tile_idx    [B, G, T, idx_stride] int32, ascending or any order, no duplicates
- *   tile_count  [B, G, T] int32
- *   head_map    [G] int32 or NULL (identity)
+ *   tile_idx    [B, Gi, T, idx_stride] int32, ascending or any order, no duplicates
+ *   tile_count  [B, Gi, T] int32
+ *   idx_kv_heads  Gi, the number of KV heads the index tensors hold (0: num_kv_heads).  When the
+ *               KV heads of a layer are sharded over GPUs, a call covers num_kv_heads local heads
+ *               while the index tensors hold the rows of all Gi heads of the anchor layer.
+ *   head_map    [num_kv_heads] int32 with values in [0, Gi), or NULL (identity, needs Gi == num_kv_heads)
  *   out         [B, L, H, D] fp16 contiguous;  lse2 [B, L, H] fp32 or NULL
  * (K4 `main_kernel`: reuse_kascade_gqa_prefill.py:146-198 and the two
  *  dynamic_alllen_reuse_cp_async_ts32_dim128_gsize4_heads32_groups8[_rolling].cu) */
@@ -176,7 +179,7 @@ int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_layout* k,
                          const kb200_act_layout* v, const int32_t* tile_idx, int64_t idx_stride,
                          const int32_t* tile_count, const int32_t* head_map, float softmax_scale,
                          void* out, float* lse2, int batch, int seq_len, int num_q_heads,
-                         int num_kv_heads, void* stream);
+                         int num_kv_heads, int idx_kv_heads, void* stream);
 
 /* Per-tile budgets of an anchor prefill layer, written on the device for kb200_topk_select:
  *   n_valid[b,g,t] = 32*t,

@@ -44,6 +44,12 @@ class ActLayout(C.Structure):
 
 _lib = None
 _inited = set()
+launch_count = 0          # kernels of this library launched so far by this process (host-side tally)
+
+
+def _launched(n: int):
+    global launch_count
+    launch_count += n
 
 
 def load() -> C.CDLL:
@@ -72,7 +78,7 @@ def load() -> C.CDLL:
         lib.kb200_prefill_dense.argtypes = [AL, AL, AL, f32, vp, vp, i32, i32, i32, i32, vp]
         lib.kb200_prefill_pool_scores.argtypes = [AL, AL, vp, f32, vp, i64, i32, i32, i32, i32, vp]
         lib.kb200_prefill_sparse.argtypes = [AL, AL, AL, vp, i64, vp, vp, f32, vp, vp, i32, i32, i32,
-                                             i32, vp]
+                                             i32, i32, vp]
         lib.kb200_prefill_budgets.argtypes = [vp, vp, i32, i32, i32, i32, f32, i32, vp]
         lib.kb200_selftest_umma.argtypes = [vp, vp, vp, vp, vp]
         _lib = lib
@@ -127,12 +133,14 @@ def topk_select(scores: torch.Tensor, n_valid: Optional[torch.Tensor], k_row: Op
     _check(lib.kb200_topk_select(_ptr(scores), scores.shape[-1], scores.shape[-1] if n_cols is None else n_cols,
                                  _ptr(n_valid), _ptr(k_row), k_max, _ptr(out_idx), out_idx.shape[-1],
                                  _ptr(out_count), rows, _stream()), "kb200_topk_select")
+    _launched(1 if rows else 0)
 
 
 def prefill_budgets(n_valid, k_row, batch, groups, tiles, k_max, pct, rolling):
     lib = init(n_valid.device.index)
     _check(lib.kb200_prefill_budgets(_ptr(n_valid), _ptr(k_row), batch, groups, tiles, k_max, float(pct),
                                      int(bool(rolling)), _stream()), "kb200_prefill_budgets")
+    _launched(1)
 
 
 def kv_layout_paged(k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], block_table: torch.Tensor) -> KvLayout:
@@ -182,6 +190,8 @@ def decode_sparse_paged(q, kv: KvLayout, topk_idx, topk_count, k_max, head_map, 
         _ptr(topk_count), k_max, _ptr(head_map), float(scale), _ptr(out), _ptr(lse2), _ptr(workspace),
         0 if workspace is None else workspace.numel() * workspace.element_size(), B, H, G, num_splits, _stream()),
         "kb200_decode_sparse_paged")
+    ns = num_splits if num_splits else lib.kb200_decode_default_splits(B, G, k_max)
+    _launched(1 + (ns > 1))
 
 
 def decode_anchor_paged(q, kv: KvLayout, seq_lens, max_seq_len, scale, logits, pooled, out, lse2,
@@ -199,6 +209,8 @@ def decode_anchor_paged(q, kv: KvLayout, seq_lens, max_seq_len, scale, logits, p
         _ptr(pooled), logits.shape[-1], _ptr(out), _ptr(lse2), _ptr(workspace),
         0 if workspace is None else workspace.numel() * workspace.element_size(), B, H, G, num_splits, _stream()),
         "kb200_decode_anchor_paged")
+    ns = num_splits if num_splits else lib.kb200_decode_default_splits(B, G, max_seq_len)
+    _launched(2 + (ns > 1))
 
 
 def act_layout(x: torch.Tensor) -> ActLayout:
@@ -220,6 +232,7 @@ def prefill_dense(q, k, v, scale, out, lse2):
         assert out.is_contiguous()
     _check(lib.kb200_prefill_dense(C.byref(ql), C.byref(kl), C.byref(vl), float(scale), _ptr(out), _ptr(lse2),
                                    B, L, H, G, _stream()), "kb200_prefill_dense")
+    _launched(1)
 
 
 def prefill_pool_scores(q, k, lse2, scale, pooled):
@@ -233,6 +246,7 @@ def prefill_pool_scores(q, k, lse2, scale, pooled):
     assert pooled.is_contiguous() and lse2.is_contiguous()
     _check(lib.kb200_prefill_pool_scores(C.byref(ql), C.byref(kl), _ptr(lse2), float(scale), _ptr(pooled),
                                          pooled.shape[-1], B, L, H, G, _stream()), "kb200_prefill_pool_scores")
+    _launched(1)
 
 
 def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=None):
@@ -247,7 +261,8 @@ def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=Non
     assert tile_idx.is_contiguous() and tile_count.is_contiguous() and out.is_contiguous()
     _check(lib.kb200_prefill_sparse(C.byref(ql), C.byref(kl), C.byref(vl), _ptr(tile_idx), tile_idx.shape[-1],
                                     _ptr(tile_count), _ptr(head_map), float(scale), _ptr(out), _ptr(lse2), B, L, H,
-                                    G, _stream()), "kb200_prefill_sparse")
+                                    G, tile_idx.shape[1], _stream()), "kb200_prefill_sparse")
+    _launched(1)
 
 
 def selftest_umma(a: torch.Tensor, b: torch.Tensor):

@@ -48,6 +48,7 @@ struct PrefillParams {
   const float* lse2_in;
   float* pooled; int64_t pooled_stride;
   int B, L, H, G, T;
+  int G_idx;                      // KV heads in the index tensors (>= G when heads are sharded)
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
   const int32_t* idx_row = nullptr;
   if (GATHER) {
     const int src_g = p.head_map ? p.head_map[g] : g;
-    const int64_t r = ((int64_t)b * p.G + src_g) * p.T + t;
+    const int64_t r = ((int64_t)b * p.G_idx + src_g) * p.T + t;
     count = p.tile_count[r];
     count = max(0, min(count, (int)min((int64_t)tile_start, p.idx_stride)));
     idx_row = p.tile_idx + r * p.idx_stride;
@@ -485,11 +486,13 @@ extern "C" int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_l
                                     const kb200_act_layout* v, const int32_t* tile_idx, int64_t idx_stride,
                                     const int32_t* tile_count, const int32_t* head_map, float softmax_scale,
                                     void* out, float* lse2, int batch, int seq_len, int num_q_heads,
-                                    int num_kv_heads, void* stream) {
+                                    int num_kv_heads, int idx_kv_heads, void* stream) {
   using namespace kb200;
   if (check_shape(batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
   KB_REQUIRE(tile_idx && tile_count && out, "prefill_sparse: null pointer");
   KB_REQUIRE(idx_stride >= 0, "prefill_sparse: negative idx_stride");
+  KB_REQUIRE(idx_kv_heads == 0 || head_map || idx_kv_heads == num_kv_heads,
+             "prefill_sparse: idx_kv_heads differs from num_kv_heads, so a head_map is required");
   KB_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15) == 0, "prefill_sparse: out must be 16-byte aligned");
   if (batch == 0 || seq_len == 0) return 0;
   PrefillParams p{};
@@ -497,6 +500,7 @@ extern "C" int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_l
   if (fill_act(k, &p.k, &p.k_sb, &p.k_st, &p.k_sh, "k") != 0) return -1;
   if (fill_act(v, &p.v, &p.v_sb, &p.v_st, &p.v_sh, "v") != 0) return -1;
   p.tile_idx = tile_idx;
+  p.G_idx = idx_kv_heads > 0 ? idx_kv_heads : num_kv_heads;
   p.idx_stride = idx_stride;
   p.tile_count = tile_count;
   p.head_map = head_map;

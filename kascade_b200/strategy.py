@@ -26,7 +26,41 @@ import torch
 
 from . import _native as nat
 
-__all__ = ["Strategy", "EfficientKascadeStrategy", "topk_budget"]
+__all__ = ["Strategy", "EfficientKascadeStrategy", "topk_budget", "shard_kv_heads", "shard_head_map",
+           "gather_index_rows"]
+
+
+def shard_kv_heads(num_kv_heads: int, rank: int, world: int) -> List[int]:
+    """KV heads owned by `rank` when a layer's heads are split evenly over `world` GPUs."""
+    if num_kv_heads % world:
+        raise ValueError(f"{num_kv_heads} KV heads do not divide over {world} ranks")
+    per = num_kv_heads // world
+    return list(range(rank * per, (rank + 1) * per))
+
+
+def shard_head_map(mapping_row: Sequence[int], rank: int, world: int) -> List[int]:
+    """The head-mapping entries of the local KV heads.  Values stay GLOBAL anchor-head ids: a reuse
+    head may map to an anchor head that another rank computed, which is why the anchors' index rows
+    are all-gathered (`gather_index_rows`)."""
+    return [int(mapping_row[g]) for g in shard_kv_heads(len(mapping_row), rank, world)]
+
+
+def gather_index_rows(local_idx: torch.Tensor, local_count: torch.Tensor, group=None):
+    """All-gather the anchor index rows of every rank's KV heads.
+
+    local_idx [1, Gl, T, k], local_count [1, Gl, T]  ->  ([1, G, T, k], [1, G, T]) with heads in rank
+    order (batch 1: the gathered buffers are then exactly the [B, G, T, k] layout the kernels index).
+    Works on NCCL (GPU) and gloo (CPU tests)."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    if local_idx.shape[0] != 1:
+        raise NotImplementedError("head-sharded prefill supports batch 1")
+    _, gl, T, k = local_idx.shape
+    idx = torch.empty((1, world * gl, T, k), dtype=local_idx.dtype, device=local_idx.device)
+    cnt = torch.empty((1, world * gl, T), dtype=local_count.dtype, device=local_count.device)
+    dist.all_gather_into_tensor(idx.view(world, -1), local_idx.reshape(1, -1).contiguous(), group=group)
+    dist.all_gather_into_tensor(cnt.view(world, -1), local_count.reshape(1, -1).contiguous(), group=group)
+    return idx, cnt
 
 
 def topk_budget(pct: float, lk: int, tile_size: int) -> int:
@@ -56,11 +90,14 @@ class EfficientKascadeStrategy(Strategy):
 
     Extra keyword arguments (not in the reference) are keyword-only: ``head_mapping`` passes the
     ``[num_layers][G]`` table directly instead of reading the ``.npy`` file, ``register`` skips the
-    HF registration (for use without transformers)."""
+    HF registration (for use without transformers), ``shard=(rank, world)`` makes this instance
+    compute only its slice of the KV heads of every prefill layer (batch 1): the caller passes the
+    local heads' q/k/v, anchor index rows are all-gathered over torch.distributed, and the per-head
+    outputs of every layer are all-gathered into ``self.gathered_out`` ([world, B, L, H/world, D])."""
 
     def __init__(self, recompute_layers: List[int], model_name: str, k=1, tile_size=1, rolling_prefill=False,
                  block_size=12288, *, head_mapping: Optional[Sequence[Sequence[int]]] = None,
-                 register: bool = True):
+                 register: bool = True, shard: Optional[tuple] = None):
         if recompute_layers is None:
             raise ValueError("recompute_layers cannot be None for EfficientKascadeStrategy")
         if not (0 <= k <= 100):
@@ -77,6 +114,9 @@ class EfficientKascadeStrategy(Strategy):
         self._head_mapping = [list(map(int, r)) for r in head_mapping] if head_mapping is not None \
             else self.get_head_mapping(model_name)
         self._register = register
+        self._shard = tuple(shard) if shard is not None else None
+        self.gathered_out: Optional[torch.Tensor] = None
+        self._pending = []
         # cross-layer state written by anchor layers (strategies/KascadeStrategy.py:95,133)
         self._tile_idx: Optional[torch.Tensor] = None       # prefill [B,G,T,k]
         self._tile_count: Optional[torch.Tensor] = None     # prefill [B,G,T]
@@ -127,7 +167,10 @@ class EfficientKascadeStrategy(Strategy):
         key = (layer_idx, device)
         m = self._map_dev.get(key)
         if m is None:
-            m = torch.tensor(self._head_mapping[layer_idx], dtype=torch.int32, device=device)
+            row = self._head_mapping[layer_idx]
+            if self._shard is not None:
+                row = shard_head_map(row, *self._shard)
+            m = torch.tensor(row, dtype=torch.int32, device=device)
             self._map_dev[key] = m
         return m
 
@@ -192,15 +235,37 @@ class EfficientKascadeStrategy(Strategy):
             self._tile_idx = self._scratch("tile_idx", (B, G, T, max(kk, 1)), torch.int32, dev)
             self._tile_count = self._scratch("tile_count", (B, G, T), torch.int32, dev)
             nat.topk_select(pooled, n_valid, k_row, kk, self._tile_idx, self._tile_count, n_cols=L)
+            if self._shard is not None:
+                self._tile_idx, self._tile_count = gather_index_rows(self._tile_idx, self._tile_count)
             if layer == 0:
-                return out
-            head_map = None
+                return self._publish(out)
+            head_map = self._mapping(layer, dev) if self._shard is not None else None
         else:
             if self._tile_idx is None:
                 raise RuntimeError("reuse layer called before any anchor layer")
             head_map = self._mapping(layer, dev)
         nat.prefill_sparse(q, k, v, self._tile_idx, self._tile_count, head_map, scaling, out)
+        return self._publish(out)
+
+    def _publish(self, out: torch.Tensor) -> torch.Tensor:
+        """Head-sharded runs: start the all-gather of this layer's per-head outputs (asynchronous, on
+        the communicator's stream) and return the local slice."""
+        if self._shard is None:
+            return out
+        import torch.distributed as dist
+        world = self._shard[1]
+        self._pending = [w for w in self._pending if not w[0].is_completed()]
+        buf = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=out.device)
+        work = dist.all_gather_into_tensor(buf.view(world, -1), out.view(1, -1), async_op=True)
+        self._pending.append((work, buf, out))
+        self.gathered_out = buf
         return out
+
+    def wait_gathers(self):
+        """Block the current stream until every output all-gather started so far has finished."""
+        for work, _, _ in self._pending:
+            work.wait()
+        self._pending = []
 
     # -- decode ------------------------------------------------------------------------------------
     def _decode_budgets(self, seq_lens: torch.Tensor, max_len: int):
