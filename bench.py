@@ -161,6 +161,85 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def bench_decode(args, dev, world, peaks, batch=None):
+    """Paged sparse decode, Llama-3.1-8B shape: batch 64 (split over the ranks), every sequence at context
+    32 768, 16-token pages behind a seeded random block table, 32 layers with anchors {0,2,8,13,14}."""
+    import torch.distributed as dist
+    from kascade_b200 import EfficientKascadeStrategy, _native as nat
+    from kascade_b200.workloads import DecodeWorkload
+    scaling = 128 ** -0.5
+    dw = DecodeWorkload() if batch is None else DecodeWorkload(batch=batch)
+    assert dw.batch % world == 0
+    dw.batch //= world                                            # batch-sharded across ranks
+    dstrat = EfficientKascadeStrategy(list(dw.anchors), "synthetic/llama31-8b-shape", k=dw.pct, tile_size=32,
+                                      rolling_prefill=True, head_mapping=dw.head_mapping(), register=False)
+    caches = [dw.make_cache(i, dev) for i in range(dw.distinct_caches)]
+    qs = [dw.query(l, dev) for l in range(dw.layers)]
+    seq_lens = torch.full((dw.batch,), dw.context, dtype=torch.int32, device=dev)
+    dout = {}
+
+    def dstep(_i=0):
+        for l in range(dw.layers):
+            kc, vc, bt = caches[l % len(caches)]
+            dout["o"] = dstrat.paged_decode_forward(l, qs[l], kc, vc, bt, seq_lens, scaling, dw.context)
+
+    for _ in range(args.warmup):
+        dstep()
+    if world > 1:
+        dist.barrier()
+    n0 = nat.launch_count
+    t = torch.tensor([_time_cuda(dstep, args.steps)], device=dev)
+    dl = (nat.launch_count - n0) // max(args.steps, 1)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us_step = float(t.item()) * 1e3
+    # reuse-layer kernel alone (the dominant decode kernel by launches: 27 of 32 layers)
+    kc, vc, bt = caches[0]
+    kv = nat.kv_layout_paged(kc, vc, bt)
+    o = torch.empty(dw.batch, dw.H, dw.D, dtype=torch.float16, device=dev)
+    kmax = dstrat._dec_kmax
+    splits = nat.decode_default_splits(dw.batch, dw.G, kmax)
+    ws = nat.decode_workspace(dw.batch, dw.H, splits, dev)
+
+    def reuse(i):
+        kc, vc, bt = caches[i % len(caches)]
+        nat.decode_sparse_paged(qs[i % len(qs)], nat.kv_layout_paged(kc, vc, bt), dstrat._dec_idx, dstrat._dec_count,
+                                kmax, None, scaling, o, None, ws, splits)
+    reuse(0)
+    t_reuse = _time_cuda(reuse, 20) * 1e3
+    # dense decode of all layers with the library's own dense pass, for the "vs dense" figure
+    stride = -(-dw.context // 4) * 4
+    logits = torch.empty(dw.batch, dw.H, stride, dtype=torch.float32, device=dev)
+    pooled = torch.empty(dw.batch, dw.G, stride, dtype=torch.float32, device=dev)
+    lse2 = torch.empty(dw.batch, dw.H, dtype=torch.float32, device=dev)
+    sa = nat.decode_default_splits(dw.batch, dw.G, dw.context)
+    wsa = nat.decode_workspace(dw.batch, dw.H, sa, dev)
+
+    def dense_dec(i):
+        kc, vc, bt = caches[i % len(caches)]
+        nat.decode_anchor_paged(qs[i % len(qs)], nat.kv_layout_paged(kc, vc, bt), seq_lens, dw.context, scaling, logits,
+                                pooled, o, lse2, wsa, sa)
+    dense_dec(0)
+    t_dense = _time_cuda(dense_dec, 8) * 1e3
+    gbs_reuse = dw.bytes_reuse() / (t_reuse * 1e-6) / 1e9
+    decode = {"us_per_step": us_step, "layers": dw.layers, "batch_per_gpu": dw.batch, "context": dw.context,
+              "page": dw.page, "topk": dw.budget(), "distinct_layer_caches": dw.distinct_caches,
+              "gpu_launches": dl,
+              "algorithmic_gb_per_step": dw.bytes_step() / 1e9,
+              "achieved_gbs_step": dw.bytes_step() / (us_step * 1e-6) / 1e9,
+              "frac_step": dw.bytes_step() / (us_step * 1e-6) / 1e9 / peaks["hbm_gbs"],
+              "reuse_layer_us": t_reuse,
+              "roofline": {"kernel": "decode_attn_kernel<sparse>", "bound": "hbm", "achieved": gbs_reuse,
+                           "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs_reuse / peaks["hbm_gbs"],
+                           "traffic": None, "peak_source": peaks["source"]},
+              "dense_layer_us": t_dense, "dense_us_per_step": t_dense * dw.layers,
+              "dense_layer_gbs": 2 * dw.bytes_dense_k() / (t_dense * 1e-6) / 1e9,
+              "speedup_vs_dense": t_dense * dw.layers / us_step}
+    del caches, logits, pooled
+    torch.cuda.empty_cache()
+    return decode
+
+
 # ------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -173,6 +252,8 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-dense", action="store_true")
+    ap.add_argument("--decode-only", action="store_true", help="profiling aid: run only the decode configuration")
+    ap.add_argument("--decode-batch", type=int, default=None, help="profiling aid: decode batch (default 64)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -192,6 +273,11 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     peaks = _peaks()
+    if args.decode_only:
+        decode = bench_decode(args, dev, world, peaks, args.decode_batch)
+        if rank == 0:
+            print(json.dumps({"metric": "decode only (profiling aid)", "decode": decode}), flush=True)
+        return
 
     # ---------------- prefill stack (headline) -----------------------------------------------------
     wl = PrefillWorkload(seq_len=args.seq_len)
@@ -330,78 +416,7 @@ def main():
     strat._buf.clear()
     torch.cuda.empty_cache()
 
-    # ---------------- paged sparse decode (batch 64, context 32768) -------------------------------
-    decode = None
-    if not args.skip_decode:
-        dw = DecodeWorkload()
-        assert dw.batch % world == 0
-        dw.batch //= world                                            # batch-sharded across ranks
-        dstrat = EfficientKascadeStrategy(list(dw.anchors), "synthetic/llama31-8b-shape", k=dw.pct, tile_size=32,
-                                          rolling_prefill=True, head_mapping=dw.head_mapping(), register=False)
-        caches = [dw.make_cache(i, dev) for i in range(dw.distinct_caches)]
-        qs = [dw.query(l, dev) for l in range(dw.layers)]
-        seq_lens = torch.full((dw.batch,), dw.context, dtype=torch.int32, device=dev)
-        dout = {}
-
-        def dstep(_i=0):
-            for l in range(dw.layers):
-                kc, vc, bt = caches[l % len(caches)]
-                dout["o"] = dstrat.paged_decode_forward(l, qs[l], kc, vc, bt, seq_lens, scaling, dw.context)
-
-        for _ in range(args.warmup):
-            dstep()
-        if world > 1:
-            dist.barrier()
-        n0 = nat.launch_count
-        t = torch.tensor([_time_cuda(dstep, args.steps)], device=dev)
-        dl = (nat.launch_count - n0) // max(args.steps, 1)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        us_step = float(t.item()) * 1e3
-        # reuse-layer kernel alone (the dominant decode kernel by launches: 27 of 32 layers)
-        kc, vc, bt = caches[0]
-        kv = nat.kv_layout_paged(kc, vc, bt)
-        o = torch.empty(dw.batch, dw.H, dw.D, dtype=torch.float16, device=dev)
-        kmax = dstrat._dec_kmax
-        splits = nat.decode_default_splits(dw.batch, dw.G, kmax)
-        ws = nat.decode_workspace(dw.batch, dw.H, splits, dev)
-
-        def reuse(i):
-            kc, vc, bt = caches[i % len(caches)]
-            nat.decode_sparse_paged(qs[i % len(qs)], nat.kv_layout_paged(kc, vc, bt), dstrat._dec_idx, dstrat._dec_count,
-                                    kmax, None, scaling, o, None, ws, splits)
-        reuse(0)
-        t_reuse = _time_cuda(reuse, 20) * 1e3
-        # dense decode of all layers with the library's own dense pass, for the "vs dense" figure
-        stride = -(-dw.context // 4) * 4
-        logits = torch.empty(dw.batch, dw.H, stride, dtype=torch.float32, device=dev)
-        pooled = torch.empty(dw.batch, dw.G, stride, dtype=torch.float32, device=dev)
-        lse2 = torch.empty(dw.batch, dw.H, dtype=torch.float32, device=dev)
-        sa = nat.decode_default_splits(dw.batch, dw.G, dw.context)
-        wsa = nat.decode_workspace(dw.batch, dw.H, sa, dev)
-
-        def dense_dec(i):
-            kc, vc, bt = caches[i % len(caches)]
-            nat.decode_anchor_paged(qs[i % len(qs)], nat.kv_layout_paged(kc, vc, bt), seq_lens, dw.context, scaling, logits,
-                                    pooled, o, lse2, wsa, sa)
-        dense_dec(0)
-        t_dense = _time_cuda(dense_dec, 8) * 1e3
-        gbs_reuse = dw.bytes_reuse() / (t_reuse * 1e-6) / 1e9
-        decode = {"us_per_step": us_step, "layers": dw.layers, "batch_per_gpu": dw.batch, "context": dw.context,
-                  "page": dw.page, "topk": dw.budget(), "distinct_layer_caches": dw.distinct_caches,
-                  "gpu_launches": dl,
-                  "algorithmic_gb_per_step": dw.bytes_step() / 1e9,
-                  "achieved_gbs_step": dw.bytes_step() / (us_step * 1e-6) / 1e9,
-                  "frac_step": dw.bytes_step() / (us_step * 1e-6) / 1e9 / peaks["hbm_gbs"],
-                  "reuse_layer_us": t_reuse,
-                  "roofline": {"kernel": "decode_attn_kernel<sparse>", "bound": "hbm", "achieved": gbs_reuse,
-                               "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs_reuse / peaks["hbm_gbs"],
-                               "traffic": None, "peak_source": peaks["source"]},
-                  "dense_layer_us": t_dense, "dense_us_per_step": t_dense * dw.layers,
-                  "dense_layer_gbs": 2 * dw.bytes_dense_k() / (t_dense * 1e-6) / 1e9,
-                  "speedup_vs_dense": t_dense * dw.layers / us_step}
-        del caches, logits, pooled
-        torch.cuda.empty_cache()
+    decode = None if args.skip_decode else bench_decode(args, dev, world, peaks)
     status |= nat.read_status()
 
     # ---------------- CPU baseline (rank 0, N = 1) --------------------------------------------------
