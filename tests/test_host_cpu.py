@@ -1,0 +1,92 @@
+"""Host-side logic and the C-ABI surface, without a GPU."""
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from kascade_b200 import _native as nat
+    lib = nat.load()                                   # dlopen only: no CUDA call
+    header = open(os.path.join(ROOT, "include", "kascade_b200.h")).read()
+    declared = sorted(set(re.findall(r"\b(kb200_[a-z0-9_]+)\s*\(", header)))
+    assert len(declared) >= 14
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/kascade_b200.h but not exported"
+    assert sorted(nat.EXPORTS) == [d for d in declared if d in nat.EXPORTS]
+    assert set(declared) <= set(nat.EXPORTS), set(declared) - set(nat.EXPORTS)
+    assert lib.kb200_abi_version() == 1
+    assert lib.kb200_decode_workspace_bytes(64, 32, 2) == 64 * 32 * 2 * 130 * 4
+
+
+def test_calls_fail_loudly_without_a_gpu():
+    from kascade_b200 import _native as nat
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    with pytest.raises(nat.KascadeNativeError):
+        nat.init()
+    # the C side refuses to launch before kb200_init
+    lib = nat.load()
+    assert lib.kb200_topk_select(None, 0, 0, None, None, 0, None, 0, None, 0, None) != 0
+    assert b"kb200_init" in lib.kb200_last_error()
+
+
+def test_budget_matches_reference_formula():
+    from kascade_b200 import topk_budget
+    from oracle.kascade_oracle import topk_budget as oracle_budget
+    for lk in (129, 200, 1280, 2048, 2049, 32768, 131072):
+        for pct in (10, 20, 50):
+            assert topk_budget(pct, lk, 32) == oracle_budget(pct, lk, 32)
+
+
+def test_strategy_constructor_contract(tmp_path, monkeypatch):
+    from kascade_b200 import EfficientKascadeStrategy
+    monkeypatch.chdir(tmp_path)
+    with pytest.raises(ValueError, match="Head mapping file not found"):
+        EfficientKascadeStrategy([0, 2], "org/some-model", k=10, tile_size=32, register=False)
+    os.makedirs("results/head_mappings")
+    hm = np.stack([np.arange(8), np.zeros(8), np.arange(8), np.array([1, 1, 1, 1, 1, 1, 4, 1])]).astype(np.int32)
+    np.save("results/head_mappings/some-model_layers_0_2.npy", hm)
+    s = EfficientKascadeStrategy([0, 2], "org/some-model", k=10, tile_size=32, rolling_prefill=True, register=False)
+    assert s.name == "efficient_kascade"
+    assert s._head_mapping == hm.tolist()
+    assert s.is_anchor(0) and s.is_anchor(2) and not s.is_anchor(1)
+    with pytest.raises(ValueError):
+        EfficientKascadeStrategy([0], "org/some-model", k=10, tile_size=16, register=False)
+    with pytest.raises(AssertionError):
+        EfficientKascadeStrategy([0], "org/some-model", k=101, tile_size=32, register=False)
+    with pytest.raises(ValueError):
+        EfficientKascadeStrategy(None, "org/some-model", k=10, tile_size=32, register=False)
+
+
+def test_registers_in_hf_registries():
+    from transformers.masking_utils import ALL_MASK_ATTENTION_FUNCTIONS
+    from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+    from kascade_b200 import EfficientKascadeStrategy
+    s = EfficientKascadeStrategy([0], "x/y", k=10, tile_size=32, head_mapping=[list(range(8))] * 2)
+    assert s.name in ALL_ATTENTION_FUNCTIONS.valid_keys()
+    assert s.name in ALL_MASK_ATTENTION_FUNCTIONS.valid_keys()
+
+
+def test_shard_helpers():
+    from kascade_b200.strategy import shard_head_map, shard_kv_heads
+    assert shard_kv_heads(8, 1, 4) == [2, 3]
+    assert shard_head_map([7, 1, 5, 6, 3, 3, 3, 3], 3, 4) == [3, 3]
+    assert shard_head_map([7, 1, 5, 6, 3, 3, 3, 3], 0, 2) == [7, 1, 5, 6]
+    with pytest.raises(ValueError):
+        shard_kv_heads(8, 0, 3)
+
+
+def test_workload_accounting():
+    from kascade_b200.workloads import DecodeWorkload, PrefillWorkload
+    wl = PrefillWorkload()
+    assert abs(wl.flops_dense() / 1e12 - 8.796) < 0.01
+    assert abs(wl.flops_sparse() / 1e12 - 0.897) < 0.01
+    assert abs(wl.flops_stack() / 1e12 - 76.2) < 0.2
+    dw = DecodeWorkload()
+    assert dw.budget() == 3244
+    assert abs(dw.bytes_dense_k() / 1e9 - 4.295) < 0.01
