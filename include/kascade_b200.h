@@ -115,6 +115,35 @@ int kb200_decode_sparse_paged(const void* q, int64_t q_stride_b, int64_t q_strid
                               size_t workspace_bytes, int batch, int num_q_heads, int num_kv_heads,
                               int num_splits, void* stream);
 
+/* Sparse decode for callers that cannot allocate.  No counterpart in the reference.
+ *
+ * Some hosts of this library have no way to give it a workspace: an inference server that hands all
+ * free HBM to its KV-cache pool at start-up and treats any later cudaMalloc as a bug, a plugin slot
+ * whose interface carries only inputs and outputs, a latency-critical loop that must not take the
+ * allocator lock.  For them this entry point computes exactly what kb200_decode_sparse_paged
+ * computes, with the split partials kept in a fixed array inside the library image instead of a
+ * caller-owned workspace.  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ *  - Limit: batch * num_q_heads * num_splits <= KB200_NOALLOC_MAX_SLOTS (4.06 MiB of partials, held
+ *    by every GPU that loads the library until the process exits).  With num_splits = 0 the library
+ *    lowers its own choice until it fits; an explicit num_splits that does not fit is rejected with
+ *    a message, nothing is launched.  num_splits = 1 needs no scratch and always fits.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress) with that
+ *    device current, and caches it; make that first call during set-up, before any stream capture.
+ *    The device that is current at the call must be the one that owns the pointers.
+ *  - All calls on a device share the one array.  Nothing in it has to start at zero — every slot the
+ *    merge step reads is written earlier in the same call — but two calls that overlap on the GPU
+ *    (different streams, or different host threads) race on it: serialise them, or use the variant
+ *    with a workspace.
+ * Arguments as kb200_decode_sparse_paged, without workspace / workspace_bytes. */
+#define KB200_NOALLOC_MAX_SLOTS 8192
+int kb200_decode_sparse_paged_noalloc(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                      const kb200_kv_layout* kv, const int32_t* topk_idx,
+                                      int64_t idx_stride_b, int64_t idx_stride_g,
+                                      const int32_t* topk_count, int k_max, const int32_t* head_map,
+                                      float softmax_scale, void* out, float* lse2_out, int batch,
+                                      int num_q_heads, int num_kv_heads, int num_splits, void* stream);
+
 /* Anchor-layer decode: dense pass over all seq_lens[b] cached keys.  Writes the scaled base-2
  * logits of every (head, key), the per-head lse2, optionally the dense output, and the pooled
  * post-softmax score  pooled[b,g,j] = sum_{h in group g} exp2(logit[b,h,j] - lse2[b,h])

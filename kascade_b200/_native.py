@@ -23,6 +23,7 @@ EXPORTS = [
     "kb200_decode_workspace_bytes", "kb200_decode_default_splits", "kb200_decode_sparse_paged",
     "kb200_decode_anchor_paged", "kb200_prefill_dense", "kb200_prefill_pool_scores",
     "kb200_prefill_sparse", "kb200_prefill_budgets", "kb200_selftest_umma", "kb200_read_status",
+    "kb200_decode_sparse_paged_noalloc",
 ]
 
 
@@ -71,6 +72,8 @@ def load() -> C.CDLL:
         lib.kb200_decode_sparse_paged.argtypes = [vp, i64, i64, C.POINTER(KvLayout), vp, i64, i64, vp,
                                                   i32, vp, f32, vp, vp, vp, C.c_size_t, i32, i32, i32,
                                                   i32, vp]
+        lib.kb200_decode_sparse_paged_noalloc.argtypes = [vp, i64, i64, C.POINTER(KvLayout), vp, i64, i64, vp,
+                                                          i32, vp, f32, vp, vp, i32, i32, i32, i32, vp]
         lib.kb200_decode_anchor_paged.argtypes = [vp, i64, i64, C.POINTER(KvLayout), vp, i32, f32, vp,
                                                   vp, i64, vp, vp, vp, C.c_size_t, i32, i32, i32, i32,
                                                   vp]
@@ -192,6 +195,28 @@ def decode_sparse_paged(q, kv: KvLayout, topk_idx, topk_count, k_max, head_map, 
         "kb200_decode_sparse_paged")
     ns = num_splits if num_splits else lib.kb200_decode_default_splits(B, G, k_max)
     _launched(1 + (ns > 1))
+
+
+NOALLOC_MAX_SLOTS = 8192
+
+
+def decode_sparse_paged_noalloc(q, kv: KvLayout, topk_idx, topk_count, k_max, head_map, scale, out, lse2=None,
+                                num_splits=0):
+    """Same result as decode_sparse_paged, for callers that cannot allocate or pass a workspace: the split
+    partials live in a fixed array inside the library (batch * heads * splits <= NOALLOC_MAX_SLOTS).
+    Calls that overlap on the GPU race on that array; the first call on a device belongs in set-up."""
+    lib = init(q.device.index)
+    _want(q, torch.float16, "q")
+    _want(out, torch.float16, "out")
+    _want(topk_idx, torch.int32, "topk_idx")
+    B, H, D = q.shape
+    G = topk_idx.shape[1]
+    assert D == HEAD_DIM and q.stride(2) == 1 and out.is_contiguous() and topk_idx.stride(2) == 1
+    _check(lib.kb200_decode_sparse_paged_noalloc(
+        _ptr(q), q.stride(0), q.stride(1), C.byref(kv), _ptr(topk_idx), topk_idx.stride(0), topk_idx.stride(1),
+        _ptr(topk_count), k_max, _ptr(head_map), float(scale), _ptr(out), _ptr(lse2), B, H, G, num_splits,
+        _stream()), "kb200_decode_sparse_paged_noalloc")
+    _launched(2 if num_splits != 1 else 1)
 
 
 def decode_anchor_paged(q, kv: KvLayout, seq_lens, max_seq_len, scale, logits, pooled, out, lse2,

@@ -12,6 +12,8 @@
 // Replaces kernels/flash_decoding/reuse_kascade_gqa_decode.py:50-200 (gathered split-K decode and
 // its combine) and recompute_kascade_gqa_decode.py:49-315 (dense split-K pass with raw-score dump,
 // combine, per-KV-head pooled score).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace kb200 {
@@ -421,6 +423,33 @@ static int set_workspace(DecodeParams& p, void* ws, size_t ws_bytes, int batch, 
   return 0;
 }
 
+// ---- scratch that lives inside the library image (for kb200_decode_sparse_paged_noalloc) ------------
+// Split partials of one call: KB200_NOALLOC_MAX_SLOTS slots of (m, l, O[128]) fp32.  Every GPU that
+// loads the library carries this array until the process exits.
+static __device__ __align__(256) float g_static_partials[KB200_NOALLOC_MAX_SLOTS * (2 + KB200_HEAD_DIM)];
+
+constexpr int kMaxDevices = 64;
+static float* g_static_ptr[kMaxDevices] = {};
+static std::mutex g_static_mutex;
+
+// Device address of g_static_partials on the CURRENT device.  In host code the array's name is only a
+// handle for the runtime, not something a kernel may dereference, so the address is looked up once
+// per device with cudaGetSymbolAddress and cached.
+static int static_partials(float** out) {
+  int dev = -1;
+  KB_CUDA(cudaGetDevice(&dev));
+  KB_REQUIRE(dev >= 0 && dev < kMaxDevices, "decode_noalloc: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_ptr[dev]) {
+    float* ptr = nullptr;
+    KB_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_partials));
+    KB_REQUIRE(ptr != nullptr, "decode_noalloc: cudaGetSymbolAddress returned a null address");
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return 0;
+}
+
 }  // namespace kb200
 
 extern "C" size_t kb200_decode_workspace_bytes(int batch, int num_q_heads, int num_splits) {
@@ -546,6 +575,70 @@ extern "C" int kb200_decode_anchor_paged(const void* q, int64_t q_stride_b, int6
     decode_pool_kernel<<<pgrid, 256, 0, st>>>(logits, lse2_out, seq_lens, pooled, logit_stride,
                                               num_q_heads, num_kv_heads);
     KB_CHECK_LAUNCH("decode_pool_kernel");
+  }
+  return 0;
+}
+
+// Same computation as kb200_decode_sparse_paged, for callers that must not allocate device memory and
+// have no workspace to hand over: the split partials go to an array inside the library image.
+extern "C" int kb200_decode_sparse_paged_noalloc(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                                 const kb200_kv_layout* kv, const int32_t* topk_idx,
+                                                 int64_t idx_stride_b, int64_t idx_stride_g,
+                                                 const int32_t* topk_count, int k_max,
+                                                 const int32_t* head_map, float softmax_scale, void* out,
+                                                 float* lse2_out, int batch, int num_q_heads,
+                                                 int num_kv_heads, int num_splits, void* stream) {
+  using namespace kb200;
+  KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
+  KB_REQUIRE(q && topk_idx && out, "decode_noalloc: null pointer");
+  KB_REQUIRE(batch >= 0 && k_max >= 0, "decode_noalloc: negative size");
+  KB_REQUIRE(num_kv_heads > 0 && num_q_heads == num_kv_heads * kHg,
+             "decode_noalloc: %d query heads / %d KV heads; exactly %d query heads per KV head are supported",
+             num_q_heads, num_kv_heads, kHg);
+  KB_REQUIRE(q_stride_h % 2 == 0 && q_stride_b % 2 == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0,
+             "decode_noalloc: q must be 4-byte aligned with even strides");
+  KB_REQUIRE(num_splits >= 0 && num_splits <= 64, "decode_noalloc: num_splits out of range");
+  if (batch == 0) return 0;
+  DecodeParams p{};
+  if (fill_kv(p, kv, true) != 0) return -1;
+  int splits = num_splits > 0 ? num_splits : default_splits(batch, num_kv_heads, k_max);
+  if (num_splits == 0) {                       // the library's own choice must fit: fall back to fewer splits
+    while (splits > 1 && (long long)batch * num_q_heads * splits > KB200_NOALLOC_MAX_SLOTS) --splits;
+  }
+  const long long slots = (long long)batch * num_q_heads * splits;
+  KB_REQUIRE(splits == 1 || (long long)batch * num_q_heads * splits <= KB200_NOALLOC_MAX_SLOTS,
+             "decode_noalloc: batch %d x %d heads x %d splits = %lld partial slots exceed the built-in scratch of %d "
+             "slots; use fewer splits or kb200_decode_sparse_paged with a caller-owned workspace",
+             batch, num_q_heads, splits, slots, KB200_NOALLOC_MAX_SLOTS);
+  float* scratch = nullptr;
+  if (static_partials(&scratch) != 0) return -1;
+  const size_t bhs = (size_t)batch * num_q_heads * splits;
+  p.ws_m = scratch;
+  p.ws_l = scratch + bhs;
+  p.ws_o = scratch + 2 * bhs;
+  p.q = static_cast<const __half*>(q);
+  p.q_stride_b = q_stride_b;
+  p.q_stride_h = q_stride_h;
+  p.idx = topk_idx;
+  p.idx_stride_b = idx_stride_b;
+  p.idx_stride_g = idx_stride_g;
+  p.count = topk_count;
+  p.k_max = k_max;
+  p.head_map = head_map;
+  p.scale2 = softmax_scale * kLog2e;
+  p.out = static_cast<__half*>(out);
+  p.lse2 = lse2_out;
+  p.H = num_q_heads;
+  p.G = num_kv_heads;
+  p.num_splits = splits;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid(splits, num_kv_heads, batch);
+  decode_attn_kernel<false, true, false><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  KB_CHECK_LAUNCH("decode_attn_kernel<sparse, noalloc>");
+  if (splits > 1) {
+    decode_combine_kernel<true><<<dim3(num_q_heads, batch), kD, 0, st>>>(p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2,
+                                                                       num_q_heads, splits);
+    KB_CHECK_LAUNCH("decode_combine_kernel<noalloc>");
   }
   return 0;
 }
