@@ -14,9 +14,11 @@
 //               sums exp2(s * scale2 - lse2[row]) over the 128 rows of the tile for its key
 //               (replaces `aggregate`, recompute_kascade_gqa_prefill.py:171-222)
 //
-// Warp roles (288 threads): warps 0-3 softmax / reducer (one thread per tensor-memory lane),
-// warps 4-7 producers (cp.async 16-byte chunks, 16 lanes per 256-byte row, written in the
-// 128-byte-swizzled operand layout of umma.cuh), warp 8 issues the MMAs from one thread.
+// Warp roles (416 threads): warps 0-7 softmax / reducer — two warpgroups, each thread owns one
+// tensor-memory lane and one half of the 128 columns of a block, so that two warps per SM
+// sub-partition overlap their tcgen05.ld / ex2 / FMA chains; warps 8-11 producers (cp.async 16-byte
+// chunks, 16 lanes per 256-byte row, written in the 128-byte-swizzled operand layout of umma.cuh);
+// warp 12 issues the MMAs from one thread.
 // Hand-offs are mbarriers; every wait is bounded (umma::mbar_wait) and a kernel that gives up
 // records a code in the device status word, drains its copies, frees its tensor memory and returns.
 //
@@ -29,9 +31,13 @@ namespace kb200 {
 
 enum PrefillMode { kDenseAttn = 0, kDenseLse = 1, kSparse = 2, kPool = 3 };
 
-constexpr int kPfThreads = 288;
+constexpr int kSoftmaxThreads = 256;             // warps 0-7
+constexpr int kProducerWarp0 = 8;                // warps 8-11
+constexpr int kMmaWarp = 12;
+constexpr int kPfThreads = 13 * 32;
 constexpr int kStageBytes = 128 * kD * 2;     // one 128-row operand tile (32 KB)
-constexpr int kNK = 3, kNV = 3;               // ring depths
+constexpr int kNKMax = 6;                     // K ring: 3 stages with a V ring, 6 without
+constexpr int kNV = 3;
 
 __device__ int g_status_word = 0;
 
@@ -69,6 +75,17 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Barriers and small exchange buffers; lives in dynamic shared memory behind the operand tiles so that
+// the 7 x 32 KB tiles, the alignment padding and this block together stay inside the 227 KB limit.
+struct PfShared {
+  uint64_t bar_q, bar_kfull[kNKMax], bar_kempty[kNKMax], bar_vfull[kNV], bar_vempty[kNV];
+  uint64_t bar_sfull[2], bar_pready[2], bar_odone, bar_x[2];
+  uint32_t tmem;
+  int give_up;
+  float xchg[2][2][128];                               // [block parity][column half][row]
+};
+constexpr int kPadAllowance = 768;                     // tiles need 1024-byte alignment
+
 template <int MODE>
 __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const PrefillParams p) {
   using namespace umma;
@@ -76,14 +93,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
   constexpr bool POOL = MODE == kPool;
   constexpr bool GATHER = MODE == kSparse;
   constexpr int GROUPS_PER_BLOCK = HAS_V ? 2 : 1;     // cp.async groups committed per key block
+  constexpr int kNK = HAS_V ? 3 : kNKMax;             // K ring depth
+  // Blocks kept in flight behind the newest one.  With a V ring the MMA warp issues Q.K^T of block
+  // j+1 before P.V of block j, so block j+1 must be published without waiting for the V stage that
+  // P.V(j) frees: the lag may not exceed kNV - 2.
+  constexpr int kLag = HAS_V ? 1 : 4;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bar_q, bar_kfull[kNK], bar_kempty[kNK], bar_vfull[kNV], bar_vempty[kNV];
-  __shared__ uint64_t bar_sfull[2], bar_pready[2], bar_odone;
-  __shared__ uint32_t tmem_sh;
-  __shared__ int give_up;
-  __shared__ float lse_s[128];
-
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int t = (int)gridDim.x - 1 - (int)blockIdx.x;   // long tiles first
   const int g = blockIdx.y, b = blockIdx.z;
@@ -106,8 +122,30 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
   }
   const int nb = (total + 127) >> 7;
   if (nb == 0) return;                                   // pool pass of tile 0: no earlier keys
+  // an earlier CTA or kernel gave up a bounded wait: do not queue up more waits behind it
+  if (*reinterpret_cast<volatile int*>(&g_status_word) != 0) return;
 
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t pad = (1024u - (smem_addr(smem_raw) & 1023u)) & 1023u;
+  if (pad > (uint32_t)kPadAllowance) {                   // never seen; refuse rather than overrun
+    if (tid == 0) atomicCAS(&g_status_word, 0, 90);
+    return;
+  }
+  uint8_t* smem = smem_raw + pad;
+  constexpr int kTiles = 1 + kNK + (HAS_V ? kNV : 0);
+  PfShared& sh = *reinterpret_cast<PfShared*>(smem + kTiles * kStageBytes);
+  uint64_t& bar_q = sh.bar_q;
+  uint64_t* bar_kfull = sh.bar_kfull;
+  uint64_t* bar_kempty = sh.bar_kempty;
+  uint64_t* bar_vfull = sh.bar_vfull;
+  uint64_t* bar_vempty = sh.bar_vempty;
+  uint64_t* bar_sfull = sh.bar_sfull;
+  uint64_t* bar_pready = sh.bar_pready;
+  uint64_t& bar_odone = sh.bar_odone;
+  uint64_t* bar_x = sh.bar_x;
+  uint32_t& tmem_sh = sh.tmem;
+  int& give_up = sh.give_up;
+  float (&xchg)[2][2][128] = sh.xchg;
+  float* lse_s = sh.xchg[0][1];                          // kPool only: that mode exchanges through xchg[.][0]
   const uint32_t q_s = smem_addr(smem);
   const uint32_t k_s = q_s + kStageBytes;
   const uint32_t v_s = k_s + kNK * kStageBytes;
@@ -116,14 +154,22 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
     mbar_init(&bar_q, 128);
     for (int i = 0; i < kNK; ++i) { mbar_init(&bar_kfull[i], 128); mbar_init(&bar_kempty[i], 1); }
     for (int i = 0; i < kNV; ++i) { mbar_init(&bar_vfull[i], 128); mbar_init(&bar_vempty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&bar_sfull[i], 1); mbar_init(&bar_pready[i], 128); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_sfull[i], 1);
+      mbar_init(&bar_pready[i], kSoftmaxThreads);
+      mbar_init(&bar_x[i], kSoftmaxThreads);
+    }
     mbar_init(&bar_odone, 1);
     mbar_fence_init();
     give_up = 0;
   }
-  if (warp == 8) {
+  if (warp == kMmaWarp) {
     tmem_alloc(&tmem_sh, 512);
     tmem_relinquish();
+  }
+  if (POOL && tid < 128) {
+    const int tok = tile_start + (tid >> 2);
+    lse_s[tid] = tok < p.L ? p.lse2_in[((int64_t)b * p.L + tok) * p.H + g * kHg + (tid & 3)] : INFINITY;
   }
   tc_fence_before();
   __syncthreads();
@@ -131,9 +177,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
   const uint32_t tmem = tmem_sh;
   const uint32_t t_s0 = tmem, t_o = tmem + 256;
 
-  if (warp >= 4 && warp < 8) {
+  if (warp >= kProducerWarp0 && warp < kMmaWarp) {
     // ================================ producers ================================================
-    const int pw = warp - 4, ptid = tid - 128;
+    const int pw = warp - kProducerWarp0, ptid = tid - kProducerWarp0 * 32;
     const __half* qb = p.q + (int64_t)b * p.q_sb;
 #pragma unroll 4
     for (int it = 0; it < 16; ++it) {
@@ -185,23 +231,25 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
         }
         cp_commit();
       }
-      // everything older than this block's groups has landed: publish it to the async proxy
-      cp_wait<GROUPS_PER_BLOCK>();
-      fence_proxy_async_smem();
-      if (j == 0) {
-        mbar_arrive(&bar_q);
-      } else {
-        mbar_arrive(&bar_kfull[(j - 1) % kNK]);
-        if (HAS_V) mbar_arrive(&bar_vfull[(j - 1) % kNV]);
+      // everything older than the newest kLag blocks has landed: publish it to the async proxy
+      cp_wait<GROUPS_PER_BLOCK * kLag>();
+      if (j >= kLag) {
+        fence_proxy_async_smem();
+        if (j == kLag) mbar_arrive(&bar_q);
+        mbar_arrive(&bar_kfull[(j - kLag) % kNK]);
+        if (HAS_V) mbar_arrive(&bar_vfull[(j - kLag) % kNV]);
       }
     }
     cp_wait<0>();
     fence_proxy_async_smem();
     if (ok) {
-      mbar_arrive(&bar_kfull[(nb - 1) % kNK]);
-      if (HAS_V) mbar_arrive(&bar_vfull[(nb - 1) % kNV]);
+      if (nb <= kLag) mbar_arrive(&bar_q);
+      for (int j = max(0, nb - kLag); j < nb; ++j) {
+        mbar_arrive(&bar_kfull[j % kNK]);
+        if (HAS_V) mbar_arrive(&bar_vfull[j % kNV]);
+      }
     }
-  } else if (warp == 8) {
+  } else if (warp == kMmaWarp) {
     // ================================ MMA issuer ===============================================
     if (lane == 0) {
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
@@ -253,56 +301,67 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
     }
     __syncwarp();
   } else if (!POOL) {
-    // ================================ softmax (one thread per row) =============================
-    const int row = tid, q_local = row >> 2;
+    // ================================ softmax ==================================================
+    // two warpgroups share every S block: thread = (row, column half); the row maximum is exchanged
+    // through shared memory once per block, the row sums are kept per half and added at the end
+    const int half = warp >> 2;
+    const int row = (warp & 3) * 32 + lane, q_local = row >> 2;
     const int tok = tile_start + q_local;
     const int off = GATHER ? count : tile_start;      // slot - off = key position inside the tile
-    const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
-    float m_run = -INFINITY, l_run = 0.f;
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f;             // m_run in the scaled (log2) domain
     bool ok = true;
     for (int j = 0; j < nb; ++j) {
       ok = mbar_wait(&bar_sfull[j & 1], (j >> 1) & 1, &give_up, 31);
       if (!ok) break;
       tc_fence_after();
       const uint32_t ts = t_s0 + (j & 1) * 128 + lane_sel;
-      uint32_t sr[4][32];
-#pragma unroll
-      for (int part = 0; part < 4; ++part) tmem_ld32(ts + part * 32, sr[part]);
+      uint32_t sr[2][32];
+      tmem_ld32(ts + half * 64, sr[0]);
+      tmem_ld32(ts + half * 64 + 32, sr[1]);
       tmem_wait_ld();
-      const bool need_mask = (j * 128 + 127 - off) > 0;
+      if (!HAS_V) {                                      // S is in registers: the buffer may be refilled
+        tc_fence_before();
+        mbar_arrive(&bar_pready[j & 1]);
+      }
+      const int c0 = j * 128 + half * 64 - off;         // key position of this thread's first column
+      const bool need_mask = (c0 + 63) > 0;
+      if (need_mask) {                                   // only the last block(s) of a tile
+#pragma unroll
+        for (int part = 0; part < 2; ++part)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if ((c0 + part * 32 + i) > q_local) sr[part][i] = 0xFF800000u;     // -inf
+      }
       float mx = -INFINITY;
 #pragma unroll
-      for (int part = 0; part < 4; ++part) {
+      for (int part = 0; part < 2; ++part)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(sr[part][i]) * p.scale2;
-          if (need_mask && (j * 128 + part * 32 + i - off) > q_local) x = -INFINITY;
-          sr[part][i] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
-        }
-      }
-      const float m_new = fmaxf(m_run, mx);
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[part][i]));
+      xchg[j & 1][half][row] = mx;
+      mbar_arrive(&bar_x[j & 1]);
+      ok = mbar_wait(&bar_x[j & 1], (j >> 1) & 1, &give_up, 34);
+      if (!ok) break;
+      mx = fmaxf(mx, xchg[j & 1][half ^ 1][row]);
+      const float m_new = fmaxf(m_run, mx * p.scale2);
       const float alpha = ex2(m_run - m_new);
       float sum = 0.f;
       if (HAS_V) {
         uint32_t pr[32];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int c = half * 64 + i * 2;
-            float p0 = ex2(__uint_as_float(sr[c >> 5][c & 31]) - m_new);
-            float p1 = ex2(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]) - m_new);
-            sum += p0 + p1;
-            pr[i] = pack2(p0, p1);
-          }
-          tmem_st32(ts + half * 32, pr);
+        for (int i = 0; i < 32; ++i) {
+          const int c = i * 2;
+          float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale2, -m_new));
+          float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), p.scale2, -m_new));
+          sum += p0 + p1;
+          pr[i] = pack2(p0, p1);
         }
+        tmem_st32(ts + half * 32, pr);
       } else {
 #pragma unroll
-        for (int part = 0; part < 4; ++part)
+        for (int part = 0; part < 2; ++part)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) sum += ex2(__uint_as_float(sr[part][i]) - m_new);
+          for (int i = 0; i < 32; ++i) sum += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -m_new));
       }
       l_run = l_run * alpha + sum;
       m_run = m_new;
@@ -312,31 +371,40 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
         tc_fence_after();
         if (!__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
 #pragma unroll 1
-          for (int part = 0; part < 4; ++part) {
+          for (int part = 0; part < 2; ++part) {
             uint32_t orr[32];
-            tmem_ld32(t_o + lane_sel + part * 32, orr);
+            tmem_ld32(t_o + lane_sel + half * 64 + part * 32, orr);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-            tmem_st32(t_o + lane_sel + part * 32, orr);
+            tmem_st32(t_o + lane_sel + half * 64 + part * 32, orr);
           }
         }
       }
-      if (HAS_V) tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&bar_pready[j & 1]);
+      if (HAS_V) {
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bar_pready[j & 1]);
+      }
     }
-    // ---- epilogue --------------------------------------------------------------------------
+    // ---- epilogue: add the two halves' row sums, normalise, store ------------------------------
+    float l_tot = l_run;
+    if (ok) {
+      xchg[nb & 1][half][row] = l_run;
+      mbar_arrive(&bar_x[nb & 1]);
+      ok = mbar_wait(&bar_x[nb & 1], (nb >> 1) & 1, &give_up, 35);
+      l_tot += xchg[nb & 1][half ^ 1][row];
+    }
     if (ok && HAS_V) {
       ok = mbar_wait(&bar_odone, (nb - 1) & 1, &give_up, 33);
       if (ok) {
         tc_fence_after();
-        const float inv = 1.0f / l_run;
-        __half* orow = p.out + (((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)) * kD;
+        const float inv = 1.0f / l_tot;
+        __half* orow = p.out + (((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)) * kD + half * 64;
 #pragma unroll 1
-        for (int part = 0; part < 4; ++part) {
+        for (int part = 0; part < 2; ++part) {
           uint32_t orr[32];
-          tmem_ld32(t_o + lane_sel + part * 32, orr);
+          tmem_ld32(t_o + lane_sel + half * 64 + part * 32, orr);
           tmem_wait_ld();
           if (tok < p.L) {
 #pragma unroll
@@ -352,34 +420,37 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
         }
       }
     }
-    if (ok && p.lse2 && tok < p.L)
-      p.lse2[((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)] = m_run + log2f(l_run);
+    if (ok && half == 0 && p.lse2 && tok < p.L)
+      p.lse2[((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)] = m_run + log2f(l_tot);
   } else {
-    // ================================ pooled-score reducer (one thread per key) ================
-    {
-      const int tok = tile_start + (tid >> 2);
-      lse_s[tid] = tok < p.L ? p.lse2_in[((int64_t)b * p.L + tok) * p.H + g * kHg + (tid & 3)] : INFINITY;
-    }
-    asm volatile("bar.sync 1, 128;\n" ::: "memory");
-    const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+    // ================================ pooled-score reducer =====================================
+    // thread = (key lane, half of the tile's 128 (query, head) rows); the halves are added through
+    // shared memory and half 0 stores
+    const int half = warp >> 2;
+    const int key_lane = (warp & 3) * 32 + lane;
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     float* prow = p.pooled + (((int64_t)b * p.G + g) * p.T + t) * p.pooled_stride;
     for (int j = 0; j < nb; ++j) {
       if (!mbar_wait(&bar_sfull[j & 1], (j >> 1) & 1, &give_up, 41)) break;
       tc_fence_after();
-      const uint32_t ts = t_s0 + (j & 1) * 128 + lane_sel;
+      const uint32_t ts = t_s0 + (j & 1) * 128 + lane_sel + half * 64;
       float acc = 0.f;
-#pragma unroll 1
-      for (int part = 0; part < 4; ++part) {
-        uint32_t sr[32];
-        tmem_ld32(ts + part * 32, sr);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc += ex2(fmaf(__uint_as_float(sr[i]), p.scale2, -lse_s[part * 32 + i]));
-      }
+      uint32_t sr[2][32];
+      tmem_ld32(ts, sr[0]);
+      tmem_ld32(ts + 32, sr[1]);
+      tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(&bar_pready[j & 1]);
-      const int key = j * 128 + tid;
-      if (key < tile_start) prow[key] = acc;
+      mbar_arrive(&bar_pready[j & 1]);                 // S^T block is in registers: the buffer is free
+#pragma unroll
+      for (int part = 0; part < 2; ++part)
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          acc += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -lse_s[half * 64 + part * 32 + i]));
+      if (half == 1) xchg[j & 1][0][key_lane] = acc;
+      mbar_arrive(&bar_x[j & 1]);
+      if (!mbar_wait(&bar_x[j & 1], (j >> 1) & 1, &give_up, 42)) break;
+      const int key = j * 128 + key_lane;
+      if (half == 0 && key < tile_start) prow[key] = acc + xchg[j & 1][0][key_lane];
     }
   }
 
@@ -387,12 +458,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 8) tmem_dealloc(tmem, 512);
+  if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
   if (tid == 0 && give_up != 0) atomicCAS(&g_status_word, 0, give_up);
 }
 
-constexpr int kSmemAttn = 1024 + kStageBytes * (1 + kNK + kNV);
-constexpr int kSmemNoV = 1024 + kStageBytes * (1 + kNK);
+static_assert(sizeof(PfShared) <= 2304, "PfShared grew");
+constexpr int kSmemAttn = kStageBytes * (1 + 3 + kNV) + kPadAllowance + 2304;   // = 232448, the sm_100 limit
+constexpr int kSmemNoV = kStageBytes * (1 + kNKMax) + kPadAllowance + 2304;
 
 int init_prefill() {
   KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kDenseAttn>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn));
