@@ -22,8 +22,10 @@
 // Hand-offs are mbarriers; every wait is bounded (umma::mbar_wait) and a kernel that gives up
 // records a code in the device status word, drains its copies, frees its tensor memory and returns.
 //
-// Tensor memory (512 columns): S0 [0,128), S1 [128,256), O [256,384).  P (fp16) overwrites the
-// first 64 columns of the S buffer it was computed from and is the A operand of the P.V product.
+// Tensor memory (512 columns): S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512): key blocks of even
+// and odd index form two independent streams (own S buffer, own O accumulator, own softmax warpgroup).
+// P (fp16) overwrites the first 64 columns of the S buffer it was computed from and is the A operand
+// of the P.V product.
 #include "common.cuh"
 #include "umma.cuh"
 
@@ -65,6 +67,15 @@ __device__ __forceinline__ float ex2(float x) {
 __device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
 }
+// 16-byte copy that writes zeros when src_bytes == 0 (the source address must still be valid)
+__device__ __forceinline__ void cp16_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+// the barrier receives one arrival from this thread once all its earlier cp.async have completed
+__device__ __forceinline__ void cp_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(umma::smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_wait() {
@@ -79,7 +90,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 // the 7 x 32 KB tiles, the alignment padding and this block together stay inside the 227 KB limit.
 struct PfShared {
   uint64_t bar_q, bar_kfull[kNKMax], bar_kempty[kNKMax], bar_vfull[kNV], bar_vempty[kNV];
-  uint64_t bar_sfull[2], bar_pready[2], bar_odone, bar_x[2];
+  uint64_t bar_sfull[2], bar_pready[2], bar_odone[2], bar_x;
   uint32_t tmem;
   int give_up;
   float xchg[2][2][128];                               // [block parity][column half][row]
@@ -92,12 +103,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
   constexpr bool HAS_V = MODE == kDenseAttn || MODE == kSparse;
   constexpr bool POOL = MODE == kPool;
   constexpr bool GATHER = MODE == kSparse;
-  constexpr int GROUPS_PER_BLOCK = HAS_V ? 2 : 1;     // cp.async groups committed per key block
   constexpr int kNK = HAS_V ? 3 : kNKMax;             // K ring depth
-  // Blocks kept in flight behind the newest one.  With a V ring the MMA warp issues Q.K^T of block
-  // j+1 before P.V of block j, so block j+1 must be published without waiting for the V stage that
-  // P.V(j) frees: the lag may not exceed kNV - 2.
-  constexpr int kLag = HAS_V ? 1 : 4;
 
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -140,8 +146,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
   uint64_t* bar_vempty = sh.bar_vempty;
   uint64_t* bar_sfull = sh.bar_sfull;
   uint64_t* bar_pready = sh.bar_pready;
-  uint64_t& bar_odone = sh.bar_odone;
-  uint64_t* bar_x = sh.bar_x;
+  uint64_t* bar_odone = sh.bar_odone;
+  uint64_t& bar_x = sh.bar_x;
   uint32_t& tmem_sh = sh.tmem;
   int& give_up = sh.give_up;
   float (&xchg)[2][2][128] = sh.xchg;
@@ -156,10 +162,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
     for (int i = 0; i < kNV; ++i) { mbar_init(&bar_vfull[i], 128); mbar_init(&bar_vempty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_sfull[i], 1);
-      mbar_init(&bar_pready[i], kSoftmaxThreads);
-      mbar_init(&bar_x[i], kSoftmaxThreads);
+      mbar_init(&bar_pready[i], 128);
+      mbar_init(&bar_odone[i], 1);
     }
-    mbar_init(&bar_odone, 1);
+    mbar_init(&bar_x, kSoftmaxThreads);
     mbar_fence_init();
     give_up = 0;
   }
@@ -179,24 +185,24 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
 
   if (warp >= kProducerWarp0 && warp < kMmaWarp) {
     // ================================ producers ================================================
+    // Every thread copies with cp.async and lets the hardware arrive on the stage's "full" barrier when
+    // its copies have landed (cp.async.mbarrier.arrive.noinc): the producers never wait for data, they
+    // run ahead as far as the rings allow.  The MMA warp orders the landed bytes against the tensor
+    // core's reads with a proxy fence after its barrier wait.
     const int pw = warp - kProducerWarp0, ptid = tid - kProducerWarp0 * 32;
     const __half* qb = p.q + (int64_t)b * p.q_sb;
 #pragma unroll 4
     for (int it = 0; it < 16; ++it) {
       const int id = it * 128 + ptid, row = id >> 4, c = id & 15;
       const int tok = tile_start + (row >> 2), head = g * kHg + (row & 3);
-      const uint32_t dst = q_s + tile_off(row, c, 128);
-      if (tok < p.L) {
-        cp16(dst, qb + (int64_t)tok * p.q_st + (int64_t)head * p.q_sh + c * 8);
-      } else {
-        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(dst), "r"(0u));
-      }
+      const bool in = tok < p.L;                         // rows past the prompt are zero-filled
+      cp16_zfill(q_s + tile_off(row, c, 128),
+                 qb + (int64_t)(in ? tok : 0) * p.q_st + (int64_t)head * p.q_sh + c * 8, in ? 16u : 0u);
     }
-    cp_commit();
+    cp_arrive_noinc(&bar_q);
     const __half* kb = p.k + (int64_t)b * p.k_sb + (int64_t)g * p.k_sh;
     const __half* vb = HAS_V ? p.v + (int64_t)b * p.v_sb + (int64_t)g * p.v_sh : nullptr;
-    bool ok = true;
-    for (int j = 0; j < nb && ok; ++j) {
+    for (int j = 0; j < nb; ++j) {
       const int s = j * 128 + pw * 32 + lane;
       int key;
       if (GATHER) key = s < count ? __ldg(idx_row + s) : tile_start + (s - count);
@@ -205,8 +211,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
       key = max(0, min(key, p.L - 1));
       const int64_t offk = (int64_t)key * p.k_st;
       const int64_t offv = HAS_V ? (int64_t)key * p.v_st : 0;
-      ok = mbar_wait(&bar_kempty[j % kNK], ((j / kNK) & 1) ^ 1, &give_up, 11);
-      if (!ok) break;
+      if (!mbar_wait(&bar_kempty[j % kNK], ((j / kNK) & 1) ^ 1, &give_up, 11)) break;
       {
         const uint32_t dst = k_s + (j % kNK) * kStageBytes;
         const int c = lane & 15;
@@ -216,11 +221,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
           const int64_t o = __shfl_sync(0xFFFFFFFFu, offk, rw);
           cp16(dst + tile_off(pw * 32 + rw, c, 128), kb + o + c * 8);
         }
-        cp_commit();
+        cp_arrive_noinc(&bar_kfull[j % kNK]);
       }
       if (HAS_V) {
-        ok = mbar_wait(&bar_vempty[j % kNV], ((j / kNV) & 1) ^ 1, &give_up, 12);
-        if (!ok) break;
+        if (!mbar_wait(&bar_vempty[j % kNV], ((j / kNV) & 1) ^ 1, &give_up, 12)) break;
         const uint32_t dst = v_s + (j % kNV) * kStageBytes;
         const int c = lane & 15;
 #pragma unroll 4
@@ -229,34 +233,20 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
           const int64_t o = __shfl_sync(0xFFFFFFFFu, offv, rw);
           cp16(dst + tile_off(pw * 32 + rw, c, 128), vb + o + c * 8);
         }
-        cp_commit();
-      }
-      // everything older than the newest kLag blocks has landed: publish it to the async proxy
-      cp_wait<GROUPS_PER_BLOCK * kLag>();
-      if (j >= kLag) {
-        fence_proxy_async_smem();
-        if (j == kLag) mbar_arrive(&bar_q);
-        mbar_arrive(&bar_kfull[(j - kLag) % kNK]);
-        if (HAS_V) mbar_arrive(&bar_vfull[(j - kLag) % kNV]);
+        cp_arrive_noinc(&bar_vfull[j % kNV]);
       }
     }
-    cp_wait<0>();
-    fence_proxy_async_smem();
-    if (ok) {
-      if (nb <= kLag) mbar_arrive(&bar_q);
-      for (int j = max(0, nb - kLag); j < nb; ++j) {
-        mbar_arrive(&bar_kfull[j % kNK]);
-        if (HAS_V) mbar_arrive(&bar_vfull[j % kNV]);
-      }
-    }
+    cp_wait_all();                                       // nothing of this CTA is in flight at teardown
   } else if (warp == kMmaWarp) {
     // ================================ MMA issuer ===============================================
     if (lane == 0) {
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
       constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
       bool ok = mbar_wait(&bar_q, 0, &give_up, 21);
+      fence_proxy_async_smem();
       auto issue_qk = [&](int j) -> bool {
         if (!mbar_wait(&bar_kfull[j % kNK], (j / kNK) & 1, &give_up, 22)) return false;
+        fence_proxy_async_smem();                        // cp.async bytes -> visible to the tensor core
         tc_fence_after();
         const uint32_t ks_addr = k_s + (j % kNK) * kStageBytes;
         const uint32_t d = t_s0 + (j & 1) * 128;
@@ -286,171 +276,229 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
           if (!ok) break;
           ok = mbar_wait(&bar_vfull[j % kNV], (j / kNV) & 1, &give_up, 25);
           if (!ok) break;
+          fence_proxy_async_smem();
           tc_fence_after();
           const uint32_t vs_addr = v_s + (j % kNV) * kStageBytes;
           const uint32_t a = t_s0 + (j & 1) * 128;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
-            mma_ts(t_o, a + ks * 8, desc_mnmajor(vs_addr + ks * 2048, kStageBytes / 2), idesc_pv,
-                   (j > 0 || ks > 0) ? 1u : 0u);
+            mma_ts(t_o + (j & 1) * 128, a + ks * 8, desc_mnmajor(vs_addr + ks * 2048, kStageBytes / 2), idesc_pv,
+                   (j > 1 || ks > 0) ? 1u : 0u);
           }
           mma_commit(&bar_vempty[j % kNV]);
-          mma_commit(&bar_odone);
+          mma_commit(&bar_odone[j & 1]);
         }
       }
     }
     __syncwarp();
   } else if (!POOL) {
     // ================================ softmax ==================================================
-    // two warpgroups share every S block: thread = (row, column half); the row maximum is exchanged
-    // through shared memory once per block, the row sums are kept per half and added at the end
-    const int half = warp >> 2;
+    // Two warpgroups, two independent streams: warpgroup w owns the key blocks j = w, w+2, ... with its
+    // own S buffer, its own running (max, sum) per row and (with V) its own O accumulator, so the
+    // tcgen05.ld / max / ex2 phases of one stream overlap those of the other and nothing is exchanged
+    // per block.  The streams are merged like split-K partials in the epilogue.
+    const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane, q_local = row >> 2;
     const int tok = tile_start + q_local;
     const int off = GATHER ? count : tile_start;      // slot - off = key position inside the tile
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t ts = t_s0 + wg * 128 + lane_sel;   // this stream's S / P buffer
+    const uint32_t to = t_o + wg * 128 + lane_sel;    // this stream's O accumulator
     float m_run = -INFINITY, l_run = 0.f;             // m_run in the scaled (log2) domain
     bool ok = true;
-    for (int j = 0; j < nb; ++j) {
-      ok = mbar_wait(&bar_sfull[j & 1], (j >> 1) & 1, &give_up, 31);
+    int it = 0;                                       // blocks this stream has processed
+    for (int j = wg; j < nb; j += 2, ++it) {
+      ok = mbar_wait(&bar_sfull[wg], it & 1, &give_up, 31);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t ts = t_s0 + (j & 1) * 128 + lane_sel;
-      uint32_t sr[2][32];
-      tmem_ld32(ts + half * 64, sr[0]);
-      tmem_ld32(ts + half * 64 + 32, sr[1]);
-      tmem_wait_ld();
-      if (!HAS_V) {                                      // S is in registers: the buffer may be refilled
-        tc_fence_before();
-        mbar_arrive(&bar_pready[j & 1]);
-      }
-      const int c0 = j * 128 + half * 64 - off;         // key position of this thread's first column
-      const bool need_mask = (c0 + 63) > 0;
-      if (need_mask) {                                   // only the last block(s) of a tile
+      const int c0 = j * 128 - off;                     // key position (inside the tile) of column 0
+      const bool need_mask = (c0 + 127) > 0;            // only the last block(s) of a tile
+      // ---- pass 1: row maximum ----------------------------------------------------------------
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int part = 0; part < 2; ++part)
+      for (int part = 0; part < 4; ++part) {
+        uint32_t sr[32];
+        tmem_ld32(ts + part * 32, sr);
+        tmem_wait_ld();
+        if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if ((c0 + part * 32 + i) > q_local) sr[part][i] = 0xFF800000u;     // -inf
+            if ((c0 + part * 32 + i) > q_local) sr[i] = 0xFF800000u;     // -inf
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
+        }
       }
-      float mx = -INFINITY;
-#pragma unroll
-      for (int part = 0; part < 2; ++part)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[part][i]));
-      xchg[j & 1][half][row] = mx;
-      mbar_arrive(&bar_x[j & 1]);
-      ok = mbar_wait(&bar_x[j & 1], (j >> 1) & 1, &give_up, 34);
-      if (!ok) break;
-      mx = fmaxf(mx, xchg[j & 1][half ^ 1][row]);
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = fmaxf(m_run, mx * p.scale2);
       const float alpha = ex2(m_run - m_new);
-      float sum = 0.f;
-      if (HAS_V) {
-        uint32_t pr[32];
+      // ---- pass 2: exponentials, row sum, P -----------------------------------------------------
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int c = i * 2;
-          float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale2, -m_new));
-          float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), p.scale2, -m_new));
-          sum += p0 + p1;
-          pr[i] = pack2(p0, p1);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sa[32], sb[32];
+        tmem_ld32(ts + half * 64, sa);
+        tmem_ld32(ts + half * 64 + 32, sb);
+        tmem_wait_ld();
+        if (!HAS_V && half == 1) {                       // S is in registers: the buffer may be refilled
+          tc_fence_before();
+          mbar_arrive(&bar_pready[wg]);
         }
-        tmem_st32(ts + half * 32, pr);
-      } else {
+        if (need_mask) {
 #pragma unroll
-        for (int part = 0; part < 2; ++part)
+          for (int i = 0; i < 32; ++i) {
+            if ((c0 + half * 64 + i) > q_local) sa[i] = 0xFF800000u;
+            if ((c0 + half * 64 + 32 + i) > q_local) sb[i] = 0xFF800000u;
+          }
+        }
+        if (HAS_V) {
+          uint32_t pr[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) sum += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -m_new));
-      }
-      l_run = l_run * alpha + sum;
-      m_run = m_new;
-      if (HAS_V && j > 0) {
-        ok = mbar_wait(&bar_odone, (j - 1) & 1, &give_up, 32);
-        if (!ok) break;
-        tc_fence_after();
-        if (!__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
-#pragma unroll 1
-          for (int part = 0; part < 2; ++part) {
-            uint32_t orr[32];
-            tmem_ld32(t_o + lane_sel + half * 64 + part * 32, orr);
-            tmem_wait_ld();
+          for (int i = 0; i < 16; i += 2) {
+            float a0 = ex2(fmaf(__uint_as_float(sa[2 * i]), p.scale2, -m_new));
+            float a1 = ex2(fmaf(__uint_as_float(sa[2 * i + 1]), p.scale2, -m_new));
+            float a2 = ex2(fmaf(__uint_as_float(sa[2 * i + 2]), p.scale2, -m_new));
+            float a3 = ex2(fmaf(__uint_as_float(sa[2 * i + 3]), p.scale2, -m_new));
+            float b0 = ex2(fmaf(__uint_as_float(sb[2 * i]), p.scale2, -m_new));
+            float b1 = ex2(fmaf(__uint_as_float(sb[2 * i + 1]), p.scale2, -m_new));
+            float b2 = ex2(fmaf(__uint_as_float(sb[2 * i + 2]), p.scale2, -m_new));
+            float b3 = ex2(fmaf(__uint_as_float(sb[2 * i + 3]), p.scale2, -m_new));
+            s0 += a0 + a1; s1 += a2 + a3; s2 += b0 + b1; s3 += b2 + b3;
+            pr[i] = pack2(a0, a1);
+            pr[i + 1] = pack2(a2, a3);
+            pr[16 + i] = pack2(b0, b1);
+            pr[16 + i + 1] = pack2(b2, b3);
+          }
+          tmem_st32(ts + half * 32, pr);                 // P columns [half*32, +32) = keys [half*64, +64)
+        } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-            tmem_st32(t_o + lane_sel + half * 64 + part * 32, orr);
+          for (int i = 0; i < 32; i += 2) {
+            s0 += ex2(fmaf(__uint_as_float(sa[i]), p.scale2, -m_new));
+            s1 += ex2(fmaf(__uint_as_float(sa[i + 1]), p.scale2, -m_new));
+            s2 += ex2(fmaf(__uint_as_float(sb[i]), p.scale2, -m_new));
+            s3 += ex2(fmaf(__uint_as_float(sb[i + 1]), p.scale2, -m_new));
           }
         }
       }
+      l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
+      m_run = m_new;
       if (HAS_V) {
+        if (it > 0) {
+          ok = mbar_wait(&bar_odone[wg], (it - 1) & 1, &give_up, 32);
+          if (!ok) break;
+          tc_fence_after();
+          if (!__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
+#pragma unroll 1
+            for (int part = 0; part < 4; ++part) {
+              uint32_t orr[32];
+              tmem_ld32(to + part * 32, orr);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+              tmem_st32(to + part * 32, orr);
+            }
+          }
+        }
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&bar_pready[j & 1]);
+        mbar_arrive(&bar_pready[wg]);
       }
     }
-    // ---- epilogue: add the two halves' row sums, normalise, store ------------------------------
-    float l_tot = l_run;
+    // ---- epilogue: merge the two streams, normalise, store -------------------------------------
+    // it = number of blocks of this stream; the other stream has nb - it
+    float f_mine = 1.f, f_other = 0.f, l_tot = l_run, m_tot = m_run;
     if (ok) {
-      xchg[nb & 1][half][row] = l_run;
-      mbar_arrive(&bar_x[nb & 1]);
-      ok = mbar_wait(&bar_x[nb & 1], (nb >> 1) & 1, &give_up, 35);
-      l_tot += xchg[nb & 1][half ^ 1][row];
+      xchg[0][wg][row] = m_run;
+      xchg[1][wg][row] = l_run;
+      mbar_arrive(&bar_x);
+      ok = mbar_wait(&bar_x, 0, &give_up, 35);
+      if (ok) {
+        const float m_o = xchg[0][wg ^ 1][row], l_o = xchg[1][wg ^ 1][row];
+        m_tot = fmaxf(m_run, m_o);
+        f_mine = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_tot);
+        f_other = (m_o == -INFINITY) ? 0.f : ex2(m_o - m_tot);
+        l_tot = l_run * f_mine + l_o * f_other;
+      }
     }
     if (ok && HAS_V) {
-      ok = mbar_wait(&bar_odone, (nb - 1) & 1, &give_up, 33);
+      const int n_mine = it, n_other = nb - it;
+      if (n_mine > 0) ok = mbar_wait(&bar_odone[wg], (n_mine - 1) & 1, &give_up, 33);
+      if (ok && n_other > 0) ok = mbar_wait(&bar_odone[wg ^ 1], (n_other - 1) & 1, &give_up, 36);
       if (ok) {
         tc_fence_after();
         const float inv = 1.0f / l_tot;
-        __half* orow = p.out + (((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)) * kD + half * 64;
+        const float w_mine = f_mine * inv, w_other = f_other * inv;
+        // this warpgroup stores output columns [wg*64, +64) of its rows, from both accumulators
+        __half* orow = p.out + (((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)) * kD + wg * 64;
+        const uint32_t o_mine = t_o + wg * 128 + lane_sel + wg * 64;
+        const uint32_t o_other = t_o + (wg ^ 1) * 128 + lane_sel + wg * 64;
 #pragma unroll 1
         for (int part = 0; part < 2; ++part) {
-          uint32_t orr[32];
-          tmem_ld32(t_o + lane_sel + half * 64 + part * 32, orr);
+          uint32_t oa[32], ob[32];
+          if (n_mine > 0) tmem_ld32(o_mine + part * 32, oa);
+          if (n_other > 0) tmem_ld32(o_other + part * 32, ob);
           tmem_wait_ld();
           if (tok < p.L) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float x = n_mine > 0 ? __uint_as_float(oa[i]) * w_mine : 0.f;
+              if (n_other > 0) x = fmaf(__uint_as_float(ob[i]), w_other, x);
+              v[i] = x;
+            }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 w;
-              w.x = pack2(__uint_as_float(orr[i * 8 + 0]) * inv, __uint_as_float(orr[i * 8 + 1]) * inv);
-              w.y = pack2(__uint_as_float(orr[i * 8 + 2]) * inv, __uint_as_float(orr[i * 8 + 3]) * inv);
-              w.z = pack2(__uint_as_float(orr[i * 8 + 4]) * inv, __uint_as_float(orr[i * 8 + 5]) * inv);
-              w.w = pack2(__uint_as_float(orr[i * 8 + 6]) * inv, __uint_as_float(orr[i * 8 + 7]) * inv);
+              w.x = pack2(v[i * 8 + 0], v[i * 8 + 1]);
+              w.y = pack2(v[i * 8 + 2], v[i * 8 + 3]);
+              w.z = pack2(v[i * 8 + 4], v[i * 8 + 5]);
+              w.w = pack2(v[i * 8 + 6], v[i * 8 + 7]);
               *reinterpret_cast<uint4*>(orow + part * 32 + i * 8) = w;
             }
           }
         }
       }
     }
-    if (ok && half == 0 && p.lse2 && tok < p.L)
-      p.lse2[((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)] = m_run + log2f(l_tot);
+    if (ok && wg == 0 && p.lse2 && tok < p.L)
+      p.lse2[((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)] = m_tot + log2f(l_tot);
   } else {
     // ================================ pooled-score reducer =====================================
-    // thread = (key lane, half of the tile's 128 (query, head) rows); the halves are added through
-    // shared memory and half 0 stores
-    const int half = warp >> 2;
+    // warpgroup w owns the key blocks j = w, w+2, ...; thread = key lane, sums over the tile's 128
+    // (query, head) rows, i.e. over the 128 columns of S^T
+    const int wg = warp >> 2;
     const int key_lane = (warp & 3) * 32 + lane;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t ts = t_s0 + wg * 128 + lane_sel;
     float* prow = p.pooled + (((int64_t)b * p.G + g) * p.T + t) * p.pooled_stride;
-    for (int j = 0; j < nb; ++j) {
-      if (!mbar_wait(&bar_sfull[j & 1], (j >> 1) & 1, &give_up, 41)) break;
+    int it = 0;
+    for (int j = wg; j < nb; j += 2, ++it) {
+      if (!mbar_wait(&bar_sfull[wg], it & 1, &give_up, 41)) break;
       tc_fence_after();
-      const uint32_t ts = t_s0 + (j & 1) * 128 + lane_sel + half * 64;
-      float acc = 0.f;
-      uint32_t sr[2][32];
-      tmem_ld32(ts, sr[0]);
-      tmem_ld32(ts + 32, sr[1]);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&bar_pready[j & 1]);                 // S^T block is in registers: the buffer is free
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-      for (int part = 0; part < 2; ++part)
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sa[32], sb[32];
+        tmem_ld32(ts + half * 64, sa);
+        tmem_ld32(ts + half * 64 + 32, sb);
+        tmem_wait_ld();
+        if (half == 1) {                                 // S^T block is in registers: the buffer is free
+          tc_fence_before();
+          mbar_arrive(&bar_pready[wg]);
+        }
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          acc += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -lse_s[half * 64 + part * 32 + i]));
-      if (half == 1) xchg[j & 1][0][key_lane] = acc;
-      mbar_arrive(&bar_x[j & 1]);
-      if (!mbar_wait(&bar_x[j & 1], (j >> 1) & 1, &give_up, 42)) break;
+        for (int i = 0; i < 32; i += 2) {
+          a0 += ex2(fmaf(__uint_as_float(sa[i]), p.scale2, -lse_s[half * 64 + i]));
+          a1 += ex2(fmaf(__uint_as_float(sa[i + 1]), p.scale2, -lse_s[half * 64 + i + 1]));
+          a2 += ex2(fmaf(__uint_as_float(sb[i]), p.scale2, -lse_s[half * 64 + 32 + i]));
+          a3 += ex2(fmaf(__uint_as_float(sb[i + 1]), p.scale2, -lse_s[half * 64 + 32 + i + 1]));
+        }
+      }
       const int key = j * 128 + key_lane;
-      if (half == 0 && key < tile_start) prow[key] = acc + xchg[j & 1][0][key_lane];
+      if (key < tile_start) prow[key] = (a0 + a1) + (a2 + a3);
     }
   }
 
