@@ -95,6 +95,7 @@ struct PfShared {
   int give_up;
   float xchg[2][2][128];                               // [block parity][column half][row]
 };
+constexpr float kRescaleLog2 = 8.0f;                   // see the softmax role
 constexpr int kPadAllowance = 768;                     // tiles need 1024-byte alignment
 
 template <int MODE>
@@ -202,12 +203,18 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
     cp_arrive_noinc(&bar_q);
     const __half* kb = p.k + (int64_t)b * p.k_sb + (int64_t)g * p.k_sh;
     const __half* vb = HAS_V ? p.v + (int64_t)b * p.v_sb + (int64_t)g * p.v_sh : nullptr;
-    for (int j = 0; j < nb; ++j) {
+    // key position of row (pw*32 + lane) of block j; index loads run two blocks ahead of their use
+    auto load_key = [&](int j) -> int {
       const int s = j * 128 + pw * 32 + lane;
-      int key;
-      if (GATHER) key = s < count ? __ldg(idx_row + s) : tile_start + (s - count);
-      else key = s;
-      if (s >= total) key = 0;
+      if (j >= nb || s >= total) return 0;
+      if (GATHER) return s < count ? __ldg(idx_row + s) : tile_start + (s - count);
+      return s;
+    };
+    int key_a = load_key(0), key_b = load_key(1);
+    for (int j = 0; j < nb; ++j) {
+      int key = key_a;
+      key_a = key_b;
+      key_b = load_key(j + 2);
       key = max(0, min(key, p.L - 1));
       const int64_t offk = (int64_t)key * p.k_st;
       const int64_t offv = HAS_V ? (int64_t)key * p.v_st : 0;
@@ -333,8 +340,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
           mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
         }
       }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      const float m_new = fmaxf(m_run, mx * p.scale2);
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale2;
+      // The reference point of the exponentials only moves when the row maximum has grown by more
+      // than 2^kRescaleLog2: probabilities then stay below 2^kRescaleLog2 (exact in fp32, harmless in
+      // fp16), and the O accumulator is rescaled only on those rare blocks.  lse2 = m + log2(l) holds
+      // for any reference point m.
+      const float m_new = (mx > m_run + kRescaleLog2) ? mx : m_run;
       const float alpha = ex2(m_run - m_new);
       // ---- pass 2: exponentials, row sum, P -----------------------------------------------------
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
@@ -387,11 +398,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
       l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
       m_run = m_new;
       if (HAS_V) {
-        if (it > 0) {
+        if (it > 0 && !__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
+          // the previous P.V of this stream must have landed in O before O is rescaled
           ok = mbar_wait(&bar_odone[wg], (it - 1) & 1, &give_up, 32);
           if (!ok) break;
           tc_fence_after();
-          if (!__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
+          {
 #pragma unroll 1
             for (int part = 0; part < 4; ++part) {
               uint32_t orr[32];
