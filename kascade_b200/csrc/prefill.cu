@@ -18,7 +18,8 @@
 // tensor-memory lane and one half of the 128 columns of a block, so that two warps per SM
 // sub-partition overlap their tcgen05.ld / ex2 / FMA chains; warps 8-11 producers (cp.async 16-byte
 // chunks, 16 lanes per 256-byte row, written in the 128-byte-swizzled operand layout of umma.cuh);
-// warp 12 issues the MMAs from one thread.
+// warp 12 issues the MMAs from one thread (warps 13-15 complete its warpgroup and idle, so that
+// setmaxnreg can move registers from the producer / MMA warpgroups to the softmax warpgroups).
 // Hand-offs are mbarriers; every wait is bounded (umma::mbar_wait) and a kernel that gives up
 // records a code in the device status word, drains its copies, frees its tensor memory and returns.
 //
@@ -36,7 +37,7 @@ enum PrefillMode { kDenseAttn = 0, kDenseLse = 1, kSparse = 2, kPool = 3 };
 constexpr int kSoftmaxThreads = 256;             // warps 0-7
 constexpr int kProducerWarp0 = 8;                // warps 8-11
 constexpr int kMmaWarp = 12;
-constexpr int kPfThreads = 13 * 32;
+constexpr int kPfThreads = 16 * 32;               // warps 13-15 only pad the last warpgroup
 constexpr int kStageBytes = 128 * kD * 2;     // one 128-row operand tile (32 KB)
 constexpr int kNKMax = 6;                     // K ring: 3 stages with a V ring, 6 without
 constexpr int kNV = 3;
@@ -184,8 +185,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
   const uint32_t tmem = tmem_sh;
   const uint32_t t_s0 = tmem, t_o = tmem + 256;
 
+  // Register budget per SM sub-partition (512 per thread slot, warps w, w+4, w+8, w+12 share one):
+  // 2 x 200 (softmax) + 56 (producer) + 40 (MMA issuer / padding warp) = 496.
   if (warp >= kProducerWarp0 && warp < kMmaWarp) {
     // ================================ producers ================================================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
     // Every thread copies with cp.async and lets the hardware arrive on the stage's "full" barrier when
     // its copies have landed (cp.async.mbarrier.arrive.noinc): the producers never wait for data, they
     // run ahead as far as the rings allow.  The MMA warp orders the landed bytes against the tensor
@@ -244,9 +248,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
       }
     }
     cp_wait_all();                                       // nothing of this CTA is in flight at teardown
-  } else if (warp == kMmaWarp) {
-    // ================================ MMA issuer ===============================================
-    if (lane == 0) {
+  } else if (warp >= kMmaWarp) {
+    // ================================ MMA issuer (warp 12; warps 13-15 idle) ====================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
+    if (warp == kMmaWarp && lane == 0) {
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
       constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
       bool ok = mbar_wait(&bar_q, 0, &give_up, 21);
@@ -304,6 +309,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
     // own S buffer, its own running (max, sum) per row and (with V) its own O accumulator, so the
     // tcgen05.ld / max / ex2 phases of one stream overlap those of the other and nothing is exchanged
     // per block.  The streams are merged like split-K partials in the epilogue.
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;\n");
     const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane, q_local = row >> 2;
     const int tok = tile_start + q_local;
@@ -320,24 +326,31 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
       tc_fence_after();
       const int c0 = j * 128 - off;                     // key position (inside the tile) of column 0
       const bool need_mask = (c0 + 127) > 0;            // only the last block(s) of a tile
-      // ---- pass 1: row maximum ----------------------------------------------------------------
+      // the whole S row (128 fp32) comes into registers with one round trip to tensor memory
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int part = 0; part < 4; ++part) tmem_ld32(ts + part * 32, sr[part]);
+      tmem_wait_ld();
+      if (!HAS_V) {                                      // S is in registers: the buffer may be refilled
+        tc_fence_before();
+        mbar_arrive(&bar_pready[wg]);
+      }
+      if (need_mask) {
+#pragma unroll
+        for (int part = 0; part < 4; ++part)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if ((c0 + part * 32 + i) > q_local) sr[part][i] = 0xFF800000u;     // -inf
+      }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
       for (int part = 0; part < 4; ++part) {
-        uint32_t sr[32];
-        tmem_ld32(ts + part * 32, sr);
-        tmem_wait_ld();
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if ((c0 + part * 32 + i) > q_local) sr[i] = 0xFF800000u;     // -inf
-        }
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
-          mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
+          mx0 = fmaxf(mx0, __uint_as_float(sr[part][i]));
+          mx1 = fmaxf(mx1, __uint_as_float(sr[part][i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sr[part][i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(sr[part][i + 3]));
         }
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale2;
@@ -347,53 +360,34 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
       // for any reference point m.
       const float m_new = (mx > m_run + kRescaleLog2) ? mx : m_run;
       const float alpha = ex2(m_run - m_new);
-      // ---- pass 2: exponentials, row sum, P -----------------------------------------------------
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      if (HAS_V) {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sa[32], sb[32];
-        tmem_ld32(ts + half * 64, sa);
-        tmem_ld32(ts + half * 64 + 32, sb);
-        tmem_wait_ld();
-        if (!HAS_V && half == 1) {                       // S is in registers: the buffer may be refilled
-          tc_fence_before();
-          mbar_arrive(&bar_pready[wg]);
-        }
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if ((c0 + half * 64 + i) > q_local) sa[i] = 0xFF800000u;
-            if ((c0 + half * 64 + 32 + i) > q_local) sb[i] = 0xFF800000u;
-          }
-        }
-        if (HAS_V) {
+        for (int half = 0; half < 2; ++half) {
           uint32_t pr[32];
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            float a0 = ex2(fmaf(__uint_as_float(sa[2 * i]), p.scale2, -m_new));
-            float a1 = ex2(fmaf(__uint_as_float(sa[2 * i + 1]), p.scale2, -m_new));
-            float a2 = ex2(fmaf(__uint_as_float(sa[2 * i + 2]), p.scale2, -m_new));
-            float a3 = ex2(fmaf(__uint_as_float(sa[2 * i + 3]), p.scale2, -m_new));
-            float b0 = ex2(fmaf(__uint_as_float(sb[2 * i]), p.scale2, -m_new));
-            float b1 = ex2(fmaf(__uint_as_float(sb[2 * i + 1]), p.scale2, -m_new));
-            float b2 = ex2(fmaf(__uint_as_float(sb[2 * i + 2]), p.scale2, -m_new));
-            float b3 = ex2(fmaf(__uint_as_float(sb[2 * i + 3]), p.scale2, -m_new));
-            s0 += a0 + a1; s1 += a2 + a3; s2 += b0 + b1; s3 += b2 + b3;
+          for (int i = 0; i < 32; i += 2) {              // P column i of this half = keys 2i, 2i+1
+            const int c = half * 64 + i * 2;
+            float a0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale2, -m_new));
+            float a1 = ex2(fmaf(__uint_as_float(sr[c >> 5][(c & 31) + 1]), p.scale2, -m_new));
+            float a2 = ex2(fmaf(__uint_as_float(sr[c >> 5][(c & 31) + 2]), p.scale2, -m_new));
+            float a3 = ex2(fmaf(__uint_as_float(sr[c >> 5][(c & 31) + 3]), p.scale2, -m_new));
+            s0 += a0; s1 += a1; s2 += a2; s3 += a3;
             pr[i] = pack2(a0, a1);
             pr[i + 1] = pack2(a2, a3);
-            pr[16 + i] = pack2(b0, b1);
-            pr[16 + i + 1] = pack2(b2, b3);
           }
           tmem_st32(ts + half * 32, pr);                 // P columns [half*32, +32) = keys [half*64, +64)
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            s0 += ex2(fmaf(__uint_as_float(sa[i]), p.scale2, -m_new));
-            s1 += ex2(fmaf(__uint_as_float(sa[i + 1]), p.scale2, -m_new));
-            s2 += ex2(fmaf(__uint_as_float(sb[i]), p.scale2, -m_new));
-            s3 += ex2(fmaf(__uint_as_float(sb[i + 1]), p.scale2, -m_new));
-          }
         }
+      } else {
+#pragma unroll
+        for (int part = 0; part < 4; ++part)
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            s0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -m_new));
+            s1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -m_new));
+            s2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -m_new));
+            s3 += ex2(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -m_new));
+          }
       }
       l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
       m_run = m_new;
@@ -481,6 +475,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
     // ================================ pooled-score reducer =====================================
     // warpgroup w owns the key blocks j = w, w+2, ...; thread = key lane, sums over the tile's 128
     // (query, head) rows, i.e. over the 128 columns of S^T
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;\n");
     const int wg = warp >> 2;
     const int key_lane = (warp & 3) * 32 + lane;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
@@ -491,24 +486,21 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
       if (!mbar_wait(&bar_sfull[wg], it & 1, &give_up, 41)) break;
       tc_fence_after();
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      uint32_t sr[4][32];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sa[32], sb[32];
-        tmem_ld32(ts + half * 64, sa);
-        tmem_ld32(ts + half * 64 + 32, sb);
-        tmem_wait_ld();
-        if (half == 1) {                                 // S^T block is in registers: the buffer is free
-          tc_fence_before();
-          mbar_arrive(&bar_pready[wg]);
-        }
+      for (int part = 0; part < 4; ++part) tmem_ld32(ts + part * 32, sr[part]);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&bar_pready[wg]);                      // S^T block is in registers: the buffer is free
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          a0 += ex2(fmaf(__uint_as_float(sa[i]), p.scale2, -lse_s[half * 64 + i]));
-          a1 += ex2(fmaf(__uint_as_float(sa[i + 1]), p.scale2, -lse_s[half * 64 + i + 1]));
-          a2 += ex2(fmaf(__uint_as_float(sb[i]), p.scale2, -lse_s[half * 64 + 32 + i]));
-          a3 += ex2(fmaf(__uint_as_float(sb[i + 1]), p.scale2, -lse_s[half * 64 + 32 + i + 1]));
+      for (int part = 0; part < 4; ++part)
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          a0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -lse_s[part * 32 + i]));
+          a1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -lse_s[part * 32 + i + 1]));
+          a2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -lse_s[part * 32 + i + 2]));
+          a3 += ex2(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -lse_s[part * 32 + i + 3]));
         }
-      }
       const int key = j * 128 + key_lane;
       if (key < tile_start) prow[key] = (a0 + a1) + (a2 + a3);
     }
