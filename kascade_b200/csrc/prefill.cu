@@ -1,6 +1,6 @@
 // Tile prefill kernels on the sm_100a tensor-core path (tcgen05.mma, accumulators in tensor memory).
 //
-// One CTA owns one query tile: 32 consecutive queries x the 4 query heads of one KV head = 128
+// A work item is one query tile: 32 consecutive queries x the 4 query heads of one KV head = 128
 // rows (row = 4 * query_in_tile + head), the M dimension of every MMA.  Keys arrive in blocks of
 // 128 rows.  The same kernel body serves four modes:
 //
@@ -14,19 +14,26 @@
 //               sums exp2(s * scale2 - lse2[row]) over the 128 rows of the tile for its key
 //               (replaces `aggregate`, recompute_kascade_gqa_prefill.py:171-222)
 //
-// Warp roles (416 threads): warps 0-7 softmax / reducer — two warpgroups, each thread owns one
-// tensor-memory lane and one half of the 128 columns of a block, so that two warps per SM
-// sub-partition overlap their tcgen05.ld / ex2 / FMA chains; warps 8-11 producers (cp.async 16-byte
-// chunks, 16 lanes per 256-byte row, written in the 128-byte-swizzled operand layout of umma.cuh);
-// warp 12 issues the MMAs from one thread (warps 13-15 complete its warpgroup and idle, so that
-// setmaxnreg can move registers from the producer / MMA warpgroups to the softmax warpgroups).
+// The kernels are persistent: one CTA per SM walks the list of tiles (ordered by descending cost,
+// handed out boustrophedon-wise), ring stages and barrier phases keep counting across tiles, so the
+// next tile's Q/K/V are already on their way while the current tile is being finished.
+//
+// Warp roles.  Warps 0-7: softmax / reducer, two warpgroups, warpgroup w owns every key block
+// j = w (mod 2) of a tile with its own S buffer and O accumulator (thread = tensor-memory lane = row).
+// Dense modes (384 threads): warp 8 lane 0 issues TMA box copies (4-D tiled tensor maps, 128-byte
+// swizzle, no multicast), warp 9 lane 0 issues the MMAs, warps 10-11 only complete the warpgroup.
+// Sparse mode (512 threads): warps 8-11 gather the selected K/V rows with cp.async (16-byte chunks,
+// 16 lanes per 256-byte row, written directly in the 128-byte-swizzled operand layout of umma.cuh),
+// warp 12 lane 0 issues the MMAs, warps 13-15 complete its warpgroup.  setmaxnreg moves registers from
+// the producer / MMA warpgroups to the softmax warpgroups.
 // Hand-offs are mbarriers; every wait is bounded (umma::mbar_wait) and a kernel that gives up
 // records a code in the device status word, drains its copies, frees its tensor memory and returns.
 //
-// Tensor memory (512 columns): S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512): key blocks of even
-// and odd index form two independent streams (own S buffer, own O accumulator, own softmax warpgroup).
-// P (fp16) overwrites the first 64 columns of the S buffer it was computed from and is the A operand
-// of the P.V product.
+// Tensor memory (512 columns): S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512).  P (fp16)
+// overwrites the first 64 columns of the S buffer it was computed from and is the A operand of P.V.
+#include <cuda.h>
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "umma.cuh"
 
@@ -34,13 +41,12 @@ namespace kb200 {
 
 enum PrefillMode { kDenseAttn = 0, kDenseLse = 1, kSparse = 2, kPool = 3 };
 
-constexpr int kSoftmaxThreads = 256;             // warps 0-7
-constexpr int kProducerWarp0 = 8;                // warps 8-11
-constexpr int kMmaWarp = 12;
-constexpr int kPfThreads = 16 * 32;               // warps 13-15 only pad the last warpgroup
+constexpr int kSoftmaxThreads = 256;          // warps 0-7
 constexpr int kStageBytes = 128 * kD * 2;     // one 128-row operand tile (32 KB)
 constexpr int kNKMax = 6;                     // K ring: 3 stages with a V ring, 6 without
 constexpr int kNV = 3;
+constexpr float kRescaleLog2 = 8.0f;          // see the softmax role
+constexpr int kPadAllowance = 768;            // tiles need 1024-byte alignment
 
 __device__ int g_status_word = 0;
 
@@ -77,11 +83,6 @@ __device__ __forceinline__ void cp_arrive_noinc(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(umma::smem_addr(bar)) : "memory");
 }
 __device__ __forceinline__ void cp_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
-}
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -90,49 +91,83 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 // Barriers and small exchange buffers; lives in dynamic shared memory behind the operand tiles so that
 // the 7 x 32 KB tiles, the alignment padding and this block together stay inside the 227 KB limit.
 struct PfShared {
-  uint64_t bar_q, bar_kfull[kNKMax], bar_kempty[kNKMax], bar_vfull[kNV], bar_vempty[kNV];
-  uint64_t bar_sfull[2], bar_pready[2], bar_odone[2], bar_x;
+  uint64_t bar_q, bar_qempty, bar_kfull[kNKMax], bar_kempty[kNKMax], bar_vfull[kNV], bar_vempty[kNV];
+  uint64_t bar_sfull[2], bar_pready[2], bar_odone[2], bar_x, bar_ofree, bar_lse[2];
   uint32_t tmem;
   int give_up;
-  float xchg[2][2][128];                               // [block parity][column half][row]
+  union {
+    float xchg[2][2][128];                             // softmax modes: [m | l][warpgroup][row]
+    float lse[2][2][128];                              // pool mode: lse2 of the tile's rows [warpgroup][tile parity]
+  };
 };
-constexpr float kRescaleLog2 = 8.0f;                   // see the softmax role
-constexpr int kPadAllowance = 768;                     // tiles need 1024-byte alignment
+static_assert(sizeof(PfShared) <= 2304, "PfShared grew");
+constexpr int kSmemAttn = kStageBytes * (1 + 3 + kNV) + kPadAllowance + 2304;   // = 232448, the sm_100 limit
+constexpr int kSmemNoV = kStageBytes * (1 + kNKMax) + kPadAllowance + 2304;
+
+// One work item = one query tile of one KV head of one sequence.
+struct TileItem {
+  int b, g, t, tile_start, rows_valid, count, total, nb;
+  const int32_t* idx_row;
+};
 
 template <int MODE>
-__global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const PrefillParams p) {
+__device__ __forceinline__ TileItem decode_item(const PrefillParams& p, int item) {
+  TileItem it;
+  // items are ordered by descending tile index over all (sequence, KV head) pairs, i.e. by
+  // descending cost, so the boustrophedon hand-out gives every CTA the same amount of work
+  const int nbg = p.B * p.G;
+  const int r = item / nbg, bg = item - r * nbg;
+  it.t = p.T - 1 - r;
+  it.b = bg / p.G;
+  it.g = bg - it.b * p.G;
+  it.tile_start = it.t * kTile;
+  it.rows_valid = min(kTile, p.L - it.tile_start);
+  it.count = 0;
+  it.idx_row = nullptr;
+  if (MODE == kSparse) {
+    const int src_g = p.head_map ? p.head_map[it.g] : it.g;
+    const int64_t row = ((int64_t)it.b * p.G_idx + src_g) * p.T + it.t;
+    const int c = p.tile_count[row];
+    it.count = max(0, min(c, (int)min((int64_t)it.tile_start, p.idx_stride)));
+    it.idx_row = p.tile_idx + row * p.idx_stride;
+    it.total = it.count + it.rows_valid;
+  } else if (MODE == kPool) {
+    it.total = it.tile_start;                          // keys strictly before the tile
+  } else {
+    it.total = it.tile_start + it.rows_valid;          // causal: keys up to the tile's last query
+  }
+  it.nb = (it.total + 127) >> 7;
+  return it;
+}
+
+template <int MODE>
+struct PfCfg {
+  static constexpr bool kHasV = MODE == kDenseAttn || MODE == kSparse;
+  static constexpr bool kIsPool = MODE == kPool;
+  static constexpr bool kGather = MODE == kSparse;
+  static constexpr int kThreads = kGather ? 512 : 384;
+  static constexpr int kNK = kHasV ? 3 : kNKMax;
+  static constexpr int kProducerArrivals = kGather ? 128 : 1;
+  static constexpr int kProducerWarp0 = 8;
+  static constexpr int kMmaWarp = kGather ? 12 : 9;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(PfCfg<MODE>::kThreads, 1)
+tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_constant__ CUtensorMap tm_q,
+                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
   using namespace umma;
-  constexpr bool HAS_V = MODE == kDenseAttn || MODE == kSparse;
-  constexpr bool POOL = MODE == kPool;
-  constexpr bool GATHER = MODE == kSparse;
-  constexpr int kNK = HAS_V ? 3 : kNKMax;             // K ring depth
+  using Cfg = PfCfg<MODE>;
+  constexpr bool HAS_V = Cfg::kHasV;
+  constexpr bool POOL = Cfg::kIsPool;
+  constexpr bool GATHER = Cfg::kGather;
+  constexpr int kNK = Cfg::kNK;
+  constexpr int kMmaWarp = Cfg::kMmaWarp;
 
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int t = (int)gridDim.x - 1 - (int)blockIdx.x;   // long tiles first
-  const int g = blockIdx.y, b = blockIdx.z;
-  const int tile_start = t * kTile;
-  const int rows_valid = min(kTile, p.L - tile_start);
-
-  int count = 0, total;
-  const int32_t* idx_row = nullptr;
-  if (GATHER) {
-    const int src_g = p.head_map ? p.head_map[g] : g;
-    const int64_t r = ((int64_t)b * p.G_idx + src_g) * p.T + t;
-    count = p.tile_count[r];
-    count = max(0, min(count, (int)min((int64_t)tile_start, p.idx_stride)));
-    idx_row = p.tile_idx + r * p.idx_stride;
-    total = count + rows_valid;
-  } else if (POOL) {
-    total = tile_start;
-  } else {
-    total = tile_start + rows_valid;
-  }
-  const int nb = (total + 127) >> 7;
-  if (nb == 0) return;                                   // pool pass of tile 0: no earlier keys
   // an earlier CTA or kernel gave up a bounded wait: do not queue up more waits behind it
   if (*reinterpret_cast<volatile int*>(&g_status_word) != 0) return;
-
   const uint32_t pad = (1024u - (smem_addr(smem_raw) & 1023u)) & 1023u;
   if (pad > (uint32_t)kPadAllowance) {                   // never seen; refuse rather than overrun
     if (tid == 0) atomicCAS(&g_status_word, 0, 90);
@@ -141,7 +176,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
   uint8_t* smem = smem_raw + pad;
   constexpr int kTiles = 1 + kNK + (HAS_V ? kNV : 0);
   PfShared& sh = *reinterpret_cast<PfShared*>(smem + kTiles * kStageBytes);
-  uint64_t& bar_q = sh.bar_q;
   uint64_t* bar_kfull = sh.bar_kfull;
   uint64_t* bar_kempty = sh.bar_kempty;
   uint64_t* bar_vfull = sh.bar_vfull;
@@ -149,255 +183,349 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
   uint64_t* bar_sfull = sh.bar_sfull;
   uint64_t* bar_pready = sh.bar_pready;
   uint64_t* bar_odone = sh.bar_odone;
-  uint64_t& bar_x = sh.bar_x;
-  uint32_t& tmem_sh = sh.tmem;
   int& give_up = sh.give_up;
-  float (&xchg)[2][2][128] = sh.xchg;
-  float* lse_s = sh.xchg[0][1];                          // kPool only: that mode exchanges through xchg[.][0]
   const uint32_t q_s = smem_addr(smem);
   const uint32_t k_s = q_s + kStageBytes;
   const uint32_t v_s = k_s + kNK * kStageBytes;
 
   if (tid == 0) {
-    mbar_init(&bar_q, 128);
-    for (int i = 0; i < kNK; ++i) { mbar_init(&bar_kfull[i], 128); mbar_init(&bar_kempty[i], 1); }
-    for (int i = 0; i < kNV; ++i) { mbar_init(&bar_vfull[i], 128); mbar_init(&bar_vempty[i], 1); }
+    mbar_init(&sh.bar_q, Cfg::kProducerArrivals);
+    mbar_init(&sh.bar_qempty, 1);
+    for (int i = 0; i < kNK; ++i) { mbar_init(&bar_kfull[i], Cfg::kProducerArrivals); mbar_init(&bar_kempty[i], 1); }
+    for (int i = 0; i < kNV; ++i) { mbar_init(&bar_vfull[i], Cfg::kProducerArrivals); mbar_init(&bar_vempty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_sfull[i], 1);
       mbar_init(&bar_pready[i], 128);
       mbar_init(&bar_odone[i], 1);
+      mbar_init(&sh.bar_lse[i], 128);
     }
-    mbar_init(&bar_x, kSoftmaxThreads);
+    mbar_init(&sh.bar_x, kSoftmaxThreads);
+    mbar_init(&sh.bar_ofree, kSoftmaxThreads);
     mbar_fence_init();
     give_up = 0;
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(&tmem_sh, 512);
+    tmem_alloc(&sh.tmem, 512);
     tmem_relinquish();
-  }
-  if (POOL && tid < 128) {
-    const int tok = tile_start + (tid >> 2);
-    lse_s[tid] = tok < p.L ? p.lse2_in[((int64_t)b * p.L + tok) * p.H + g * kHg + (tid & 3)] : INFINITY;
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = tmem_sh;
+  const uint32_t tmem = sh.tmem;
   const uint32_t t_s0 = tmem, t_o = tmem + 256;
 
-  // Register budget per SM sub-partition (512 per thread slot, warps w, w+4, w+8, w+12 share one):
-  // 2 x 200 (softmax) + 56 (producer) + 40 (MMA issuer / padding warp) = 496.
-  if (warp >= kProducerWarp0 && warp < kMmaWarp) {
-    // ================================ producers ================================================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
-    // Every thread copies with cp.async and lets the hardware arrive on the stage's "full" barrier when
-    // its copies have landed (cp.async.mbarrier.arrive.noinc): the producers never wait for data, they
-    // run ahead as far as the rings allow.  The MMA warp orders the landed bytes against the tensor
-    // core's reads with a proxy fence after its barrier wait.
-    const int pw = warp - kProducerWarp0, ptid = tid - kProducerWarp0 * 32;
-    const __half* qb = p.q + (int64_t)b * p.q_sb;
+  const int n_items = p.B * p.G * p.T;
+  const int P = (int)gridDim.x;
+  const int n_rounds = (n_items + P - 1) / P;
+  auto item_of = [&](int k) -> int { return k * P + ((k & 1) ? (P - 1 - (int)blockIdx.x) : (int)blockIdx.x); };
+
+  // ================================ producer: gathered rows by cp.async (sparse mode) ===========
+  // Every thread copies with cp.async and lets the hardware arrive on the stage's "full" barrier when
+  // its copies have landed (cp.async.mbarrier.arrive.noinc): the producers never wait for data, they
+  // run ahead as far as the rings allow.  The MMA warp orders the landed bytes against the tensor
+  // core's reads with a proxy fence after its barrier wait.
+  auto producer_gather = [&]() {
+    const int pw = warp - Cfg::kProducerWarp0, ptid = tid - Cfg::kProducerWarp0 * 32;
+    int kc = 0, vc = 0, qn = 0;                          // blocks put into the K / V rings, Q tiles loaded
+    bool ok = true;
+    for (int k = 0; k < n_rounds && ok; ++k) {
+      const int item = item_of(k);
+      if (item >= n_items) continue;
+      const TileItem it = decode_item<MODE>(p, item);
+      if (it.nb == 0) continue;
+      // the Q buffer is free once the last Q.K^T of the previous tile has completed
+      ok = mbar_wait(&sh.bar_qempty, (qn & 1) ^ 1, &give_up, 13);
+      if (!ok) break;
+      const __half* qb = p.q + (int64_t)it.b * p.q_sb;
 #pragma unroll 4
-    for (int it = 0; it < 16; ++it) {
-      const int id = it * 128 + ptid, row = id >> 4, c = id & 15;
-      const int tok = tile_start + (row >> 2), head = g * kHg + (row & 3);
-      const bool in = tok < p.L;                         // rows past the prompt are zero-filled
-      cp16_zfill(q_s + tile_off(row, c, 128),
-                 qb + (int64_t)(in ? tok : 0) * p.q_st + (int64_t)head * p.q_sh + c * 8, in ? 16u : 0u);
-    }
-    cp_arrive_noinc(&bar_q);
-    const __half* kb = p.k + (int64_t)b * p.k_sb + (int64_t)g * p.k_sh;
-    const __half* vb = HAS_V ? p.v + (int64_t)b * p.v_sb + (int64_t)g * p.v_sh : nullptr;
-    // key position of row (pw*32 + lane) of block j; index loads run two blocks ahead of their use
-    auto load_key = [&](int j) -> int {
-      const int s = j * 128 + pw * 32 + lane;
-      if (j >= nb || s >= total) return 0;
-      if (GATHER) return s < count ? __ldg(idx_row + s) : tile_start + (s - count);
-      return s;
-    };
-    int key_a = load_key(0), key_b = load_key(1);
-    for (int j = 0; j < nb; ++j) {
-      int key = key_a;
-      key_a = key_b;
-      key_b = load_key(j + 2);
-      key = max(0, min(key, p.L - 1));
-      const int64_t offk = (int64_t)key * p.k_st;
-      const int64_t offv = HAS_V ? (int64_t)key * p.v_st : 0;
-      if (!mbar_wait(&bar_kempty[j % kNK], ((j / kNK) & 1) ^ 1, &give_up, 11)) break;
-      {
-        const uint32_t dst = k_s + (j % kNK) * kStageBytes;
-        const int c = lane & 15;
-#pragma unroll 4
-        for (int it = 0; it < 16; ++it) {
-          const int rw = it * 2 + (lane >> 4);
-          const int64_t o = __shfl_sync(0xFFFFFFFFu, offk, rw);
-          cp16(dst + tile_off(pw * 32 + rw, c, 128), kb + o + c * 8);
-        }
-        cp_arrive_noinc(&bar_kfull[j % kNK]);
+      for (int i = 0; i < 16; ++i) {
+        const int id = i * 128 + ptid, row = id >> 4, c = id & 15;
+        const int tok = it.tile_start + (row >> 2), head = it.g * kHg + (row & 3);
+        const bool in = tok < p.L;                       // rows past the prompt are zero-filled
+        cp16_zfill(q_s + tile_off(row, c, 128),
+                   qb + (int64_t)(in ? tok : 0) * p.q_st + (int64_t)head * p.q_sh + c * 8, in ? 16u : 0u);
       }
-      if (HAS_V) {
-        if (!mbar_wait(&bar_vempty[j % kNV], ((j / kNV) & 1) ^ 1, &give_up, 12)) break;
-        const uint32_t dst = v_s + (j % kNV) * kStageBytes;
+      cp_arrive_noinc(&sh.bar_q);
+      ++qn;
+      const __half* kb = p.k + (int64_t)it.b * p.k_sb + (int64_t)it.g * p.k_sh;
+      const __half* vb = p.v + (int64_t)it.b * p.v_sb + (int64_t)it.g * p.v_sh;
+      // key position of row (pw*32 + lane) of block j; index loads run two blocks ahead of their use
+      auto load_key = [&](int j) -> int {
+        const int s = j * 128 + pw * 32 + lane;
+        if (j >= it.nb || s >= it.total) return 0;
+        return s < it.count ? __ldg(it.idx_row + s) : it.tile_start + (s - it.count);
+      };
+      int key_a = load_key(0), key_b = load_key(1);
+      for (int j = 0; j < it.nb; ++j) {
+        int key = key_a;
+        key_a = key_b;
+        key_b = load_key(j + 2);
+        key = max(0, min(key, p.L - 1));
+        const int64_t offk = (int64_t)key * p.k_st, offv = (int64_t)key * p.v_st;
         const int c = lane & 15;
+        ok = mbar_wait(&bar_kempty[kc % kNK], ((kc / kNK) & 1) ^ 1, &give_up, 11);
+        if (!ok) break;
+        {
+          const uint32_t dst = k_s + (kc % kNK) * kStageBytes;
 #pragma unroll 4
-        for (int it = 0; it < 16; ++it) {
-          const int rw = it * 2 + (lane >> 4);
-          const int64_t o = __shfl_sync(0xFFFFFFFFu, offv, rw);
-          cp16(dst + tile_off(pw * 32 + rw, c, 128), vb + o + c * 8);
+          for (int i = 0; i < 16; ++i) {
+            const int rw = i * 2 + (lane >> 4);
+            const int64_t o = __shfl_sync(0xFFFFFFFFu, offk, rw);
+            cp16(dst + tile_off(pw * 32 + rw, c, 128), kb + o + c * 8);
+          }
+          cp_arrive_noinc(&bar_kfull[kc % kNK]);
+          ++kc;
         }
-        cp_arrive_noinc(&bar_vfull[j % kNV]);
+        ok = mbar_wait(&bar_vempty[vc % kNV], ((vc / kNV) & 1) ^ 1, &give_up, 12);
+        if (!ok) break;
+        {
+          const uint32_t dst = v_s + (vc % kNV) * kStageBytes;
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int rw = i * 2 + (lane >> 4);
+            const int64_t o = __shfl_sync(0xFFFFFFFFu, offv, rw);
+            cp16(dst + tile_off(pw * 32 + rw, c, 128), vb + o + c * 8);
+          }
+          cp_arrive_noinc(&bar_vfull[vc % kNV]);
+          ++vc;
+        }
       }
     }
     cp_wait_all();                                       // nothing of this CTA is in flight at teardown
-  } else if (warp >= kMmaWarp) {
-    // ================================ MMA issuer (warp 12; warps 13-15 idle) ====================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
-    if (warp == kMmaWarp && lane == 0) {
-      constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
-      constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
-      bool ok = mbar_wait(&bar_q, 0, &give_up, 21);
-      fence_proxy_async_smem();
-      auto issue_qk = [&](int j) -> bool {
-        if (!mbar_wait(&bar_kfull[j % kNK], (j / kNK) & 1, &give_up, 22)) return false;
-        fence_proxy_async_smem();                        // cp.async bytes -> visible to the tensor core
-        tc_fence_after();
-        const uint32_t ks_addr = k_s + (j % kNK) * kStageBytes;
-        const uint32_t d = t_s0 + (j & 1) * 128;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * (kStageBytes / 2) + (ks & 3) * 32;
-          const uint64_t dq = desc_kmajor(q_s + off), dk = desc_kmajor(ks_addr + off);
-          if (POOL) mma_ss(d, dk, dq, idesc_qk, ks > 0);     // S^T: lanes = keys
-          else mma_ss(d, dq, dk, idesc_qk, ks > 0);          // S: lanes = (query, head) rows
-        }
-        mma_commit(&bar_kempty[j % kNK]);
-        mma_commit(&bar_sfull[j & 1]);
-        return true;
-      };
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; j < nb && ok; ++j) {
-        if (j + 1 < nb) {
-          if (!HAS_V && j >= 1) {
-            ok = mbar_wait(&bar_pready[(j - 1) & 1], ((j - 1) >> 1) & 1, &give_up, 23);
-            if (!ok) break;
-          }
-          ok = issue_qk(j + 1);
-          if (!ok) break;
+  };
+
+  // ================================ producer: TMA box copies (dense modes), one thread ===========
+  // Tensor-map dimensions are (d, head, token, batch); a K/V tile is two boxes of 64 x 1 x 128 x 1 (the
+  // two 64-column halves of the operand tile), a Q tile two boxes of 64 x 4 x 32 x 1 whose rows come
+  // out as row = 4 * token + head.  Rows past the prompt are zero-filled by the copy engine.
+  auto producer_tma = [&]() {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    if (HAS_V) tma_prefetch_desc(&tm_v);
+    int kc = 0, vc = 0, qn = 0;
+    bool ok = true;
+    for (int k = 0; k < n_rounds && ok; ++k) {
+      const int item = item_of(k);
+      if (item >= n_items) continue;
+      const TileItem it = decode_item<MODE>(p, item);
+      if (it.nb == 0) continue;
+      ok = mbar_wait(&sh.bar_qempty, (qn & 1) ^ 1, &give_up, 13);
+      if (!ok) break;
+      mbar_arrive_expect_tx(&sh.bar_q, kStageBytes);
+      tma_load_4d(q_s, &tm_q, 0, it.g * kHg, it.tile_start, it.b, &sh.bar_q);
+      tma_load_4d(q_s + kStageBytes / 2, &tm_q, 64, it.g * kHg, it.tile_start, it.b, &sh.bar_q);
+      ++qn;
+      for (int j = 0; j < it.nb; ++j) {
+        ok = mbar_wait(&bar_kempty[kc % kNK], ((kc / kNK) & 1) ^ 1, &give_up, 11);
+        if (!ok) break;
+        {
+          const uint32_t dst = k_s + (kc % kNK) * kStageBytes;
+          uint64_t* bar = &bar_kfull[kc % kNK];
+          mbar_arrive_expect_tx(bar, kStageBytes);
+          tma_load_4d(dst, &tm_k, 0, it.g, j * 128, it.b, bar);
+          tma_load_4d(dst + kStageBytes / 2, &tm_k, 64, it.g, j * 128, it.b, bar);
+          ++kc;
         }
         if (HAS_V) {
-          ok = mbar_wait(&bar_pready[j & 1], (j >> 1) & 1, &give_up, 24);
+          ok = mbar_wait(&bar_vempty[vc % kNV], ((vc / kNV) & 1) ^ 1, &give_up, 12);
           if (!ok) break;
-          ok = mbar_wait(&bar_vfull[j % kNV], (j / kNV) & 1, &give_up, 25);
-          if (!ok) break;
-          fence_proxy_async_smem();
-          tc_fence_after();
-          const uint32_t vs_addr = v_s + (j % kNV) * kStageBytes;
-          const uint32_t a = t_s0 + (j & 1) * 128;
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            mma_ts(t_o + (j & 1) * 128, a + ks * 8, desc_mnmajor(vs_addr + ks * 2048, kStageBytes / 2), idesc_pv,
-                   (j > 1 || ks > 0) ? 1u : 0u);
-          }
-          mma_commit(&bar_vempty[j % kNV]);
-          mma_commit(&bar_odone[j & 1]);
+          const uint32_t dst = v_s + (vc % kNV) * kStageBytes;
+          uint64_t* bar = &bar_vfull[vc % kNV];
+          mbar_arrive_expect_tx(bar, kStageBytes);
+          tma_load_4d(dst, &tm_v, 0, it.g, j * 128, it.b, bar);
+          tma_load_4d(dst + kStageBytes / 2, &tm_v, 64, it.g, j * 128, it.b, bar);
+          ++vc;
         }
       }
     }
-    __syncwarp();
-  } else if (!POOL) {
-    // ================================ softmax ==================================================
-    // Two warpgroups, two independent streams: warpgroup w owns the key blocks j = w, w+2, ... with its
-    // own S buffer, its own running (max, sum) per row and (with V) its own O accumulator, so the
-    // tcgen05.ld / max / ex2 phases of one stream overlap those of the other and nothing is exchanged
-    // per block.  The streams are merged like split-K partials in the epilogue.
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;\n");
+  };
+
+  // ================================ MMA issuer (one thread) ======================================
+  auto mma_role = [&]() {
+    constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
+    constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
+    int kc = 0, vc = 0, qn = 0, tiles_done = 0;
+    int issued0 = 0, issued1 = 0;                      // Q.K^T blocks written into S buffer 0 / 1 so far
+    int released0 = 0, released1 = 0;                  // ... and how many of them the softmax side consumed
+    bool ok = true;
+    // S buffer w may be overwritten once every block issued into it has been consumed
+    auto wait_s_free = [&](int w) -> bool {
+      int& rel = w ? released1 : released0;
+      const int iss = w ? issued1 : issued0;
+      while (rel < iss) {
+        if (!mbar_wait(&bar_pready[w], rel & 1, &give_up, 23)) return false;
+        ++rel;
+      }
+      return true;
+    };
+    auto issue_qk = [&](int w) -> bool {
+      if (!wait_s_free(w)) return false;
+      if (!mbar_wait(&bar_kfull[kc % kNK], (kc / kNK) & 1, &give_up, 22)) return false;
+      if (GATHER) fence_proxy_async_smem();            // cp.async bytes -> visible to the tensor core
+      tc_fence_after();
+      const uint32_t ks_addr = k_s + (kc % kNK) * kStageBytes;
+      const uint32_t d = t_s0 + w * 128;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t off = (ks >> 2) * (kStageBytes / 2) + (ks & 3) * 32;
+        const uint64_t dq = desc_kmajor(q_s + off), dk = desc_kmajor(ks_addr + off);
+        if (POOL) mma_ss(d, dk, dq, idesc_qk, ks > 0);     // S^T: lanes = keys
+        else mma_ss(d, dq, dk, idesc_qk, ks > 0);          // S: lanes = (query, head) rows
+      }
+      mma_commit(&bar_kempty[kc % kNK]);
+      mma_commit(&bar_sfull[w]);
+      ++kc;
+      if (w) ++issued1; else ++issued0;
+      return true;
+    };
+    for (int k = 0; k < n_rounds && ok; ++k) {
+      const int item = item_of(k);
+      if (item >= n_items) continue;
+      const TileItem it = decode_item<MODE>(p, item);
+      if (it.nb == 0) continue;
+      ok = mbar_wait(&sh.bar_q, qn & 1, &give_up, 21);
+      if (!ok) break;
+      if (GATHER) fence_proxy_async_smem();
+      ++qn;
+      ok = issue_qk(0);
+      if (ok && it.nb == 1) mma_commit(&sh.bar_qempty);  // the tile's last Q.K^T is queued: Q may be replaced
+      for (int j = 0; j < it.nb && ok; ++j) {
+        const int w = j & 1;
+        if (j + 1 < it.nb) {
+          ok = issue_qk((j + 1) & 1);
+          if (!ok) break;
+          if (j + 2 == it.nb) mma_commit(&sh.bar_qempty);
+        }
+        if (HAS_V) {
+          // P(j) is in tensor memory (and S(j) has been consumed)
+          int& rel = w ? released1 : released0;
+          ok = mbar_wait(&bar_pready[w], rel & 1, &give_up, 24);
+          if (!ok) break;
+          ++rel;
+          ok = mbar_wait(&bar_vfull[vc % kNV], (vc / kNV) & 1, &give_up, 25);
+          if (!ok) break;
+          if (j < 2 && tiles_done > 0) {
+            // the first P.V of a stream in a new tile overwrites O: the previous tile's epilogue must
+            // have read both accumulators
+            ok = mbar_wait(&sh.bar_ofree, (tiles_done - 1) & 1, &give_up, 26);
+            if (!ok) break;
+          }
+          if (GATHER) fence_proxy_async_smem();
+          tc_fence_after();
+          const uint32_t vs_addr = v_s + (vc % kNV) * kStageBytes;
+          const uint32_t a = t_s0 + w * 128;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            mma_ts(t_o + w * 128, a + ks * 8, desc_mnmajor(vs_addr + ks * 2048, kStageBytes / 2), idesc_pv,
+                   (j > 1 || ks > 0) ? 1u : 0u);
+          }
+          mma_commit(&bar_vempty[vc % kNV]);
+          mma_commit(&bar_odone[w]);
+          ++vc;
+        }
+      }
+      ++tiles_done;
+    }
+  };
+
+  // ================================ softmax ======================================================
+  // Two warpgroups, two independent streams: warpgroup w owns the key blocks j = w, w+2, ... of every
+  // tile with its own S buffer, its own running (max, sum) per row and (with V) its own O
+  // accumulator, so the tcgen05.ld / max / ex2 phases of one stream overlap those of the other and
+  // nothing is exchanged per block.  The streams are merged like split-K partials in the epilogue.
+  auto softmax_role = [&]() {
     const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane, q_local = row >> 2;
-    const int tok = tile_start + q_local;
-    const int off = GATHER ? count : tile_start;      // slot - off = key position inside the tile
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t ts = t_s0 + wg * 128 + lane_sel;   // this stream's S / P buffer
     const uint32_t to = t_o + wg * 128 + lane_sel;    // this stream's O accumulator
-    float m_run = -INFINITY, l_run = 0.f;             // m_run in the scaled (log2) domain
+    int done_mine = 0, done_other = 0, tiles_done = 0; // blocks finished per stream, tiles finished
     bool ok = true;
-    int it = 0;                                       // blocks this stream has processed
-    for (int j = wg; j < nb; j += 2, ++it) {
-      ok = mbar_wait(&bar_sfull[wg], it & 1, &give_up, 31);
-      if (!ok) break;
-      tc_fence_after();
-      const int c0 = j * 128 - off;                     // key position (inside the tile) of column 0
-      const bool need_mask = (c0 + 127) > 0;            // only the last block(s) of a tile
-      // the whole S row (128 fp32) comes into registers with one round trip to tensor memory
-      uint32_t sr[4][32];
+    for (int k = 0; k < n_rounds && ok; ++k) {
+      const int item = item_of(k);
+      if (item >= n_items) continue;
+      const TileItem it = decode_item<MODE>(p, item);
+      if (it.nb == 0) continue;
+      const int tok = it.tile_start + q_local;
+      const int off = GATHER ? it.count : it.tile_start;   // slot - off = key position inside the tile
+      const int n_mine = (it.nb - wg + 1) >> 1, n_other = it.nb - n_mine;
+      float m_run = -INFINITY, l_run = 0.f;             // m_run in the scaled (log2) domain
+      for (int j = wg, jj = 0; j < it.nb; j += 2, ++jj) {
+        ok = mbar_wait(&bar_sfull[wg], (done_mine + jj) & 1, &give_up, 31);
+        if (!ok) break;
+        tc_fence_after();
+        const int c0 = j * 128 - off;                     // key position (inside the tile) of column 0
+        const bool need_mask = (c0 + 127) > 0;            // only the last block(s) of a tile
+        // the whole S row (128 fp32) comes into registers with one round trip to tensor memory
+        uint32_t sr[4][32];
 #pragma unroll
-      for (int part = 0; part < 4; ++part) tmem_ld32(ts + part * 32, sr[part]);
-      tmem_wait_ld();
-      if (!HAS_V) {                                      // S is in registers: the buffer may be refilled
-        tc_fence_before();
-        mbar_arrive(&bar_pready[wg]);
-      }
-      if (need_mask) {
-#pragma unroll
-        for (int part = 0; part < 4; ++part)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if ((c0 + part * 32 + i) > q_local) sr[part][i] = 0xFF800000u;     // -inf
-      }
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-      for (int part = 0; part < 4; ++part) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(sr[part][i]));
-          mx1 = fmaxf(mx1, __uint_as_float(sr[part][i + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(sr[part][i + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(sr[part][i + 3]));
+        for (int part = 0; part < 4; ++part) tmem_ld32(ts + part * 32, sr[part]);
+        tmem_wait_ld();
+        if (!HAS_V) {                                      // S is in registers: the buffer may be refilled
+          tc_fence_before();
+          mbar_arrive(&bar_pready[wg]);
         }
-      }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale2;
-      // The reference point of the exponentials only moves when the row maximum has grown by more
-      // than 2^kRescaleLog2: probabilities then stay below 2^kRescaleLog2 (exact in fp32, harmless in
-      // fp16), and the O accumulator is rescaled only on those rare blocks.  lse2 = m + log2(l) holds
-      // for any reference point m.
-      const float m_new = (mx > m_run + kRescaleLog2) ? mx : m_run;
-      const float alpha = ex2(m_run - m_new);
-      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-      if (HAS_V) {
+        if (need_mask) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t pr[32];
+          for (int part = 0; part < 4; ++part)
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {              // P column i of this half = keys 2i, 2i+1
-            const int c = half * 64 + i * 2;
-            float a0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), p.scale2, -m_new));
-            float a1 = ex2(fmaf(__uint_as_float(sr[c >> 5][(c & 31) + 1]), p.scale2, -m_new));
-            float a2 = ex2(fmaf(__uint_as_float(sr[c >> 5][(c & 31) + 2]), p.scale2, -m_new));
-            float a3 = ex2(fmaf(__uint_as_float(sr[c >> 5][(c & 31) + 3]), p.scale2, -m_new));
-            s0 += a0; s1 += a1; s2 += a2; s3 += a3;
-            pr[i] = pack2(a0, a1);
-            pr[i + 1] = pack2(a2, a3);
-          }
-          tmem_st32(ts + half * 32, pr);                 // P columns [half*32, +32) = keys [half*64, +64)
+            for (int i = 0; i < 32; ++i)
+              if ((c0 + part * 32 + i) > q_local) sr[part][i] = 0xFF800000u;     // -inf
         }
-      } else {
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int part = 0; part < 4; ++part)
+        for (int part = 0; part < 4; ++part) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            s0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -m_new));
-            s1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -m_new));
-            s2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -m_new));
-            s3 += ex2(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -m_new));
+            mx0 = fmaxf(mx0, __uint_as_float(sr[part][i]));
+            mx1 = fmaxf(mx1, __uint_as_float(sr[part][i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(sr[part][i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(sr[part][i + 3]));
           }
-      }
-      l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
-      m_run = m_new;
-      if (HAS_V) {
-        if (it > 0 && !__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
-          // the previous P.V of this stream must have landed in O before O is rescaled
-          ok = mbar_wait(&bar_odone[wg], (it - 1) & 1, &give_up, 32);
-          if (!ok) break;
-          tc_fence_after();
-          {
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale2;
+        // The reference point of the exponentials only moves when the row maximum has grown by more
+        // than 2^kRescaleLog2: probabilities then stay below 2^kRescaleLog2 (exact in fp32, harmless in
+        // fp16), and the O accumulator is rescaled only on those rare blocks.  lse2 = m + log2(l) holds
+        // for any reference point m.
+        const float m_new = (mx > m_run + kRescaleLog2) ? mx : m_run;
+        const float alpha = ex2(m_run - m_new);
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        if (HAS_V) {
+#pragma unroll
+          for (int part = 0; part < 4; ++part) {           // 32 keys -> 16 packed P columns
+            uint32_t pr[16];
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              float a0 = ex2(fmaf(__uint_as_float(sr[part][2 * i]), p.scale2, -m_new));
+              float a1 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 1]), p.scale2, -m_new));
+              float a2 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 2]), p.scale2, -m_new));
+              float a3 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 3]), p.scale2, -m_new));
+              s0 += a0; s1 += a1; s2 += a2; s3 += a3;
+              pr[i] = pack2(a0, a1);
+              pr[i + 1] = pack2(a2, a3);
+            }
+            tmem_st16(ts + part * 16, pr);                 // P columns [part*16, +16) = keys [part*32, +32)
+          }
+        } else {
+#pragma unroll
+          for (int part = 0; part < 4; ++part)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              s0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -m_new));
+              s1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -m_new));
+              s2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -m_new));
+              s3 += ex2(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -m_new));
+            }
+        }
+        l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
+        m_run = m_new;
+        if (HAS_V) {
+          if (jj > 0 && !__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
+            // the previous P.V of this stream must have landed in O before O is rescaled
+            ok = mbar_wait(&bar_odone[wg], (done_mine + jj - 1) & 1, &give_up, 32);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll 1
             for (int part = 0; part < 4; ++part) {
               uint32_t orr[32];
@@ -408,38 +536,39 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
               tmem_st32(to + part * 32, orr);
             }
           }
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&bar_pready[wg]);
         }
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&bar_pready[wg]);
       }
-    }
-    // ---- epilogue: merge the two streams, normalise, store -------------------------------------
-    // it = number of blocks of this stream; the other stream has nb - it
-    float f_mine = 1.f, f_other = 0.f, l_tot = l_run, m_tot = m_run;
-    if (ok) {
-      xchg[0][wg][row] = m_run;
-      xchg[1][wg][row] = l_run;
-      mbar_arrive(&bar_x);
-      ok = mbar_wait(&bar_x, 0, &give_up, 35);
-      if (ok) {
-        const float m_o = xchg[0][wg ^ 1][row], l_o = xchg[1][wg ^ 1][row];
-        m_tot = fmaxf(m_run, m_o);
-        f_mine = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_tot);
-        f_other = (m_o == -INFINITY) ? 0.f : ex2(m_o - m_tot);
-        l_tot = l_run * f_mine + l_o * f_other;
+      if (!ok) break;
+      done_mine += n_mine;
+      done_other += n_other;
+      // ---- epilogue: merge the two streams, normalise, store -----------------------------------
+      // the exchange buffer is free once both warpgroups have finished the previous tile's epilogue
+      if (tiles_done > 0) {
+        ok = mbar_wait(&sh.bar_ofree, (tiles_done - 1) & 1, &give_up, 37);
+        if (!ok) break;
       }
-    }
-    if (ok && HAS_V) {
-      const int n_mine = it, n_other = nb - it;
-      if (n_mine > 0) ok = mbar_wait(&bar_odone[wg], (n_mine - 1) & 1, &give_up, 33);
-      if (ok && n_other > 0) ok = mbar_wait(&bar_odone[wg ^ 1], (n_other - 1) & 1, &give_up, 36);
-      if (ok) {
+      sh.xchg[0][wg][row] = m_run;
+      sh.xchg[1][wg][row] = l_run;
+      mbar_arrive(&sh.bar_x);
+      ok = mbar_wait(&sh.bar_x, tiles_done & 1, &give_up, 35);
+      if (!ok) break;
+      const float m_o = sh.xchg[0][wg ^ 1][row], l_o = sh.xchg[1][wg ^ 1][row];
+      const float m_tot = fmaxf(m_run, m_o);
+      const float f_mine = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_tot);
+      const float f_other = (m_o == -INFINITY) ? 0.f : ex2(m_o - m_tot);
+      const float l_tot = l_run * f_mine + l_o * f_other;
+      if (HAS_V) {
+        if (n_mine > 0) ok = mbar_wait(&bar_odone[wg], (done_mine - 1) & 1, &give_up, 33);
+        if (ok && n_other > 0) ok = mbar_wait(&bar_odone[wg ^ 1], (done_other - 1) & 1, &give_up, 36);
+        if (!ok) break;
         tc_fence_after();
         const float inv = 1.0f / l_tot;
         const float w_mine = f_mine * inv, w_other = f_other * inv;
         // this warpgroup stores output columns [wg*64, +64) of its rows, from both accumulators
-        __half* orow = p.out + (((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)) * kD + wg * 64;
+        __half* orow = p.out + (((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)) * kD + wg * 64;
         const uint32_t o_mine = t_o + wg * 128 + lane_sel + wg * 64;
         const uint32_t o_other = t_o + (wg ^ 1) * 128 + lane_sel + wg * 64;
 #pragma unroll 1
@@ -468,41 +597,100 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
           }
         }
       }
+      if (wg == 0 && p.lse2 && tok < p.L)
+        p.lse2[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)] = m_tot + log2f(l_tot);
+      // both accumulators and the exchange buffer have been read
+      tc_fence_before();
+      mbar_arrive(&sh.bar_ofree);
+      ++tiles_done;
     }
-    if (ok && wg == 0 && p.lse2 && tok < p.L)
-      p.lse2[((int64_t)b * p.L + tok) * p.H + g * kHg + (row & 3)] = m_tot + log2f(l_tot);
-  } else {
-    // ================================ pooled-score reducer =====================================
-    // warpgroup w owns the key blocks j = w, w+2, ...; thread = key lane, sums over the tile's 128
-    // (query, head) rows, i.e. over the 128 columns of S^T
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;\n");
+  };
+
+  // ================================ pooled-score reducer =========================================
+  // warpgroup w owns the key blocks j = w, w+2, ... of every tile; thread = key lane, sums over the
+  // tile's 128 (query, head) rows, i.e. over the 128 columns of S^T
+  auto pool_role = [&]() {
     const int wg = warp >> 2;
     const int key_lane = (warp & 3) * 32 + lane;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t ts = t_s0 + wg * 128 + lane_sel;
-    float* prow = p.pooled + (((int64_t)b * p.G + g) * p.T + t) * p.pooled_stride;
-    int it = 0;
-    for (int j = wg; j < nb; j += 2, ++it) {
-      if (!mbar_wait(&bar_sfull[wg], it & 1, &give_up, 41)) break;
-      tc_fence_after();
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      uint32_t sr[4][32];
+    int done_mine = 0, tiles_seen = 0;
+    bool ok = true;
+    for (int k = 0; k < n_rounds && ok; ++k) {
+      const int item = item_of(k);
+      if (item >= n_items) continue;
+      const TileItem it = decode_item<MODE>(p, item);
+      if (it.nb == 0) continue;
+      const int n_mine = (it.nb - wg + 1) >> 1;
+      // this warpgroup's copy of the tile's 128 lse2 values (row = 4 * query + head), double-buffered
+      // by tile parity: a thread that runs ahead must not overwrite values that a slower thread of
+      // the warpgroup still reads for the previous tile
+      float* lse_s = sh.lse[wg][tiles_seen & 1];
+      {
+        const int tok = it.tile_start + (key_lane >> 2);
+        lse_s[key_lane] =
+            tok < p.L ? p.lse2_in[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (key_lane & 3)] : INFINITY;
+        mbar_arrive(&sh.bar_lse[wg]);
+        ok = mbar_wait(&sh.bar_lse[wg], tiles_seen & 1, &give_up, 43);
+        if (!ok) break;
+        ++tiles_seen;
+      }
+      float* prow = p.pooled + (((int64_t)it.b * p.G + it.g) * p.T + it.t) * p.pooled_stride;
+      for (int j = wg, jj = 0; j < it.nb; j += 2, ++jj) {
+        ok = mbar_wait(&bar_sfull[wg], (done_mine + jj) & 1, &give_up, 41);
+        if (!ok) break;
+        tc_fence_after();
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        uint32_t sr[4][32];
 #pragma unroll
-      for (int part = 0; part < 4; ++part) tmem_ld32(ts + part * 32, sr[part]);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&bar_pready[wg]);                      // S^T block is in registers: the buffer is free
+        for (int part = 0; part < 4; ++part) tmem_ld32(ts + part * 32, sr[part]);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&bar_pready[wg]);                      // S^T block is in registers: the buffer is free
 #pragma unroll
-      for (int part = 0; part < 4; ++part)
+        for (int part = 0; part < 4; ++part)
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          a0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -lse_s[part * 32 + i]));
-          a1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -lse_s[part * 32 + i + 1]));
-          a2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -lse_s[part * 32 + i + 2]));
-          a3 += ex2(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -lse_s[part * 32 + i + 3]));
-        }
-      const int key = j * 128 + key_lane;
-      if (key < tile_start) prow[key] = (a0 + a1) + (a2 + a3);
+          for (int i = 0; i < 32; i += 4) {
+            a0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -lse_s[part * 32 + i]));
+            a1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -lse_s[part * 32 + i + 1]));
+            a2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -lse_s[part * 32 + i + 2]));
+            a3 += ex2(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -lse_s[part * 32 + i + 3]));
+          }
+        const int key = j * 128 + key_lane;
+        if (key < it.tile_start) prow[key] = (a0 + a1) + (a2 + a3);
+      }
+      done_mine += n_mine;
+    }
+  };
+
+  // ================================ role dispatch =================================================
+  // Register hand-over (setmaxnreg).  The pool is what the CTA got at launch: the softmax warpgroups
+  // can only take what the other warpgroups give back, and the warps that share an SM sub-partition
+  // (w, w+4, w+8, w+12) must stay within 512 registers per thread slot.
+  //   sparse: 512 threads x 128 at launch; 256 x 200 + 128 x 64 + 128 x 48 = 65536; 2 x 200 + 64 + 48 = 512
+  //   dense : 384 threads x 168 at launch; 256 x 200 + 128 x 96 = 63488 <= 64512; 2 x 200 + 96 <= 512
+  // The instruction is warpgroup-wide: all four warps of a warpgroup execute the same one, and the role
+  // code sits inside the branch that issued it.
+  if (warp < 8) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;\n");
+    if (POOL) pool_role(); else softmax_role();
+  } else if (GATHER) {
+    if (warp < 12) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 64;\n");
+      producer_gather();
+    } else {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 48;\n");
+      if (warp == kMmaWarp && lane == 0) mma_role();
+      __syncwarp();
+    }
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;\n");
+    if (warp == Cfg::kProducerWarp0) {
+      if (lane == 0) producer_tma();
+      __syncwarp();
+    } else if (warp == kMmaWarp) {
+      if (lane == 0) mma_role();
+      __syncwarp();
     }
   }
 
@@ -514,15 +702,46 @@ __global__ void __launch_bounds__(kPfThreads, 1) tile_prefill_kernel(const Prefi
   if (tid == 0 && give_up != 0) atomicCAS(&g_status_word, 0, give_up);
 }
 
-static_assert(sizeof(PfShared) <= 2304, "PfShared grew");
-constexpr int kSmemAttn = kStageBytes * (1 + 3 + kNV) + kPadAllowance + 2304;   // = 232448, the sm_100 limit
-constexpr int kSmemNoV = kStageBytes * (1 + kNKMax) + kPadAllowance + 2304;
+// ---- host side ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode_tiled = nullptr;
 
 int init_prefill() {
   KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kDenseAttn>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn));
   KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kSparse>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn));
   KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kDenseLse>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemNoV));
   KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kPool>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemNoV));
+  if (!g_encode_tiled) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    KB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &res));
+    KB_REQUIRE(res == cudaDriverEntryPointSuccess && fn, "the driver does not export cuTensorMapEncodeTiled");
+    g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  return 0;
+}
+
+// 4-D tiled map over fp16 activations: dimensions (d, head, token, batch), 128-byte swizzle, boxes of
+// 64 x box_heads x box_tokens x 1 elements.  Host-only work (the descriptor is passed by value).
+static int make_act_map(CUtensorMap* map, const __half* base, int64_t sb, int64_t st, int64_t sh, int heads,
+                        int tokens, int batch, int box_heads, int box_tokens, const char* what) {
+  KB_REQUIRE(g_encode_tiled, "kb200_init has not been called");
+  // a dimension of extent 1 never uses its stride; give it a legal one
+  const int64_t min_stride = 8;
+  if (heads == 1 && sh < min_stride) sh = kD;
+  if (batch == 1 && sb < min_stride) sb = (int64_t)tokens * (st > 0 ? st : kD);
+  const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)heads, (cuuint64_t)tokens, (cuuint64_t)batch};
+  const cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)st * 2, (cuuint64_t)sb * 2};
+  const cuuint32_t box[4] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_tokens, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<__half*>(base), dims, strides, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  KB_REQUIRE(r == CUDA_SUCCESS,
+             "prefill: cuTensorMapEncodeTiled rejected the layout of %s (error %d; strides b/t/h = %lld/%lld/%lld)", what,
+             (int)r, (long long)sb, (long long)st, (long long)sh);
   return 0;
 }
 
@@ -539,12 +758,19 @@ static int fill_act(const kb200_act_layout* a, const __half** ptr, int64_t* sb, 
   return 0;
 }
 
+// one CTA per SM (the kernels are persistent), fewer when there are fewer tiles than SMs
+static unsigned persistent_grid(const PrefillParams& p) {
+  int64_t items = (int64_t)p.B * p.G * p.T;
+  int64_t sms = sm_count();
+  return (unsigned)(items < sms ? items : sms);
+}
+
 static int check_shape(int batch, int seq_len, int H, int G) {
   KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
   KB_REQUIRE(batch >= 0 && seq_len >= 0, "prefill: negative size");
   KB_REQUIRE(G > 0 && H == G * kHg,
              "prefill: %d query heads / %d KV heads; exactly %d query heads per KV head are supported", H, G, kHg);
-  KB_REQUIRE(batch <= 65535 && G <= 65535, "prefill: batch and KV heads must fit a grid dimension");
+  KB_REQUIRE((int64_t)batch * G * ceil_div(seq_len > 0 ? seq_len : 1, kTile) < (1ll << 30), "prefill: too many tiles");
   return 0;
 }
 
@@ -575,9 +801,16 @@ extern "C" int kb200_prefill_dense(const kb200_act_layout* q, const kb200_act_la
   p.out = static_cast<__half*>(out);
   p.lse2 = lse2;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
-  dim3 grid(p.T, num_kv_heads, batch);
-  if (out) tile_prefill_kernel<kDenseAttn><<<grid, kPfThreads, kSmemAttn, (cudaStream_t)stream>>>(p);
-  else tile_prefill_kernel<kDenseLse><<<grid, kPfThreads, kSmemNoV, (cudaStream_t)stream>>>(p);
+  CUtensorMap tq, tk, tv;
+  if (make_act_map(&tq, p.q, p.q_sb, p.q_st, p.q_sh, num_q_heads, seq_len, batch, kHg, kTile, "q") != 0) return -1;
+  if (make_act_map(&tk, p.k, p.k_sb, p.k_st, p.k_sh, num_kv_heads, seq_len, batch, 1, 128, "k") != 0) return -1;
+  tv = tk;
+  if (out && make_act_map(&tv, p.v, p.v_sb, p.v_st, p.v_sh, num_kv_heads, seq_len, batch, 1, 128, "v") != 0) return -1;
+  dim3 grid(persistent_grid(p));
+  if (out)
+    tile_prefill_kernel<kDenseAttn><<<grid, PfCfg<kDenseAttn>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, tq, tk, tv);
+  else
+    tile_prefill_kernel<kDenseLse><<<grid, PfCfg<kDenseLse>::kThreads, kSmemNoV, (cudaStream_t)stream>>>(p, tq, tk, tv);
   KB_CHECK_LAUNCH("tile_prefill_kernel<dense>");
   return 0;
 }
@@ -600,8 +833,11 @@ extern "C" int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_
   p.pooled = pooled;
   p.pooled_stride = row_stride;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
-  dim3 grid(p.T, num_kv_heads, batch);
-  tile_prefill_kernel<kPool><<<grid, kPfThreads, kSmemNoV, (cudaStream_t)stream>>>(p);
+  CUtensorMap tq, tk;
+  if (make_act_map(&tq, p.q, p.q_sb, p.q_st, p.q_sh, num_q_heads, seq_len, batch, kHg, kTile, "q") != 0) return -1;
+  if (make_act_map(&tk, p.k, p.k_sb, p.k_st, p.k_sh, num_kv_heads, seq_len, batch, 1, 128, "k") != 0) return -1;
+  dim3 grid(persistent_grid(p));
+  tile_prefill_kernel<kPool><<<grid, PfCfg<kPool>::kThreads, kSmemNoV, (cudaStream_t)stream>>>(p, tq, tk, tk);
   KB_CHECK_LAUNCH("tile_prefill_kernel<pool>");
   return 0;
 }
@@ -632,8 +868,9 @@ extern "C" int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_l
   p.out = static_cast<__half*>(out);
   p.lse2 = lse2;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
-  dim3 grid(p.T, num_kv_heads, batch);
-  tile_prefill_kernel<kSparse><<<grid, kPfThreads, kSmemAttn, (cudaStream_t)stream>>>(p);
+  CUtensorMap none{};                                    // the gather path uses no tensor maps
+  dim3 grid(persistent_grid(p));
+  tile_prefill_kernel<kSparse><<<grid, PfCfg<kSparse>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, none, none, none);
   KB_CHECK_LAUNCH("tile_prefill_kernel<sparse>");
   return 0;
 }
