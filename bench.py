@@ -356,8 +356,15 @@ def main():
         top = max(share, key=share.get)
         t_ms, flops, _n = kernels[top]
         achieved = flops / (t_ms * 1e-3) / 1e12
+        # dram__bytes_read + dram__bytes_write per launch from the ncu capture at 16 384 tokens
+        # (profiles/tile_prefill_kernels_16k_ncu.md), scaled linearly in L: every operand grows linearly
+        ncu_mb_16k = {"prefill_dense_attn": 515.2, "prefill_dense_lse": 172.9, "prefill_pool_scores": 289.7,
+                      "prefill_sparse": 312.6}
+        traffic = ncu_mb_16k.get(top)
+        traffic = None if traffic is None else traffic * 1e6 * (L / 16384)
         roof = {"kernel": "tile_prefill_kernel<%s>" % top, "bound": "tensor", "achieved": achieved,
-                "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"], "traffic": None,
+                "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"], "traffic": traffic,
+                "traffic_note": "bytes per launch, ncu capture at L=16384 scaled by L/16384",
                 "peak_source": peaks["source"] + " (sustained bf16 GEMM)",
                 "per_kernel_ms": {k: round(v[0], 4) for k, v in kernels.items()},
                 "per_kernel_tflops": {k: round(v[1] / (v[0] * 1e-3) / 1e12, 1) for k, v in kernels.items() if v[1]},
@@ -369,18 +376,39 @@ def main():
         n_host = min(4, wl.layers)
         host = [tuple(x.cpu().pin_memory() for x in inputs[l]) for l in range(n_host)]
         host_out = torch.empty(inputs[0][0].shape, dtype=torch.float16).pin_memory()
-        dq, dk, dv = (torch.empty_like(x) for x in inputs[0])
+        dbuf = [tuple(torch.empty_like(x) for x in inputs[0]) for _ in range(2)]   # double-buffered device inputs
         h2d = sum(x.numel() * 2 for x in inputs[0]) * wl.layers
         d2h = host_out.numel() * 2 * wl.layers
+        in_s, out_s = torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_free = [torch.cuda.Event() for _ in range(2)]
 
         def e2e_step(_i=0):
+            # three streams: H2D of layer l+1 and D2H of layer l-1 overlap the kernels of layer l; every copy and
+            # every kernel of the step lies between the two timing events on the current stream
+            cur = torch.cuda.current_stream()
+            in_s.wait_stream(cur)
+            out_s.wait_stream(cur)
             for l in range(wl.layers):
+                slot = l & 1
+                dq, dk, dv = dbuf[slot]
                 hq, hk, hv = host[l % n_host]
-                dq.copy_(hq, non_blocking=True)
-                dk.copy_(hk, non_blocking=True)
-                dv.copy_(hv, non_blocking=True)
+                with torch.cuda.stream(in_s):
+                    if l >= 2:
+                        in_s.wait_event(ev_free[slot])            # layer l-2 has finished reading this slot
+                    dq.copy_(hq, non_blocking=True)
+                    dk.copy_(hk, non_blocking=True)
+                    dv.copy_(hv, non_blocking=True)
+                    ev_in[slot].record(in_s)
+                cur.wait_event(ev_in[slot])
                 o, _ = strat.attention_forward(mods[l], dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2), None, scaling)
-                host_out.copy_(o, non_blocking=True)
+                ev_free[slot].record(cur)
+                out_s.wait_event(ev_free[slot])
+                with torch.cuda.stream(out_s):
+                    host_out.copy_(o, non_blocking=True)
+                o.record_stream(out_s)
+            cur.wait_stream(in_s)
+            cur.wait_stream(out_s)
 
         e2e_step()
         if world > 1:
@@ -389,8 +417,10 @@ def main():
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e = {"value": float(t.item()), "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "note": f"{n_host} distinct pinned host layers cycled over {wl.layers} layers; copies serialised with compute"}
-        del host, host_out, dq, dk, dv
+               "note": f"{n_host} distinct pinned host layers cycled over {wl.layers} layers; H2D, kernels and D2H of "
+                       "consecutive layers overlap on three streams (double-buffered device inputs)"}
+        dq = dk = dv = None
+        del host, host_out, dbuf, dq, dk, dv
 
     # ---------------- dense attention on the same GPU ----------------------------------------------
     dense = None
