@@ -2,7 +2,7 @@
 //
 // Replaces the torch.topk call sites of the reference's efficient path
 // (strategies/EfficientKascadeStrategy.py:82,90,111).  The row is read from global memory (L2 after
-// the first pass): four 8-bit histogram passes find the k-th largest key exactly, a fifth pass
+// the first pass): three 11/11/10-bit histogram passes find the k-th largest key exactly, a fourth pass
 // compacts the selected positions in ascending index order, taking ties at the threshold from the
 // lowest index upwards.
 #include "common.cuh"
@@ -10,6 +10,7 @@
 namespace kb200 {
 
 constexpr int kTopkThreads = 512;
+constexpr int kTopkBins = 2048;                           // 11-bit digits: 3 passes cover the 32-bit key
 
 // order-preserving map float -> uint32 (larger float <=> larger key)
 __device__ __forceinline__ uint32_t float_key(float x) {
@@ -17,20 +18,12 @@ __device__ __forceinline__ uint32_t float_key(float x) {
   return b ^ ((b >> 31) ? 0xFFFFFFFFu : 0x80000000u);
 }
 
-__device__ __forceinline__ void hist_add(uint32_t* hist, bool valid, uint32_t digit, int lane) {
-  // warp-aggregated shared-memory atomic: post-softmax scores share their leading bits, so most
-  // lanes of a warp hit the same bin
-  uint32_t tag = valid ? digit : 0xFFFFu;
-  uint32_t peers = __match_any_sync(0xFFFFFFFFu, tag);
-  if (valid && (__ffs(peers) - 1) == lane) atomicAdd(&hist[digit], (uint32_t)__popc(peers));
-}
-
 __global__ void __launch_bounds__(kTopkThreads)
 topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_cols,
                    const int32_t* __restrict__ n_valid, const int32_t* __restrict__ k_row, int k_max,
                    int32_t* __restrict__ out_idx, int64_t idx_stride, int32_t* __restrict__ out_count,
                    int64_t rows) {
-  __shared__ uint32_t hist[256];
+  __shared__ uint32_t hist[kTopkBins];
   __shared__ uint32_t warp_tot[kTopkThreads / 32];
   __shared__ uint32_t sh_digit, sh_remaining;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -51,42 +44,58 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
     const int n4 = (n + 3) >> 2;
     const int iters = (n4 + kTopkThreads - 1) / kTopkThreads;
 
+    // three histogram passes over key bits [31:21], [20:10], [9:0]; post-softmax scores spread over
+    // many exponent / mantissa bins in every pass, so plain shared-memory atomics do
     uint32_t prefix = 0, mask = 0, remaining = (uint32_t)k;
 #pragma unroll 1
-    for (int pass = 0; pass < 4; ++pass) {
-      const int shift = 24 - 8 * pass;
-      if (tid < 256) hist[tid] = 0;
+    for (int pass = 0; pass < 3; ++pass) {
+      const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
+      const uint32_t dmask = pass == 2 ? 1023u : 2047u;
+      for (int i = tid; i < kTopkBins; i += kTopkThreads) hist[i] = 0;
       __syncthreads();
       for (int it = 0; it < iters; ++it) {
-        int i4 = it * kTopkThreads + tid;
-        bool in = i4 < n4;
-        float4 x = in ? __ldg(row4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
-        float xs[4] = {x.x, x.y, x.z, x.w};
+        const int i4 = it * kTopkThreads + tid;
+        const bool in = i4 < n4;
+        const float4 x = in ? __ldg(row4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float xs[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          uint32_t u = float_key(xs[e]);
-          bool valid = in && (i4 * 4 + e < n) && ((u & mask) == prefix);
-          hist_add(hist, valid, (u >> shift) & 255u, lane);
+          const uint32_t u = float_key(xs[e]);
+          const bool valid = in && (i4 * 4 + e < n) && ((u & mask) == prefix);
+          const uint32_t digit = (u >> shift) & dmask;
+          if (pass == 0) {
+            // the leading bits of the scores of a row mostly coincide: aggregate within the warp
+            const uint32_t peers = __match_any_sync(0xFFFFFFFFu, valid ? digit : 0xFFFFu);
+            if (valid && (__ffs(peers) - 1) == lane) atomicAdd(&hist[digit], (uint32_t)__popc(peers));
+          } else if (valid) {
+            atomicAdd(&hist[digit], 1u);
+          }
         }
       }
       __syncthreads();
-      if (warp == 0) {
-        uint32_t c[8], s = 0;
+      // bin d with count(> d) < remaining <= count(>= d): suffix sums over 4 bins per thread
+      {
+        uint32_t c[4], ssum = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { c[i] = hist[lane * 8 + i]; s += c[i]; }
-        uint32_t suf = s;  // sum over lanes >= lane
+        for (int i = 0; i < 4; ++i) { c[i] = hist[tid * 4 + i]; ssum += c[i]; }
+        uint32_t suf = ssum;                               // sum over lanes >= lane of this warp
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
-          uint32_t v = __shfl_down_sync(0xFFFFFFFFu, suf, off);
+          const uint32_t v = __shfl_down_sync(0xFFFFFFFFu, suf, off);
           if (lane + off < 32) suf += v;
         }
-        uint32_t above = suf - s;
-        if (above < remaining && remaining <= above + s) {
+        if (lane == 0) warp_tot[warp] = suf;
+        __syncthreads();
+        uint32_t higher = 0;
+#pragma unroll
+        for (int w = 0; w < kTopkThreads / 32; ++w) higher += w > warp ? warp_tot[w] : 0u;
+        const uint32_t above = higher + suf - ssum;        // candidates in bins of higher threads
+        if (above < remaining && remaining <= above + ssum) {
           uint32_t acc = above;
 #pragma unroll
-          for (int i = 7; i >= 0; --i) {
+          for (int i = 3; i >= 0; --i) {
             if (acc < remaining && acc + c[i] >= remaining) {
-              sh_digit = (uint32_t)(lane * 8 + i);
+              sh_digit = (uint32_t)(tid * 4 + i);
               sh_remaining = remaining - acc;
             }
             acc += c[i];
@@ -95,7 +104,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
       }
       __syncthreads();
       prefix |= sh_digit << shift;
-      mask |= 255u << shift;
+      mask |= dmask << shift;
       remaining = sh_remaining;
       __syncthreads();
     }
