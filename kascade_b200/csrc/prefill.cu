@@ -46,7 +46,7 @@ constexpr int kStageBytes = 128 * kD * 2;     // one 128-row operand tile (32 KB
 constexpr int kNKMax = 6;                     // K ring: 3 stages with a V ring, 6 without
 constexpr int kNV = 3;
 constexpr float kRescaleLog2 = 8.0f;          // see the softmax role
-constexpr int kPadAllowance = 768;            // tiles need 1024-byte alignment
+constexpr int kPadAllowance = 512;            // tiles need 1024-byte alignment
 
 __device__ int g_status_word = 0;
 
@@ -92,7 +92,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 // the 7 x 32 KB tiles, the alignment padding and this block together stay inside the 227 KB limit.
 struct PfShared {
   uint64_t bar_q, bar_qempty, bar_kfull[kNKMax], bar_kempty[kNKMax], bar_vfull[kNV], bar_vempty[kNV];
-  uint64_t bar_sfull[2], bar_pready[2], bar_odone[2], bar_x, bar_ofree, bar_lse[2];
+  uint64_t bar_sfull[3], bar_pready[3], bar_odone[3], bar_x, bar_ofree, bar_lse[2];
   uint32_t tmem;
   int give_up;
   union {
@@ -100,9 +100,9 @@ struct PfShared {
     float lse[2][2][128];                              // pool mode: lse2 of the tile's rows [warpgroup][tile parity]
   };
 };
-static_assert(sizeof(PfShared) <= 2304, "PfShared grew");
-constexpr int kSmemAttn = kStageBytes * (1 + 3 + kNV) + kPadAllowance + 2304;   // = 232448, the sm_100 limit
-constexpr int kSmemNoV = kStageBytes * (1 + kNKMax) + kPadAllowance + 2304;
+static_assert(sizeof(PfShared) <= 2560, "PfShared grew");
+constexpr int kSmemAttn = kStageBytes * (1 + 3 + kNV) + kPadAllowance + 2560;   // = 232448, the sm_100 limit
+constexpr int kSmemNoV = kStageBytes * (1 + kNKMax) + kPadAllowance + 2560;
 
 // One work item = one query tile of one KV head of one sequence.
 struct TileItem {
@@ -193,12 +193,14 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     mbar_init(&sh.bar_qempty, 1);
     for (int i = 0; i < kNK; ++i) { mbar_init(&bar_kfull[i], Cfg::kProducerArrivals); mbar_init(&bar_kempty[i], 1); }
     for (int i = 0; i < kNV; ++i) { mbar_init(&bar_vfull[i], Cfg::kProducerArrivals); mbar_init(&bar_vempty[i], 1); }
-    for (int i = 0; i < 2; ++i) {
+    // with V all 256 softmax threads work on the same block (column halves); without V each
+    // warpgroup has its own blocks
+    for (int i = 0; i < 3; ++i) {
       mbar_init(&bar_sfull[i], 1);
-      mbar_init(&bar_pready[i], 128);
+      mbar_init(&bar_pready[i], HAS_V ? kSoftmaxThreads : 128);
       mbar_init(&bar_odone[i], 1);
-      mbar_init(&sh.bar_lse[i], 128);
     }
+    for (int i = 0; i < 2; ++i) mbar_init(&sh.bar_lse[i], HAS_V ? kSoftmaxThreads : 128);
     mbar_init(&sh.bar_x, kSoftmaxThreads);
     mbar_init(&sh.bar_ofree, kSoftmaxThreads);
     mbar_fence_init();
@@ -424,6 +426,226 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
           ++vc;
         }
       }
+      ++tiles_done;
+    }
+  };
+
+  // ================================ modes with V: one stream, three S buffers ======================
+  // With V, P(j) lives in the S buffer it was computed from until P.V(j) has read it, so a stream
+  // that owns one S buffer runs  softmax -> P.V -> Q.K^T -> softmax  strictly one after the other.
+  // Here all 256 softmax threads work on the same block (each thread one row and one half of the 128
+  // columns, row maximum exchanged through shared memory) and the blocks rotate through three S
+  // buffers (S0, S1, S2 = 384 columns, O = 128 columns): Q.K^T runs two blocks ahead of the softmax,
+  // P.V one block behind it, and the softmax of consecutive blocks is back to back.
+  auto mma_role_v = [&]() {
+    constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
+    constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
+    const uint32_t t_acc = tmem + 384;
+    int kc = 0, vc = 0, qn = 0, tiles_done = 0, sc = 0, pc = 0;   // sc / pc: blocks issued / consumed so far
+    bool ok = true;
+    auto issue_qk = [&]() -> bool {
+      if (!mbar_wait(&bar_kfull[kc % kNK], (kc / kNK) & 1, &give_up, 22)) return false;
+      if (GATHER) fence_proxy_async_smem();            // cp.async bytes -> visible to the tensor core
+      tc_fence_after();
+      const uint32_t ks_addr = k_s + (kc % kNK) * kStageBytes;
+      const uint32_t d = t_s0 + (sc % 3) * 128;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t off = (ks >> 2) * (kStageBytes / 2) + (ks & 3) * 32;
+        mma_ss(d, desc_kmajor(q_s + off), desc_kmajor(ks_addr + off), idesc_qk, ks > 0);
+      }
+      mma_commit(&bar_kempty[kc % kNK]);
+      mma_commit(&bar_sfull[sc % 3]);
+      ++kc;
+      ++sc;
+      return true;
+    };
+    for (int k = 0; k < n_rounds && ok; ++k) {
+      const int item = item_of(k);
+      if (item >= n_items) continue;
+      const TileItem it = decode_item<MODE>(p, item);
+      if (it.nb == 0) continue;
+      ok = mbar_wait(&sh.bar_q, qn & 1, &give_up, 21);
+      if (!ok) break;
+      if (GATHER) fence_proxy_async_smem();
+      ++qn;
+      // S buffer (sc % 3) last held block sc - 3, whose P.V was issued before (in order)
+      int issued = 0;
+      for (; issued < 2 && issued < it.nb && ok; ++issued) ok = issue_qk();
+      if (ok && issued == it.nb) mma_commit(&sh.bar_qempty);   // the tile's last Q.K^T is queued: Q may be replaced
+      for (int j = 0; j < it.nb && ok; ++j) {
+        if (issued < it.nb) {
+          ok = issue_qk();
+          if (!ok) break;
+          if (++issued == it.nb) mma_commit(&sh.bar_qempty);
+        }
+        // P(j) is in tensor memory (and S(j) has been consumed)
+        ok = mbar_wait(&bar_pready[pc % 3], (pc / 3) & 1, &give_up, 24);
+        if (!ok) break;
+        ok = mbar_wait(&bar_vfull[vc % kNV], (vc / kNV) & 1, &give_up, 25);
+        if (!ok) break;
+        if (j == 0 && tiles_done > 0) {
+          // the first P.V of a new tile overwrites O: the previous tile's epilogue must have read it
+          ok = mbar_wait(&sh.bar_ofree, (tiles_done - 1) & 1, &give_up, 26);
+          if (!ok) break;
+        }
+        if (GATHER) fence_proxy_async_smem();
+        tc_fence_after();
+        const uint32_t vs_addr = v_s + (vc % kNV) * kStageBytes;
+        const uint32_t a = t_s0 + (pc % 3) * 128;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          mma_ts(t_acc, a + ks * 8, desc_mnmajor(vs_addr + ks * 2048, kStageBytes / 2), idesc_pv,
+                 (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        mma_commit(&bar_vempty[vc % kNV]);
+        // up to three P.V can be in flight; a wait names a phase only by its parity, so consecutive
+        // P.V signal three different barriers and a waiter is never more than one phase behind
+        mma_commit(&bar_odone[pc % 3]);
+        ++vc;
+        ++pc;
+      }
+      ++tiles_done;
+    }
+  };
+
+  auto softmax_role_v = [&]() {
+    const int half = warp >> 2;                        // which 64 of the 128 columns
+    const int row = (warp & 3) * 32 + lane, q_local = row >> 2;
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t t_acc = tmem + 384 + lane_sel + half * 64;   // this thread's 64 columns of O
+    int bc = 0, tiles_done = 0;                        // blocks / tiles finished so far
+    bool ok = true;
+    for (int k = 0; k < n_rounds && ok; ++k) {
+      const int item = item_of(k);
+      if (item >= n_items) continue;
+      const TileItem it = decode_item<MODE>(p, item);
+      if (it.nb == 0) continue;
+      const int tok = it.tile_start + q_local;
+      const int off = GATHER ? it.count : it.tile_start;   // slot - off = key position inside the tile
+      float m_run = -INFINITY, l_run = 0.f;             // m_run: reference of the row (both halves agree)
+      // the exchange buffer is free once both halves have finished the previous tile's epilogue
+      if (tiles_done > 0) {
+        ok = mbar_wait(&sh.bar_ofree, (tiles_done - 1) & 1, &give_up, 37);
+        if (!ok) break;
+      }
+      for (int j = 0; j < it.nb; ++j, ++bc) {
+        ok = mbar_wait(&bar_sfull[bc % 3], (bc / 3) & 1, &give_up, 31);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t ts = t_s0 + (bc % 3) * 128 + lane_sel;
+        const int c0 = j * 128 + half * 64 - off;         // key position (inside the tile) of this thread's column 0
+        const bool need_mask = (c0 + 63) > 0;             // only the last block(s) of a tile
+        uint32_t sr[2][32];
+        tmem_ld32(ts + half * 64, sr[0]);
+        tmem_ld32(ts + half * 64 + 32, sr[1]);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int part = 0; part < 2; ++part)
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if ((c0 + part * 32 + e) > q_local) sr[part][e] = 0xFF800000u;     // -inf
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(sr[part][e]));
+            mx1 = fmaxf(mx1, __uint_as_float(sr[part][e + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(sr[part][e + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(sr[part][e + 3]));
+          }
+        }
+        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        // both halves of a row must use the same reference: exchange the half-row maxima (this also
+        // orders the other half's S loads before this half's P stores into the shared buffer)
+        sh.xchg[bc & 1][half][row] = mx;
+        mbar_arrive(&sh.bar_lse[bc & 1]);
+        ok = mbar_wait(&sh.bar_lse[bc & 1], (bc >> 1) & 1, &give_up, 34);
+        if (!ok) break;
+        mx = fmaxf(mx, sh.xchg[bc & 1][half ^ 1][row]) * p.scale2;
+        // The reference point of the exponentials only moves when the row maximum has grown by more
+        // than 2^kRescaleLog2: probabilities then stay below 2^kRescaleLog2 (exact in fp32, harmless in
+        // fp16), and the O accumulator is rescaled only on those rare blocks.  lse2 = m + log2(l) holds
+        // for any reference point m.
+        const float m_new = (mx > m_run + kRescaleLog2) ? mx : m_run;
+        const float alpha = ex2(m_run - m_new);
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {             // 32 keys -> 16 packed P columns
+          uint32_t pr[16];
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            float a0 = ex2(fmaf(__uint_as_float(sr[part][2 * e]), p.scale2, -m_new));
+            float a1 = ex2(fmaf(__uint_as_float(sr[part][2 * e + 1]), p.scale2, -m_new));
+            float a2 = ex2(fmaf(__uint_as_float(sr[part][2 * e + 2]), p.scale2, -m_new));
+            float a3 = ex2(fmaf(__uint_as_float(sr[part][2 * e + 3]), p.scale2, -m_new));
+            s0 += a0; s1 += a1; s2 += a2; s3 += a3;
+            pr[e] = pack2(a0, a1);
+            pr[e + 1] = pack2(a2, a3);
+          }
+          // P columns [half*32 + part*16, +16) = keys [half*64 + part*32, +32)
+          tmem_st16(ts + half * 32 + part * 16, pr);
+        }
+        l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
+        m_run = m_new;
+        if (j > 0 && !__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
+          // the previous P.V must have landed in O before this thread's 64 columns of O are rescaled
+          ok = mbar_wait(&bar_odone[(bc - 1) % 3], ((bc - 1) / 3) & 1, &give_up, 32);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll 1
+          for (int part = 0; part < 2; ++part) {
+            uint32_t orr[32];
+            tmem_ld32(t_acc + part * 32, orr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) orr[e] = __float_as_uint(__uint_as_float(orr[e]) * alpha);
+            tmem_st32(t_acc + part * 32, orr);
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bar_pready[bc % 3]);
+      }
+      if (!ok) break;
+      // ---- epilogue: add the two halves' row sums, normalise, store ------------------------------
+      // (parities of the exchange: the block loop used xchg[bc & 1] with barriers bar_lse; the row sums
+      //  go through bar_x once per tile)
+      sh.xchg[bc & 1][half][row] = l_run;
+      mbar_arrive(&sh.bar_x);
+      ok = mbar_wait(&sh.bar_x, tiles_done & 1, &give_up, 35);
+      if (!ok) break;
+      const float l_tot = l_run + sh.xchg[bc & 1][half ^ 1][row];
+      ok = mbar_wait(&bar_odone[(bc - 1) % 3], ((bc - 1) / 3) & 1, &give_up, 33);   // the tile's last P.V
+      if (!ok) break;
+      tc_fence_after();
+      const float inv = 1.0f / l_tot;
+      __half* orow = p.out + (((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)) * kD + half * 64;
+#pragma unroll 1
+      for (int part = 0; part < 2; ++part) {
+        uint32_t oa[32];
+        tmem_ld32(t_acc + part * 32, oa);
+        tmem_wait_ld();
+        if (tok < p.L) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            uint4 w;
+            w.x = pack2(__uint_as_float(oa[e * 8 + 0]) * inv, __uint_as_float(oa[e * 8 + 1]) * inv);
+            w.y = pack2(__uint_as_float(oa[e * 8 + 2]) * inv, __uint_as_float(oa[e * 8 + 3]) * inv);
+            w.z = pack2(__uint_as_float(oa[e * 8 + 4]) * inv, __uint_as_float(oa[e * 8 + 5]) * inv);
+            w.w = pack2(__uint_as_float(oa[e * 8 + 6]) * inv, __uint_as_float(oa[e * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + part * 32 + e * 8) = w;
+          }
+        }
+      }
+      if (half == 0 && p.lse2 && tok < p.L)
+        p.lse2[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)] = m_run + log2f(l_tot);
+      // O and the exchange buffer have been read
+      tc_fence_before();
+      mbar_arrive(&sh.bar_ofree);
       ++tiles_done;
     }
   };
@@ -673,14 +895,14 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   // code sits inside the branch that issued it.
   if (warp < 8) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 200;\n");
-    if (POOL) pool_role(); else softmax_role();
+    if (POOL) pool_role(); else if (HAS_V) softmax_role_v(); else softmax_role();
   } else if (GATHER) {
     if (warp < 12) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 64;\n");
       producer_gather();
     } else {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 48;\n");
-      if (warp == kMmaWarp && lane == 0) mma_role();
+      if (warp == kMmaWarp && lane == 0) { if (HAS_V) mma_role_v(); else mma_role(); }
       __syncwarp();
     }
   } else {
@@ -689,7 +911,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (lane == 0) producer_tma();
       __syncwarp();
     } else if (warp == kMmaWarp) {
-      if (lane == 0) mma_role();
+      if (lane == 0) { if (HAS_V) mma_role_v(); else mma_role(); }
       __syncwarp();
     }
   }
