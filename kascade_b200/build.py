@@ -11,6 +11,7 @@ from __future__ import annotations
 import argparse
 import hashlib
 import os
+import shlex
 import subprocess
 import sys
 from concurrent.futures import ThreadPoolExecutor
@@ -26,6 +27,8 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
 ]
+# extra compiler flags, e.g. KB200_NVCC_EXTRA=-DKB200_TRACE for the kernels' timeline tracing
+NVCC_FLAGS += shlex.split(os.environ.get("KB200_NVCC_EXTRA", ""))
 
 
 def _nvcc() -> str:

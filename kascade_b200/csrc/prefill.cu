@@ -147,10 +147,30 @@ struct PfCfg {
   static constexpr bool kGather = MODE == kSparse;
   static constexpr int kThreads = kGather ? 512 : 384;
   static constexpr int kNK = kHasV ? 3 : kNKMax;
-  static constexpr int kProducerArrivals = kGather ? 128 : 1;
+  static constexpr int kProducerArrivals = kGather ? 128 : 1;   // Q tile: all gather threads
+  static constexpr int kRingArrivals = kGather ? 64 : 1;        // K / V stage: one warp pair each
   static constexpr int kProducerWarp0 = 8;
   static constexpr int kMmaWarp = kGather ? 12 : 9;
 };
+
+// Optional timeline tracing (compile with -DKB200_TRACE): up to four roles of CTA 0 record
+// (tag, clock64) pairs, read back by kb200_debug_trace.  Compiled out by default.
+#ifdef KB200_TRACE
+__device__ long long g_trace[4][2048][2];
+__device__ int g_trace_n[4];
+#define KB_TR_DECL int trn = 0
+#define KB_TR(role, tag)                                                     \
+  do {                                                                       \
+    if (blockIdx.x == 0 && trn < 2048) {                                     \
+      g_trace[role][trn][0] = (tag);                                         \
+      g_trace[role][trn][1] = clock64();                                     \
+      g_trace_n[role] = ++trn;                                               \
+    }                                                                        \
+  } while (0)
+#else
+#define KB_TR_DECL
+#define KB_TR(role, tag)
+#endif
 
 template <int MODE>
 __global__ void __launch_bounds__(PfCfg<MODE>::kThreads, 1)
@@ -191,8 +211,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   if (tid == 0) {
     mbar_init(&sh.bar_q, Cfg::kProducerArrivals);
     mbar_init(&sh.bar_qempty, 1);
-    for (int i = 0; i < kNK; ++i) { mbar_init(&bar_kfull[i], Cfg::kProducerArrivals); mbar_init(&bar_kempty[i], 1); }
-    for (int i = 0; i < kNV; ++i) { mbar_init(&bar_vfull[i], Cfg::kProducerArrivals); mbar_init(&bar_vempty[i], 1); }
+    for (int i = 0; i < kNK; ++i) { mbar_init(&bar_kfull[i], HAS_V ? Cfg::kRingArrivals : Cfg::kProducerArrivals); mbar_init(&bar_kempty[i], 1); }
+    for (int i = 0; i < kNV; ++i) { mbar_init(&bar_vfull[i], Cfg::kRingArrivals); mbar_init(&bar_vempty[i], 1); }
     // with V all 256 softmax threads work on the same block (column halves); without V each
     // warpgroup has its own blocks
     for (int i = 0; i < 3; ++i) {
@@ -228,7 +248,13 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   // core's reads with a proxy fence after its barrier wait.
   auto producer_gather = [&]() {
     const int pw = warp - Cfg::kProducerWarp0, ptid = tid - Cfg::kProducerWarp0 * 32;
-    int kc = 0, vc = 0, qn = 0;                          // blocks put into the K / V rings, Q tiles loaded
+    const bool is_v = pw >= 2;                           // warps 0,1 fill the K ring, warps 2,3 the V ring
+    const int half_rows = (pw & 1) * 64;                 // this warp's 64 rows of a 128-row stage
+    uint64_t* bar_full = is_v ? bar_vfull : bar_kfull;
+    uint64_t* bar_empty = is_v ? bar_vempty : bar_kempty;
+    const uint32_t ring_s = is_v ? v_s : k_s;
+    const int n_st = is_v ? kNV : kNK;
+    int st = 0, ph = 1, qn = 0;                          // ring position, parity of its "empty" phase; Q tiles loaded
     bool ok = true;
     for (int k = 0; k < n_rounds && ok; ++k) {
       const int item = item_of(k);
@@ -249,48 +275,40 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       }
       cp_arrive_noinc(&sh.bar_q);
       ++qn;
-      const __half* kb = p.k + (int64_t)it.b * p.k_sb + (int64_t)it.g * p.k_sh;
-      const __half* vb = p.v + (int64_t)it.b * p.v_sb + (int64_t)it.g * p.v_sh;
-      // key position of row (pw*32 + lane) of block j; index loads run two blocks ahead of their use
-      auto load_key = [&](int j) -> int {
-        const int s = j * 128 + pw * 32 + lane;
+      const __half* base = is_v ? p.v + (int64_t)it.b * p.v_sb + (int64_t)it.g * p.v_sh
+                                : p.k + (int64_t)it.b * p.k_sb + (int64_t)it.g * p.k_sh;
+      const int64_t tok_stride = is_v ? p.v_st : p.k_st;
+      // key positions of rows (half_rows + lane) and (half_rows + 32 + lane) of block j; the index
+      // loads run two blocks ahead of their use
+      auto load_key = [&](int j, int r) -> int {
+        const int s = j * 128 + half_rows + r * 32 + lane;
         if (j >= it.nb || s >= it.total) return 0;
         return s < it.count ? __ldg(it.idx_row + s) : it.tile_start + (s - it.count);
       };
-      int key_a = load_key(0), key_b = load_key(1);
+      int a0 = load_key(0, 0), a1 = load_key(0, 1), b0 = load_key(1, 0), b1 = load_key(1, 1);
       for (int j = 0; j < it.nb; ++j) {
-        int key = key_a;
-        key_a = key_b;
-        key_b = load_key(j + 2);
-        key = max(0, min(key, p.L - 1));
-        const int64_t offk = (int64_t)key * p.k_st, offv = (int64_t)key * p.v_st;
+        const int key0 = max(0, min(a0, p.L - 1)), key1 = max(0, min(a1, p.L - 1));
+        a0 = b0; a1 = b1;
+        b0 = load_key(j + 2, 0); b1 = load_key(j + 2, 1);
+        const int64_t off0 = (int64_t)key0 * tok_stride, off1 = (int64_t)key1 * tok_stride;
         const int c = lane & 15;
-        ok = mbar_wait(&bar_kempty[kc % kNK], ((kc / kNK) & 1) ^ 1, &give_up, 11);
+        ok = mbar_wait(&bar_empty[st], ph, &give_up, is_v ? 12 : 11);
         if (!ok) break;
-        {
-          const uint32_t dst = k_s + (kc % kNK) * kStageBytes;
+        const uint32_t dst = ring_s + st * kStageBytes;
 #pragma unroll 4
-          for (int i = 0; i < 16; ++i) {
-            const int rw = i * 2 + (lane >> 4);
-            const int64_t o = __shfl_sync(0xFFFFFFFFu, offk, rw);
-            cp16(dst + tile_off(pw * 32 + rw, c, 128), kb + o + c * 8);
-          }
-          cp_arrive_noinc(&bar_kfull[kc % kNK]);
-          ++kc;
+        for (int i = 0; i < 16; ++i) {
+          const int rw = i * 2 + (lane >> 4);
+          const int64_t o = __shfl_sync(0xFFFFFFFFu, off0, rw);
+          cp16(dst + tile_off(half_rows + rw, c, 128), base + o + c * 8);
         }
-        ok = mbar_wait(&bar_vempty[vc % kNV], ((vc / kNV) & 1) ^ 1, &give_up, 12);
-        if (!ok) break;
-        {
-          const uint32_t dst = v_s + (vc % kNV) * kStageBytes;
 #pragma unroll 4
-          for (int i = 0; i < 16; ++i) {
-            const int rw = i * 2 + (lane >> 4);
-            const int64_t o = __shfl_sync(0xFFFFFFFFu, offv, rw);
-            cp16(dst + tile_off(pw * 32 + rw, c, 128), vb + o + c * 8);
-          }
-          cp_arrive_noinc(&bar_vfull[vc % kNV]);
-          ++vc;
+        for (int i = 0; i < 16; ++i) {
+          const int rw = i * 2 + (lane >> 4);
+          const int64_t o = __shfl_sync(0xFFFFFFFFu, off1, rw);
+          cp16(dst + tile_off(half_rows + 32 + rw, c, 128), base + o + c * 8);
         }
+        cp_arrive_noinc(&bar_full[st]);
+        if (++st == n_st) { st = 0; ph ^= 1; }
       }
     }
     cp_wait_all();                                       // nothing of this CTA is in flight at teardown
@@ -300,11 +318,10 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   // Tensor-map dimensions are (d, head, token, batch); a K/V tile is two boxes of 64 x 1 x 128 x 1 (the
   // two 64-column halves of the operand tile), a Q tile two boxes of 64 x 4 x 32 x 1 whose rows come
   // out as row = 4 * token + head.  Rows past the prompt are zero-filled by the copy engine.
-  auto producer_tma = [&]() {
+  auto producer_tma = [&]() {                          // Q tiles and the K ring
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
-    if (HAS_V) tma_prefetch_desc(&tm_v);
-    int kc = 0, vc = 0, qn = 0;
+    int st = 0, ph = 1, qn = 0;
     bool ok = true;
     for (int k = 0; k < n_rounds && ok; ++k) {
       const int item = item_of(k);
@@ -318,26 +335,34 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       tma_load_4d(q_s + kStageBytes / 2, &tm_q, 64, it.g * kHg, it.tile_start, it.b, &sh.bar_q);
       ++qn;
       for (int j = 0; j < it.nb; ++j) {
-        ok = mbar_wait(&bar_kempty[kc % kNK], ((kc / kNK) & 1) ^ 1, &give_up, 11);
+        ok = mbar_wait(&bar_kempty[st], ph, &give_up, 11);
         if (!ok) break;
-        {
-          const uint32_t dst = k_s + (kc % kNK) * kStageBytes;
-          uint64_t* bar = &bar_kfull[kc % kNK];
-          mbar_arrive_expect_tx(bar, kStageBytes);
-          tma_load_4d(dst, &tm_k, 0, it.g, j * 128, it.b, bar);
-          tma_load_4d(dst + kStageBytes / 2, &tm_k, 64, it.g, j * 128, it.b, bar);
-          ++kc;
-        }
-        if (HAS_V) {
-          ok = mbar_wait(&bar_vempty[vc % kNV], ((vc / kNV) & 1) ^ 1, &give_up, 12);
-          if (!ok) break;
-          const uint32_t dst = v_s + (vc % kNV) * kStageBytes;
-          uint64_t* bar = &bar_vfull[vc % kNV];
-          mbar_arrive_expect_tx(bar, kStageBytes);
-          tma_load_4d(dst, &tm_v, 0, it.g, j * 128, it.b, bar);
-          tma_load_4d(dst + kStageBytes / 2, &tm_v, 64, it.g, j * 128, it.b, bar);
-          ++vc;
-        }
+        const uint32_t dst = k_s + st * kStageBytes;
+        uint64_t* bar = &bar_kfull[st];
+        mbar_arrive_expect_tx(bar, kStageBytes);
+        tma_load_4d(dst, &tm_k, 0, it.g, j * 128, it.b, bar);
+        tma_load_4d(dst + kStageBytes / 2, &tm_k, 64, it.g, j * 128, it.b, bar);
+        if (++st == kNK) { st = 0; ph ^= 1; }
+      }
+    }
+  };
+  auto producer_tma_v = [&]() {                        // the V ring, independent of the K ring's progress
+    tma_prefetch_desc(&tm_v);
+    int st = 0, ph = 1;
+    bool ok = true;
+    for (int k = 0; k < n_rounds && ok; ++k) {
+      const int item = item_of(k);
+      if (item >= n_items) continue;
+      const TileItem it = decode_item<MODE>(p, item);
+      for (int j = 0; j < it.nb; ++j) {
+        ok = mbar_wait(&bar_vempty[st], ph, &give_up, 12);
+        if (!ok) break;
+        const uint32_t dst = v_s + st * kStageBytes;
+        uint64_t* bar = &bar_vfull[st];
+        mbar_arrive_expect_tx(bar, kStageBytes);
+        tma_load_4d(dst, &tm_v, 0, it.g, j * 128, it.b, bar);
+        tma_load_4d(dst + kStageBytes / 2, &tm_v, 64, it.g, j * 128, it.b, bar);
+        if (++st == kNV) { st = 0; ph ^= 1; }
       }
     }
   };
@@ -350,6 +375,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     int issued0 = 0, issued1 = 0;                      // Q.K^T blocks written into S buffer 0 / 1 so far
     int released0 = 0, released1 = 0;                  // ... and how many of them the softmax side consumed
     bool ok = true;
+    // the whole warp runs this role with uniform control flow; one elected lane issues
+    const bool el = elect_one();
     // S buffer w may be overwritten once every block issued into it has been consumed
     auto wait_s_free = [&](int w) -> bool {
       int& rel = w ? released1 : released0;
@@ -365,17 +392,20 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (!mbar_wait(&bar_kfull[kc % kNK], (kc / kNK) & 1, &give_up, 22)) return false;
       if (GATHER) fence_proxy_async_smem();            // cp.async bytes -> visible to the tensor core
       tc_fence_after();
-      const uint32_t ks_addr = k_s + (kc % kNK) * kStageBytes;
+      const uint32_t k_lo = desc_lo(k_s, 16) + (kc % kNK) * (kStageBytes >> 4);
+      const uint32_t q_lo = desc_lo(q_s, 16);
       const uint32_t d = t_s0 + w * 128;
+      if (el) {
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t off = (ks >> 2) * (kStageBytes / 2) + (ks & 3) * 32;
-        const uint64_t dq = desc_kmajor(q_s + off), dk = desc_kmajor(ks_addr + off);
-        if (POOL) mma_ss(d, dk, dq, idesc_qk, ks > 0);     // S^T: lanes = keys
-        else mma_ss(d, dq, dk, idesc_qk, ks > 0);          // S: lanes = (query, head) rows
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t off = (ks >> 2) * (kStageBytes / 2 / 16) + (ks & 3) * 2;
+          if (POOL) mma_ss_lo(d, k_lo + off, q_lo + off, idesc_qk, ks > 0);     // S^T: lanes = keys
+          else mma_ss_lo(d, q_lo + off, k_lo + off, idesc_qk, ks > 0);          // S: lanes = (query, head) rows
+        }
+        mma_commit(&bar_kempty[kc % kNK]);
+        mma_commit(&bar_sfull[w]);
       }
-      mma_commit(&bar_kempty[kc % kNK]);
-      mma_commit(&bar_sfull[w]);
+      __syncwarp();
       ++kc;
       if (w) ++issued1; else ++issued0;
       return true;
@@ -390,13 +420,13 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (GATHER) fence_proxy_async_smem();
       ++qn;
       ok = issue_qk(0);
-      if (ok && it.nb == 1) mma_commit(&sh.bar_qempty);  // the tile's last Q.K^T is queued: Q may be replaced
+      if (ok && it.nb == 1 && el) mma_commit(&sh.bar_qempty);  // the tile's last Q.K^T is queued: Q may be replaced
       for (int j = 0; j < it.nb && ok; ++j) {
         const int w = j & 1;
         if (j + 1 < it.nb) {
           ok = issue_qk((j + 1) & 1);
           if (!ok) break;
-          if (j + 2 == it.nb) mma_commit(&sh.bar_qempty);
+          if (j + 2 == it.nb && el) mma_commit(&sh.bar_qempty);
         }
         if (HAS_V) {
           // P(j) is in tensor memory (and S(j) has been consumed)
@@ -437,29 +467,23 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   // columns, row maximum exchanged through shared memory) and the blocks rotate through three S
   // buffers (S0, S1, S2 = 384 columns, O = 128 columns): Q.K^T runs two blocks ahead of the softmax,
   // P.V one block behind it, and the softmax of consecutive blocks is back to back.
-  auto mma_role_v = [&]() {
+  // Two warps issue: one the Q.K^T products, one the P.V products.  An issuing lane is held up while
+  // the tensor core works through what it was given, so a single issuer would spend its barrier
+  // waits with the tensor core idle; with two, each warp waits while the other's products run.
+  // Products of different warps are not ordered: Q.K^T(b) overwrites the buffer of block b-3 and
+  // therefore waits for P.V(b-3) explicitly.
+  auto mma_qk_v = [&]() {
+    KB_TR_DECL;
     constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
-    constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
-    const uint32_t t_acc = tmem + 384;
-    int kc = 0, vc = 0, qn = 0, tiles_done = 0, sc = 0, pc = 0;   // sc / pc: blocks issued / consumed so far
+    constexpr uint32_t kStage16 = kStageBytes >> 4;      // descriptor address units are 16 bytes
+    const uint32_t q_lo = desc_lo(q_s, 16), k_lo0 = desc_lo(k_s, 16);
+    // ring positions and phase parities are kept incrementally: K ring, S buffers
+    int k_st = 0, k_ph = 0, s_st = 0, s_wrap = 0, qn = 0;
     bool ok = true;
-    auto issue_qk = [&]() -> bool {
-      if (!mbar_wait(&bar_kfull[kc % kNK], (kc / kNK) & 1, &give_up, 22)) return false;
-      if (GATHER) fence_proxy_async_smem();            // cp.async bytes -> visible to the tensor core
-      tc_fence_after();
-      const uint32_t ks_addr = k_s + (kc % kNK) * kStageBytes;
-      const uint32_t d = t_s0 + (sc % 3) * 128;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t off = (ks >> 2) * (kStageBytes / 2) + (ks & 3) * 32;
-        mma_ss(d, desc_kmajor(q_s + off), desc_kmajor(ks_addr + off), idesc_qk, ks > 0);
-      }
-      mma_commit(&bar_kempty[kc % kNK]);
-      mma_commit(&bar_sfull[sc % 3]);
-      ++kc;
-      ++sc;
-      return true;
-    };
+    // The whole warp runs this role with uniform control flow and one elected lane issues: addresses,
+    // descriptors and ring positions are then warp-uniform values, which is what lets the tensor
+    // core be fed at its own rate (a single diverged lane computing them per instruction cannot).
+    const bool el = elect_one();
     for (int k = 0; k < n_rounds && ok; ++k) {
       const int item = item_of(k);
       if (item >= n_items) continue;
@@ -467,49 +491,89 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (it.nb == 0) continue;
       ok = mbar_wait(&sh.bar_q, qn & 1, &give_up, 21);
       if (!ok) break;
-      if (GATHER) fence_proxy_async_smem();
       ++qn;
-      // S buffer (sc % 3) last held block sc - 3, whose P.V was issued before (in order)
-      int issued = 0;
-      for (; issued < 2 && issued < it.nb && ok; ++issued) ok = issue_qk();
-      if (ok && issued == it.nb) mma_commit(&sh.bar_qempty);   // the tile's last Q.K^T is queued: Q may be replaced
-      for (int j = 0; j < it.nb && ok; ++j) {
-        if (issued < it.nb) {
-          ok = issue_qk();
+      for (int j = 0; j < it.nb; ++j) {
+        if (s_wrap > 0) {
+          // S buffer s_st held block (this one - 3): its P.V must have read P out of it
+          ok = mbar_wait(&bar_odone[s_st], (s_wrap - 1) & 1, &give_up, 23);
           if (!ok) break;
-          if (++issued == it.nb) mma_commit(&sh.bar_qempty);
         }
-        // P(j) is in tensor memory (and S(j) has been consumed)
-        ok = mbar_wait(&bar_pready[pc % 3], (pc / 3) & 1, &give_up, 24);
+        ok = mbar_wait(&bar_kfull[k_st], k_ph, &give_up, 22);
         if (!ok) break;
-        ok = mbar_wait(&bar_vfull[vc % kNV], (vc / kNV) & 1, &give_up, 25);
+        if (GATHER) fence_proxy_async_smem();            // cp.async bytes -> visible to the tensor core
+        tc_fence_after();
+        if (lane == 0) KB_TR(2, 10);
+        const uint32_t k_lo = k_lo0 + k_st * kStage16;
+        const uint32_t d = t_s0 + s_st * 128;
+        if (el) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            constexpr uint32_t kHalf16 = kStageBytes / 2 / 16;
+            const uint32_t off = (ks >> 2) * kHalf16 + (ks & 3) * 2;
+            mma_ss_lo(d, q_lo + off, k_lo + off, idesc_qk, ks > 0);
+          }
+          mma_commit(&bar_kempty[k_st]);
+          mma_commit(&bar_sfull[s_st]);
+          if (j + 1 == it.nb) mma_commit(&sh.bar_qempty);  // the tile's last Q.K^T is queued: Q may be replaced
+        }
+        __syncwarp();
+        if (lane == 0) KB_TR(2, 11);
+        if (++k_st == kNK) { k_st = 0; k_ph ^= 1; }
+        if (++s_st == 3) { s_st = 0; ++s_wrap; }
+      }
+    }
+  };
+  auto mma_pv_v = [&]() {
+    KB_TR_DECL;
+    constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
+    constexpr uint32_t kStage16 = kStageBytes >> 4;
+    const uint32_t t_acc = tmem + 384;
+    const uint32_t v_lo0 = desc_lo(v_s, kStageBytes / 2);
+    int v_st = 0, v_ph = 0, p_st = 0, p_ph = 0, tiles_done = 0;
+    bool ok = true;
+    const bool el = elect_one();
+    for (int k = 0; k < n_rounds && ok; ++k) {
+      const int item = item_of(k);
+      if (item >= n_items) continue;
+      const TileItem it = decode_item<MODE>(p, item);
+      if (it.nb == 0) continue;
+      for (int j = 0; j < it.nb; ++j) {
+        ok = mbar_wait(&bar_vfull[v_st], v_ph, &give_up, 25);
         if (!ok) break;
         if (j == 0 && tiles_done > 0) {
           // the first P.V of a new tile overwrites O: the previous tile's epilogue must have read it
           ok = mbar_wait(&sh.bar_ofree, (tiles_done - 1) & 1, &give_up, 26);
           if (!ok) break;
         }
+        // P(j) is in tensor memory (and S(j) has been consumed)
+        ok = mbar_wait(&bar_pready[p_st], p_ph, &give_up, 24);
+        if (!ok) break;
+        if (lane == 0) KB_TR(3, 13);
         if (GATHER) fence_proxy_async_smem();
         tc_fence_after();
-        const uint32_t vs_addr = v_s + (vc % kNV) * kStageBytes;
-        const uint32_t a = t_s0 + (pc % 3) * 128;
+        const uint32_t v_lo = v_lo0 + v_st * kStage16;
+        const uint32_t a = t_s0 + p_st * 128;
+        if (el) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          mma_ts(t_acc, a + ks * 8, desc_mnmajor(vs_addr + ks * 2048, kStageBytes / 2), idesc_pv,
-                 (j > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < 8; ++ks)
+            mma_ts_lo(t_acc, a + ks * 8, v_lo + ks * (2048 >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          mma_commit(&bar_vempty[v_st]);
+          // up to three P.V can be in flight; a wait names a phase only by its parity, so consecutive
+          // P.V signal three different barriers and a waiter is never more than one phase behind
+          mma_commit(&bar_odone[p_st]);
         }
-        mma_commit(&bar_vempty[vc % kNV]);
-        // up to three P.V can be in flight; a wait names a phase only by its parity, so consecutive
-        // P.V signal three different barriers and a waiter is never more than one phase behind
-        mma_commit(&bar_odone[pc % 3]);
-        ++vc;
-        ++pc;
+        __syncwarp();
+        if (lane == 0) KB_TR(3, 14);
+        if (++v_st == kNV) { v_st = 0; v_ph ^= 1; }
+        if (++p_st == 3) { p_st = 0; p_ph ^= 1; }
       }
+      if (!ok) break;
       ++tiles_done;
     }
   };
 
   auto softmax_role_v = [&]() {
+    KB_TR_DECL;
     const int half = warp >> 2;                        // which 64 of the 128 columns
     const int row = (warp & 3) * 32 + lane, q_local = row >> 2;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
@@ -530,9 +594,11 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         if (!ok) break;
       }
       for (int j = 0; j < it.nb; ++j, ++bc) {
+        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 0);
         ok = mbar_wait(&bar_sfull[bc % 3], (bc / 3) & 1, &give_up, 31);
         if (!ok) break;
         tc_fence_after();
+        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 1);
         const uint32_t ts = t_s0 + (bc % 3) * 128 + lane_sel;
         const int c0 = j * 128 + half * 64 - off;         // key position (inside the tile) of this thread's column 0
         const bool need_mask = (c0 + 63) > 0;             // only the last block(s) of a tile
@@ -540,6 +606,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         tmem_ld32(ts + half * 64, sr[0]);
         tmem_ld32(ts + half * 64 + 32, sr[1]);
         tmem_wait_ld();
+        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 2);
         if (need_mask) {
 #pragma unroll
           for (int part = 0; part < 2; ++part)
@@ -562,9 +629,11 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         // both halves of a row must use the same reference: exchange the half-row maxima (this also
         // orders the other half's S loads before this half's P stores into the shared buffer)
         sh.xchg[bc & 1][half][row] = mx;
+        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 3);
         mbar_arrive(&sh.bar_lse[bc & 1]);
         ok = mbar_wait(&sh.bar_lse[bc & 1], (bc >> 1) & 1, &give_up, 34);
         if (!ok) break;
+        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 4);
         mx = fmaxf(mx, sh.xchg[bc & 1][half ^ 1][row]) * p.scale2;
         // The reference point of the exponentials only moves when the row maximum has grown by more
         // than 2^kRescaleLog2: probabilities then stay below 2^kRescaleLog2 (exact in fp32, harmless in
@@ -591,6 +660,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         }
         l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
         m_run = m_new;
+        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 5);
         if (j > 0 && !__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
           // the previous P.V must have landed in O before this thread's 64 columns of O are rescaled
           ok = mbar_wait(&bar_odone[(bc - 1) % 3], ((bc - 1) / 3) & 1, &give_up, 32);
@@ -607,6 +677,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
           }
         }
         tmem_wait_st();
+        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 6);
         tc_fence_before();
         mbar_arrive(&bar_pready[bc % 3]);
       }
@@ -902,8 +973,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       producer_gather();
     } else {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 48;\n");
-      if (warp == kMmaWarp && lane == 0) { if (HAS_V) mma_role_v(); else mma_role(); }
-      __syncwarp();
+      if (warp == kMmaWarp) mma_qk_v();
+      else if (warp == kMmaWarp + 1) mma_pv_v();
     }
   } else {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 96;\n");
@@ -911,8 +982,12 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (lane == 0) producer_tma();
       __syncwarp();
     } else if (warp == kMmaWarp) {
-      if (lane == 0) { if (HAS_V) mma_role_v(); else mma_role(); }
+      if (HAS_V) mma_qk_v(); else mma_role();
+    } else if (HAS_V && warp == kMmaWarp + 1) {
+      if (lane == 0) producer_tma_v();
       __syncwarp();
+    } else if (HAS_V && warp == kMmaWarp + 2) {
+      mma_pv_v();
     }
   }
 
@@ -998,6 +1073,15 @@ static int check_shape(int batch, int seq_len, int H, int G) {
 
 }  // namespace kb200
 
+#ifdef KB200_TRACE
+extern "C" int kb200_debug_trace(long long* buf, int* cnt) {
+  cudaMemcpyFromSymbol(buf, kb200::g_trace, sizeof(long long) * 4 * 2048 * 2);
+  cudaMemcpyFromSymbol(cnt, kb200::g_trace_n, sizeof(int) * 4);
+  int z[4] = {0, 0, 0, 0};
+  cudaMemcpyToSymbol(kb200::g_trace_n, z, sizeof(z));
+  return 0;
+}
+#endif
 extern "C" int kb200_read_status(int* host_out) {
   using namespace kb200;
   KB_REQUIRE(host_out, "read_status: null pointer");
