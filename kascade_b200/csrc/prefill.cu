@@ -92,11 +92,11 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 // the 7 x 32 KB tiles, the alignment padding and this block together stay inside the 227 KB limit.
 struct PfShared {
   uint64_t bar_q, bar_qempty, bar_kfull[kNKMax], bar_kempty[kNKMax], bar_vfull[kNV], bar_vempty[kNV];
-  uint64_t bar_sfull[3], bar_pready[3], bar_odone[3], bar_x, bar_ofree, bar_lse[2];
+  uint64_t bar_sfull[3], bar_pready[3], bar_odone[3], bar_x, bar_ofree, bar_lse[2], bar_sfree[2];
   uint32_t tmem;
   int give_up;
   union {
-    float xchg[2][2][128];                             // softmax modes: [m | l][warpgroup][row]
+    float xchg[2][2][128];                             // softmax modes: [m (with V: row reference) | l][warpgroup][row]
     float lse[2][2][128];                              // pool mode: lse2 of the tile's rows [warpgroup][tile parity]
   };
 };
@@ -213,14 +213,13 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     mbar_init(&sh.bar_qempty, 1);
     for (int i = 0; i < kNK; ++i) { mbar_init(&bar_kfull[i], HAS_V ? Cfg::kRingArrivals : Cfg::kProducerArrivals); mbar_init(&bar_kempty[i], 1); }
     for (int i = 0; i < kNV; ++i) { mbar_init(&bar_vfull[i], Cfg::kRingArrivals); mbar_init(&bar_vempty[i], 1); }
-    // with V all 256 softmax threads work on the same block (column halves); without V each
-    // warpgroup has its own blocks
+    // each softmax warpgroup (128 threads) owns every other key block of a tile
     for (int i = 0; i < 3; ++i) {
       mbar_init(&bar_sfull[i], 1);
-      mbar_init(&bar_pready[i], HAS_V ? kSoftmaxThreads : 128);
+      mbar_init(&bar_pready[i], 128);
       mbar_init(&bar_odone[i], 1);
     }
-    for (int i = 0; i < 2; ++i) mbar_init(&sh.bar_lse[i], HAS_V ? kSoftmaxThreads : 128);
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh.bar_lse[i], 128); mbar_init(&sh.bar_sfree[i], 128); }
     mbar_init(&sh.bar_x, kSoftmaxThreads);
     mbar_init(&sh.bar_ofree, kSoftmaxThreads);
     mbar_fence_init();
@@ -467,18 +466,21 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   // columns, row maximum exchanged through shared memory) and the blocks rotate through three S
   // buffers (S0, S1, S2 = 384 columns, O = 128 columns): Q.K^T runs two blocks ahead of the softmax,
   // P.V one block behind it, and the softmax of consecutive blocks is back to back.
+  // Tensor-memory columns with V: S0, S1 (fp32, 2 x 128) | P0, P1 (fp16 pairs, 2 x 64) | O (fp32, 128).
+  // Even key blocks of a tile go through (S0, P0), odd ones through (S1, P1); there is ONE accumulator.
+  //
   // Two warps issue: one the Q.K^T products, one the P.V products.  An issuing lane is held up while
   // the tensor core works through what it was given, so a single issuer would spend its barrier
   // waits with the tensor core idle; with two, each warp waits while the other's products run.
-  // Products of different warps are not ordered: Q.K^T(b) overwrites the buffer of block b-3 and
-  // therefore waits for P.V(b-3) explicitly.
+  // Products of different warps are not ordered; every dependency between them goes through a
+  // barrier (S consumed -> next Q.K^T into that buffer; P written -> P.V; P.V done -> P rewritten).
   auto mma_qk_v = [&]() {
     KB_TR_DECL;
     constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
     constexpr uint32_t kStage16 = kStageBytes >> 4;      // descriptor address units are 16 bytes
     const uint32_t q_lo = desc_lo(q_s, 16), k_lo0 = desc_lo(k_s, 16);
-    // ring positions and phase parities are kept incrementally: K ring, S buffers
-    int k_st = 0, k_ph = 0, s_st = 0, s_wrap = 0, qn = 0;
+    int k_st = 0, k_ph = 0, qn = 0;                      // K ring position / parity, Q tiles seen
+    int iss0 = 0, iss1 = 0;                              // blocks issued into S0 / S1 so far
     bool ok = true;
     // The whole warp runs this role with uniform control flow and one elected lane issues: addresses,
     // descriptors and ring positions are then warp-uniform values, which is what lets the tensor
@@ -493,9 +495,11 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (!ok) break;
       ++qn;
       for (int j = 0; j < it.nb; ++j) {
-        if (s_wrap > 0) {
-          // S buffer s_st held block (this one - 3): its P.V must have read P out of it
-          ok = mbar_wait(&bar_odone[s_st], (s_wrap - 1) & 1, &give_up, 23);
+        const int w = j & 1;
+        int& iss = w ? iss1 : iss0;
+        if (iss > 0) {
+          // the softmax side has the previous block of this buffer in registers
+          ok = mbar_wait(&sh.bar_sfree[w], (iss - 1) & 1, &give_up, 23);
           if (!ok) break;
         }
         ok = mbar_wait(&bar_kfull[k_st], k_ph, &give_up, 22);
@@ -504,7 +508,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         tc_fence_after();
         if (lane == 0) KB_TR(2, 10);
         const uint32_t k_lo = k_lo0 + k_st * kStage16;
-        const uint32_t d = t_s0 + s_st * 128;
+        const uint32_t d = t_s0 + w * 128;
         if (el) {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
@@ -513,13 +517,13 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
             mma_ss_lo(d, q_lo + off, k_lo + off, idesc_qk, ks > 0);
           }
           mma_commit(&bar_kempty[k_st]);
-          mma_commit(&bar_sfull[s_st]);
+          mma_commit(&bar_sfull[w]);
           if (j + 1 == it.nb) mma_commit(&sh.bar_qempty);  // the tile's last Q.K^T is queued: Q may be replaced
         }
         __syncwarp();
         if (lane == 0) KB_TR(2, 11);
+        ++iss;
         if (++k_st == kNK) { k_st = 0; k_ph ^= 1; }
-        if (++s_st == 3) { s_st = 0; ++s_wrap; }
       }
     }
   };
@@ -527,9 +531,10 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     KB_TR_DECL;
     constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
     constexpr uint32_t kStage16 = kStageBytes >> 4;
-    const uint32_t t_acc = tmem + 384;
+    const uint32_t t_acc = tmem + 384, t_p = tmem + 256;
     const uint32_t v_lo0 = desc_lo(v_s, kStageBytes / 2);
-    int v_st = 0, v_ph = 0, p_st = 0, p_ph = 0, tiles_done = 0;
+    int v_st = 0, v_ph = 0, tiles_done = 0;
+    int cons0 = 0, cons1 = 0;                            // blocks consumed from P0 / P1 so far
     bool ok = true;
     const bool el = elect_one();
     for (int k = 0; k < n_rounds && ok; ++k) {
@@ -538,6 +543,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       const TileItem it = decode_item<MODE>(p, item);
       if (it.nb == 0) continue;
       for (int j = 0; j < it.nb; ++j) {
+        const int w = j & 1;
+        int& cons = w ? cons1 : cons0;
         ok = mbar_wait(&bar_vfull[v_st], v_ph, &give_up, 25);
         if (!ok) break;
         if (j == 0 && tiles_done > 0) {
@@ -545,40 +552,55 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
           ok = mbar_wait(&sh.bar_ofree, (tiles_done - 1) & 1, &give_up, 26);
           if (!ok) break;
         }
-        // P(j) is in tensor memory (and S(j) has been consumed)
-        ok = mbar_wait(&bar_pready[p_st], p_ph, &give_up, 24);
+        // P(j) is in tensor memory, and O is in the scale P(j) was computed in
+        ok = mbar_wait(&bar_pready[w], cons & 1, &give_up, 24);
         if (!ok) break;
         if (lane == 0) KB_TR(3, 13);
         if (GATHER) fence_proxy_async_smem();
         tc_fence_after();
         const uint32_t v_lo = v_lo0 + v_st * kStage16;
-        const uint32_t a = t_s0 + p_st * 128;
+        const uint32_t a = t_p + w * 64;
         if (el) {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             mma_ts_lo(t_acc, a + ks * 8, v_lo + ks * (2048 >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
           mma_commit(&bar_vempty[v_st]);
-          // up to three P.V can be in flight; a wait names a phase only by its parity, so consecutive
-          // P.V signal three different barriers and a waiter is never more than one phase behind
-          mma_commit(&bar_odone[p_st]);
+          mma_commit(&bar_odone[w]);
         }
         __syncwarp();
         if (lane == 0) KB_TR(3, 14);
+        ++cons;
         if (++v_st == kNV) { v_st = 0; v_ph ^= 1; }
-        if (++p_st == 3) { p_st = 0; p_ph ^= 1; }
       }
       if (!ok) break;
       ++tiles_done;
     }
   };
 
+  // Softmax with V.  Warpgroup w owns the key blocks j = w, w+2, ... of every tile: a thread holds a
+  // whole S row (128 values) of its block, so nothing is exchanged inside a block, and the two
+  // warpgroups are naturally out of phase (one fetches and reduces while the other's exponentials
+  // keep the special-function unit busy).  S(j) is free for Q.K^T(j+2) as soon as it is in
+  // registers; P goes to its own tensor-memory buffer.
+  //
+  // Both streams accumulate into ONE O, so every row has one reference point for its exponentials,
+  // decided block by block in block order: ref(j) = ref(j-1), unless the maximum of block j exceeds
+  // it by more than 2^kRescaleLog2, then ref(j) = that maximum.  The owner of block j reads ref(j-1)
+  // from the other warpgroup (published right after that block's maximum was known, long before its
+  // exponentials are done) and publishes ref(j).  Where ref(j) != ref(j-1), which is rare, the owner of
+  // block j waits for P.V(j-1) and rescales its O row before it releases P(j).  Each thread keeps
+  // its part of the row sum in the reference of its own last block; the parts meet in the epilogue.
   auto softmax_role_v = [&]() {
     KB_TR_DECL;
-    const int half = warp >> 2;                        // which 64 of the 128 columns
+    const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane, q_local = row >> 2;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t t_acc = tmem + 384 + lane_sel + half * 64;   // this thread's 64 columns of O
-    int bc = 0, tiles_done = 0;                        // blocks / tiles finished so far
+    const uint32_t ts = t_s0 + wg * 128 + lane_sel;           // this stream's S buffer
+    const uint32_t tp = tmem + 256 + wg * 64 + lane_sel;      // this stream's P buffer
+    const uint32_t t_acc = tmem + 384 + lane_sel;             // the O accumulator (this thread's row)
+    float* ref_mine = &sh.xchg[0][wg][row];
+    const float* ref_other = &sh.xchg[0][wg ^ 1][row];
+    int done_mine = 0, done_other = 0, tiles_done = 0;        // blocks finished per stream, tiles finished
     bool ok = true;
     for (int k = 0; k < n_rounds && ok; ++k) {
       const int item = item_of(k);
@@ -587,118 +609,138 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (it.nb == 0) continue;
       const int tok = it.tile_start + q_local;
       const int off = GATHER ? it.count : it.tile_start;   // slot - off = key position inside the tile
-      float m_run = -INFINITY, l_run = 0.f;             // m_run: reference of the row (both halves agree)
-      // the exchange buffer is free once both halves have finished the previous tile's epilogue
+      const int n_mine = (it.nb - wg + 1) >> 1, n_other = it.nb - n_mine;
+      float m_l = -INFINITY, l_run = 0.f;               // l_run is in the scale of reference m_l
+      // the exchange buffer (and O) are free once both warpgroups have finished the previous tile's epilogue
       if (tiles_done > 0) {
         ok = mbar_wait(&sh.bar_ofree, (tiles_done - 1) & 1, &give_up, 37);
         if (!ok) break;
       }
-      for (int j = 0; j < it.nb; ++j, ++bc) {
-        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 0);
-        ok = mbar_wait(&bar_sfull[bc % 3], (bc / 3) & 1, &give_up, 31);
+      for (int j = wg, jj = 0; j < it.nb; j += 2, ++jj) {
+        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 0);
+        ok = mbar_wait(&bar_sfull[wg], (done_mine + jj) & 1, &give_up, 31);
         if (!ok) break;
         tc_fence_after();
-        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 1);
-        const uint32_t ts = t_s0 + (bc % 3) * 128 + lane_sel;
-        const int c0 = j * 128 + half * 64 - off;         // key position (inside the tile) of this thread's column 0
-        const bool need_mask = (c0 + 63) > 0;             // only the last block(s) of a tile
-        uint32_t sr[2][32];
-        tmem_ld32(ts + half * 64, sr[0]);
-        tmem_ld32(ts + half * 64 + 32, sr[1]);
+        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 1);
+        // the whole S row (128 fp32) comes into registers with one round trip to tensor memory
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int part = 0; part < 4; ++part) tmem_ld32(ts + part * 32, sr[part]);
         tmem_wait_ld();
-        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 2);
-        if (need_mask) {
+        tc_fence_before();
+        mbar_arrive(&sh.bar_sfree[wg]);                   // Q.K^T(j+2) may overwrite the buffer
+        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 2);
+        const int c0 = j * 128 - off;                     // key position (inside the tile) of column 0
+        if ((c0 + 127) > 0) {                             // only the last block(s) of a tile
 #pragma unroll
-          for (int part = 0; part < 2; ++part)
+          for (int part = 0; part < 4; ++part)
 #pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if ((c0 + part * 32 + e) > q_local) sr[part][e] = 0xFF800000u;     // -inf
+            for (int i = 0; i < 32; ++i)
+              if ((c0 + part * 32 + i) > q_local) sr[part][i] = 0xFF800000u;     // -inf
         }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {
+        for (int part = 0; part < 4; ++part) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(sr[part][e]));
-            mx1 = fmaxf(mx1, __uint_as_float(sr[part][e + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(sr[part][e + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(sr[part][e + 3]));
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(sr[part][i]));
+            mx1 = fmaxf(mx1, __uint_as_float(sr[part][i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(sr[part][i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(sr[part][i + 3]));
           }
         }
-        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        // both halves of a row must use the same reference: exchange the half-row maxima (this also
-        // orders the other half's S loads before this half's P stores into the shared buffer)
-        sh.xchg[bc & 1][half][row] = mx;
-        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 3);
-        mbar_arrive(&sh.bar_lse[bc & 1]);
-        ok = mbar_wait(&sh.bar_lse[bc & 1], (bc >> 1) & 1, &give_up, 34);
-        if (!ok) break;
-        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 4);
-        mx = fmaxf(mx, sh.xchg[bc & 1][half ^ 1][row]) * p.scale2;
-        // The reference point of the exponentials only moves when the row maximum has grown by more
-        // than 2^kRescaleLog2: probabilities then stay below 2^kRescaleLog2 (exact in fp32, harmless in
-        // fp16), and the O accumulator is rescaled only on those rare blocks.  lse2 = m + log2(l) holds
-        // for any reference point m.
-        const float m_new = (mx > m_run + kRescaleLog2) ? mx : m_run;
-        const float alpha = ex2(m_run - m_new);
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale2;
+        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 3);
+        // ---- the row's reference for this block --------------------------------------------------
+        // index (in the other stream's count) of block j-1: the other stream owns j-1, j-3, ...
+        const int prev_idx = done_other + ((j - 1) >> 1);
+        float ref_prev = -INFINITY;
+        if (j > 0) {
+          ok = mbar_wait(&sh.bar_lse[wg ^ 1], prev_idx & 1, &give_up, 34);
+          if (!ok) break;
+          ref_prev = *ref_other;
+        }
+        // Probabilities stay below 2^kRescaleLog2 (exact in fp32, harmless in fp16).  A block whose
+        // rows are all masked for this thread (maximum -inf) keeps the previous reference.
+        const float ref = (mx > ref_prev + kRescaleLog2) ? mx : ref_prev;
+        *ref_mine = ref;
+        mbar_arrive(&sh.bar_lse[wg]);
+        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 4);
+        // P.V of this stream's previous block has read the P buffer
+        if (done_mine + jj > 0) {
+          ok = mbar_wait(&bar_odone[wg], (done_mine + jj - 1) & 1, &give_up, 38);
+          if (!ok) break;
+        }
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {             // 32 keys -> 16 packed P columns
+        for (int part = 0; part < 4; ++part) {             // 32 keys -> 16 packed P columns
           uint32_t pr[16];
 #pragma unroll
-          for (int e = 0; e < 16; e += 2) {
-            float a0 = ex2(fmaf(__uint_as_float(sr[part][2 * e]), p.scale2, -m_new));
-            float a1 = ex2(fmaf(__uint_as_float(sr[part][2 * e + 1]), p.scale2, -m_new));
-            float a2 = ex2(fmaf(__uint_as_float(sr[part][2 * e + 2]), p.scale2, -m_new));
-            float a3 = ex2(fmaf(__uint_as_float(sr[part][2 * e + 3]), p.scale2, -m_new));
+          for (int i = 0; i < 16; i += 2) {
+            float a0 = ex2(fmaf(__uint_as_float(sr[part][2 * i]), p.scale2, -ref));
+            float a1 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 1]), p.scale2, -ref));
+            float a2 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 2]), p.scale2, -ref));
+            float a3 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 3]), p.scale2, -ref));
             s0 += a0; s1 += a1; s2 += a2; s3 += a3;
-            pr[e] = pack2(a0, a1);
-            pr[e + 1] = pack2(a2, a3);
+            pr[i] = pack2(a0, a1);
+            pr[i + 1] = pack2(a2, a3);
           }
-          // P columns [half*32 + part*16, +16) = keys [half*64 + part*32, +32)
-          tmem_st16(ts + half * 32 + part * 16, pr);
+          tmem_st16(tp + part * 16, pr);                   // P columns [part*16, +16) = keys [part*32, +32)
         }
-        l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
-        m_run = m_new;
-        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 5);
-        if (j > 0 && !__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
-          // the previous P.V must have landed in O before this thread's 64 columns of O are rescaled
-          ok = mbar_wait(&bar_odone[(bc - 1) % 3], ((bc - 1) / 3) & 1, &give_up, 32);
+        // this thread's part of the row sum moves to the block's reference
+        const float beta = (m_l == -INFINITY) ? 0.f : ex2(m_l - ref);
+        l_run = l_run * beta + ((s0 + s1) + (s2 + s3));
+        m_l = ref;
+        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 5);
+        if (j > 0 && __any_sync(0xFFFFFFFFu, ref != ref_prev)) {
+          // O is in the scale of ref(j-1): once P.V(j-1) has landed, bring this row to ref(j).
+          // (P.V(j-3) is known complete: this thread waited for P.V(j-2) above, and they complete in order.)
+          ok = mbar_wait(&bar_odone[wg ^ 1], prev_idx & 1, &give_up, 32);
           if (!ok) break;
           tc_fence_after();
+          const float alpha = ex2(ref_prev - ref);         // 1 for the rows whose reference stayed
 #pragma unroll 1
-          for (int part = 0; part < 2; ++part) {
+          for (int part = 0; part < 4; ++part) {
             uint32_t orr[32];
             tmem_ld32(t_acc + part * 32, orr);
             tmem_wait_ld();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) orr[e] = __float_as_uint(__uint_as_float(orr[e]) * alpha);
+            for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
             tmem_st32(t_acc + part * 32, orr);
           }
         }
         tmem_wait_st();
-        if (lane == 0 && (warp & 3) == 0) KB_TR(half, 6);
+        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 6);
         tc_fence_before();
-        mbar_arrive(&bar_pready[bc % 3]);
+        mbar_arrive(&bar_pready[wg]);
       }
       if (!ok) break;
-      // ---- epilogue: add the two halves' row sums, normalise, store ------------------------------
-      // (parities of the exchange: the block loop used xchg[bc & 1] with barriers bar_lse; the row sums
-      //  go through bar_x once per tile)
-      sh.xchg[bc & 1][half][row] = l_run;
+      done_mine += n_mine;
+      done_other += n_other;
+      // ---- epilogue: bring the two parts of the row sum together, normalise, store ----------------
+      // (xchg[0][wg] already holds this stream's last reference = m_l, unless it had no block)
+      if (n_mine == 0) *ref_mine = m_l;
+      sh.xchg[1][wg][row] = l_run;
       mbar_arrive(&sh.bar_x);
       ok = mbar_wait(&sh.bar_x, tiles_done & 1, &give_up, 35);
       if (!ok) break;
-      const float l_tot = l_run + sh.xchg[bc & 1][half ^ 1][row];
-      ok = mbar_wait(&bar_odone[(bc - 1) % 3], ((bc - 1) / 3) & 1, &give_up, 33);   // the tile's last P.V
+      const float m_o = *ref_other, l_o = sh.xchg[1][wg ^ 1][row];
+      const float m_tot = fmaxf(m_l, m_o);               // the reference of the tile's last block
+      const float f_mine = (m_l == -INFINITY) ? 0.f : ex2(m_l - m_tot);
+      const float f_other = (m_o == -INFINITY) ? 0.f : ex2(m_o - m_tot);
+      const float l_tot = l_run * f_mine + l_o * f_other;
+      // the tile's last P.V (own stream first: a wait may be at most one phase behind its barrier)
+      if (n_mine > 0) ok = mbar_wait(&bar_odone[wg], (done_mine - 1) & 1, &give_up, 33);
+      if (ok && n_other > 0) ok = mbar_wait(&bar_odone[wg ^ 1], (done_other - 1) & 1, &give_up, 36);
       if (!ok) break;
       tc_fence_after();
       const float inv = 1.0f / l_tot;
-      __half* orow = p.out + (((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)) * kD + half * 64;
+      // this warpgroup stores output columns [wg*64, +64) of its rows
+      __half* orow = p.out + (((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)) * kD + wg * 64;
 #pragma unroll 1
       for (int part = 0; part < 2; ++part) {
         uint32_t oa[32];
-        tmem_ld32(t_acc + part * 32, oa);
+        tmem_ld32(t_acc + wg * 64 + part * 32, oa);
         tmem_wait_ld();
         if (tok < p.L) {
 #pragma unroll
@@ -712,8 +754,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
           }
         }
       }
-      if (half == 0 && p.lse2 && tok < p.L)
-        p.lse2[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)] = m_run + log2f(l_tot);
+      if (wg == 0 && p.lse2 && tok < p.L)
+        p.lse2[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)] = m_tot + log2f(l_tot);
       // O and the exchange buffer have been read
       tc_fence_before();
       mbar_arrive(&sh.bar_ofree);
