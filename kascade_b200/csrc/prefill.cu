@@ -153,11 +153,11 @@ struct PfCfg {
   static constexpr int kMmaWarp = kGather ? 12 : 9;
 };
 
-// Optional timeline tracing (compile with -DKB200_TRACE): up to four roles of CTA 0 record
+// Optional timeline tracing (compile with -DKB200_TRACE): up to six roles of CTA 0 record
 // (tag, clock64) pairs, read back by kb200_debug_trace.  Compiled out by default.
 #ifdef KB200_TRACE
-__device__ long long g_trace[4][2048][2];
-__device__ int g_trace_n[4];
+__device__ long long g_trace[6][2048][2];
+__device__ int g_trace_n[6];
 #define KB_TR_DECL int trn = 0
 #define KB_TR(role, tag)                                                     \
   do {                                                                       \
@@ -255,6 +255,10 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     const int n_st = is_v ? kNV : kNK;
     int st = 0, ph = 1, qn = 0;                          // ring position, parity of its "empty" phase; Q tiles loaded
     bool ok = true;
+    KB_TR_DECL;
+    uint32_t soff[4];                                    // swizzled offset of (row 2 q + (lane >> 4), chunk lane & 15)
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) soff[q4] = tile_off(2 * q4 + (lane >> 4), lane & 15, 128);
     for (int k = 0; k < n_rounds && ok; ++k) {
       const int item = item_of(k);
       if (item >= n_items) continue;
@@ -274,9 +278,12 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       }
       cp_arrive_noinc(&sh.bar_q);
       ++qn;
-      const __half* base = is_v ? p.v + (int64_t)it.b * p.v_sb + (int64_t)it.g * p.v_sh
-                                : p.k + (int64_t)it.b * p.k_sb + (int64_t)it.g * p.k_sh;
-      const int64_t tok_stride = is_v ? p.v_st : p.k_st;
+      // this lane copies 16-byte chunk c of the rows (2 i + sub), i = 0..31, of its warp's 64 rows
+      const int c = lane & 15, sub = lane >> 4;
+      const char* base = reinterpret_cast<const char*>(
+          (is_v ? p.v + (int64_t)it.b * p.v_sb + (int64_t)it.g * p.v_sh
+                : p.k + (int64_t)it.b * p.k_sb + (int64_t)it.g * p.k_sh) + c * 8);
+      const int tok_bytes = (int)((is_v ? p.v_st : p.k_st) * 2);   // host side checks that this fits
       // key positions of rows (half_rows + lane) and (half_rows + 32 + lane) of block j; the index
       // loads run two blocks ahead of their use
       auto load_key = [&](int j, int r) -> int {
@@ -289,24 +296,25 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         const int key0 = max(0, min(a0, p.L - 1)), key1 = max(0, min(a1, p.L - 1));
         a0 = b0; a1 = b1;
         b0 = load_key(j + 2, 0); b1 = load_key(j + 2, 1);
-        const int64_t off0 = (int64_t)key0 * tok_stride, off1 = (int64_t)key1 * tok_stride;
-        const int c = lane & 15;
+        if (lane == 0 && (pw & 1) == 0) KB_TR(4 + (pw >> 1), 20);
         ok = mbar_wait(&bar_empty[st], ph, &give_up, is_v ? 12 : 11);
         if (!ok) break;
-        const uint32_t dst = ring_s + st * kStageBytes;
-#pragma unroll 4
+        if (lane == 0 && (pw & 1) == 0) KB_TR(4 + (pw >> 1), 21);
+        // Per copy: one shuffle (the row's key), one multiply-add (its address), one cp.async; the
+        // swizzled destination of row (2 i + sub) repeats every four i, 1024 bytes further on.
+        const uint32_t dst = ring_s + st * kStageBytes + half_rows * 128;
+#pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const int rw = i * 2 + (lane >> 4);
-          const int64_t o = __shfl_sync(0xFFFFFFFFu, off0, rw);
-          cp16(dst + tile_off(half_rows + rw, c, 128), base + o + c * 8);
+          const int key = __shfl_sync(0xFFFFFFFFu, key0, i * 2 + sub);
+          cp16(dst + (i >> 2) * 1024 + soff[i & 3], base + (int64_t)key * tok_bytes);
         }
-#pragma unroll 4
+#pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const int rw = i * 2 + (lane >> 4);
-          const int64_t o = __shfl_sync(0xFFFFFFFFu, off1, rw);
-          cp16(dst + tile_off(half_rows + 32 + rw, c, 128), base + o + c * 8);
+          const int key = __shfl_sync(0xFFFFFFFFu, key1, i * 2 + sub);
+          cp16(dst + 4096 + (i >> 2) * 1024 + soff[i & 3], base + (int64_t)key * tok_bytes);
         }
         cp_arrive_noinc(&bar_full[st]);
+        if (lane == 0 && (pw & 1) == 0) KB_TR(4 + (pw >> 1), 22);
         if (++st == n_st) { st = 0; ph ^= 1; }
       }
     }
@@ -1117,9 +1125,9 @@ static int check_shape(int batch, int seq_len, int H, int G) {
 
 #ifdef KB200_TRACE
 extern "C" int kb200_debug_trace(long long* buf, int* cnt) {
-  cudaMemcpyFromSymbol(buf, kb200::g_trace, sizeof(long long) * 4 * 2048 * 2);
-  cudaMemcpyFromSymbol(cnt, kb200::g_trace_n, sizeof(int) * 4);
-  int z[4] = {0, 0, 0, 0};
+  cudaMemcpyFromSymbol(buf, kb200::g_trace, sizeof(long long) * 6 * 2048 * 2);
+  cudaMemcpyFromSymbol(cnt, kb200::g_trace_n, sizeof(int) * 6);
+  int z[6] = {0, 0, 0, 0, 0, 0};
   cudaMemcpyToSymbol(kb200::g_trace_n, z, sizeof(z));
   return 0;
 }
@@ -1207,6 +1215,9 @@ extern "C" int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_l
   if (fill_act(q, &p.q, &p.q_sb, &p.q_st, &p.q_sh, "q") != 0) return -1;
   if (fill_act(k, &p.k, &p.k_sb, &p.k_st, &p.k_sh, "k") != 0) return -1;
   if (fill_act(v, &p.v, &p.v_sb, &p.v_st, &p.v_sh, "v") != 0) return -1;
+  // the gather computes row addresses as key * (token stride in bytes) with a 32-bit factor
+  KB_REQUIRE(p.k_st >= 0 && p.k_st < (1ll << 29) && p.v_st >= 0 && p.v_st < (1ll << 29),
+             "prefill_sparse: token strides of k and v must lie in [0, 2^29) elements");
   p.tile_idx = tile_idx;
   p.G_idx = idx_kv_heads > 0 ? idx_kv_heads : num_kv_heads;
   p.idx_stride = idx_stride;
