@@ -148,7 +148,7 @@ struct PfCfg {
   static constexpr int kThreads = kGather ? 512 : 384;
   static constexpr int kNK = kHasV ? 3 : kNKMax;
   static constexpr int kProducerArrivals = kGather ? 128 : 1;   // Q tile: all gather threads
-  static constexpr int kRingArrivals = kGather ? 64 : 1;        // K / V stage: one warp pair each
+  static constexpr int kRingArrivals = kGather ? 96 : 1;        // K / V stage: three gather warps each
   static constexpr int kProducerWarp0 = 8;
   static constexpr int kMmaWarp = kGather ? 12 : 9;
 };
@@ -243,12 +243,17 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   // ================================ producer: gathered rows by cp.async (sparse mode) ===========
   // Every thread copies with cp.async and lets the hardware arrive on the stage's "full" barrier when
   // its copies have landed (cp.async.mbarrier.arrive.noinc): the producers never wait for data, they
-  // run ahead as far as the rings allow.  The MMA warp orders the landed bytes against the tensor
-  // core's reads with a proxy fence after its barrier wait.
+  // run ahead as far as the rings allow.  The MMA warps order the landed bytes against the tensor
+  // core's reads with a proxy fence after their barrier waits.
+  // One warp issues a 512-byte cp.async instruction only every ~50 cycles, however little else it
+  // does, and the SM takes one about every 12: six warps gather, three per ring (rows 0-47, 48-95,
+  // 96-127 of a stage), the K ring independent of the V ring.
   auto producer_gather = [&]() {
-    const int pw = warp - Cfg::kProducerWarp0, ptid = tid - Cfg::kProducerWarp0 * 32;
-    const bool is_v = pw >= 2;                           // warps 0,1 fill the K ring, warps 2,3 the V ring
-    const int half_rows = (pw & 1) * 64;                 // this warp's 64 rows of a 128-row stage
+    const int gw = warp < 12 ? warp - 8 : warp - 10;     // warps 8, 9, 10: K ring; warps 11, 14, 15: V ring
+    const bool is_v = gw >= 3;
+    const int part = is_v ? gw - 3 : gw;
+    const int r_begin = part * 48;                       // this warp's rows of a 128-row stage: 48, 48, 32
+    const bool has_tail = part < 2;                      // rows r_begin + 32 .. r_begin + 47
     uint64_t* bar_full = is_v ? bar_vfull : bar_kfull;
     uint64_t* bar_empty = is_v ? bar_vempty : bar_kempty;
     const uint32_t ring_s = is_v ? v_s : k_s;
@@ -264,31 +269,35 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (item >= n_items) continue;
       const TileItem it = decode_item<MODE>(p, item);
       if (it.nb == 0) continue;
-      // the Q buffer is free once the last Q.K^T of the previous tile has completed
-      ok = mbar_wait(&sh.bar_qempty, (qn & 1) ^ 1, &give_up, 13);
-      if (!ok) break;
-      const __half* qb = p.q + (int64_t)it.b * p.q_sb;
+      if (warp < 12) {
+        // warps 8-11 also load the Q tile; its buffer is free once the last Q.K^T of the previous
+        // tile has completed
+        const int ptid = tid - 8 * 32;
+        ok = mbar_wait(&sh.bar_qempty, (qn & 1) ^ 1, &give_up, 13);
+        if (!ok) break;
+        const __half* qb = p.q + (int64_t)it.b * p.q_sb;
 #pragma unroll 4
-      for (int i = 0; i < 16; ++i) {
-        const int id = i * 128 + ptid, row = id >> 4, c = id & 15;
-        const int tok = it.tile_start + (row >> 2), head = it.g * kHg + (row & 3);
-        const bool in = tok < p.L;                       // rows past the prompt are zero-filled
-        cp16_zfill(q_s + tile_off(row, c, 128),
-                   qb + (int64_t)(in ? tok : 0) * p.q_st + (int64_t)head * p.q_sh + c * 8, in ? 16u : 0u);
+        for (int i = 0; i < 16; ++i) {
+          const int id = i * 128 + ptid, row = id >> 4, c = id & 15;
+          const int tok = it.tile_start + (row >> 2), head = it.g * kHg + (row & 3);
+          const bool in = tok < p.L;                     // rows past the prompt are zero-filled
+          cp16_zfill(q_s + tile_off(row, c, 128),
+                     qb + (int64_t)(in ? tok : 0) * p.q_st + (int64_t)head * p.q_sh + c * 8, in ? 16u : 0u);
+        }
+        cp_arrive_noinc(&sh.bar_q);
+        ++qn;
       }
-      cp_arrive_noinc(&sh.bar_q);
-      ++qn;
-      // this lane copies 16-byte chunk c of the rows (2 i + sub), i = 0..31, of its warp's 64 rows
+      // this lane copies 16-byte chunk c of the rows r_begin + 2 i + sub
       const int c = lane & 15, sub = lane >> 4;
       const char* base = reinterpret_cast<const char*>(
           (is_v ? p.v + (int64_t)it.b * p.v_sb + (int64_t)it.g * p.v_sh
                 : p.k + (int64_t)it.b * p.k_sb + (int64_t)it.g * p.k_sh) + c * 8);
       const int tok_bytes = (int)((is_v ? p.v_st : p.k_st) * 2);   // host side checks that this fits
-      // key positions of rows (half_rows + lane) and (half_rows + 32 + lane) of block j; the index
-      // loads run two blocks ahead of their use
+      // key positions of rows (r_begin + lane) and (r_begin + 32 + lane) of block j; the index loads
+      // run two blocks ahead of their use
       auto load_key = [&](int j, int r) -> int {
-        const int s = j * 128 + half_rows + r * 32 + lane;
-        if (j >= it.nb || s >= it.total) return 0;
+        const int s = j * 128 + r_begin + r * 32 + lane;
+        if (j >= it.nb || s >= it.total || (r == 1 && (!has_tail || lane >= 16))) return 0;
         return s < it.count ? __ldg(it.idx_row + s) : it.tile_start + (s - it.count);
       };
       int a0 = load_key(0, 0), a1 = load_key(0, 1), b0 = load_key(1, 0), b1 = load_key(1, 1);
@@ -296,25 +305,27 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         const int key0 = max(0, min(a0, p.L - 1)), key1 = max(0, min(a1, p.L - 1));
         a0 = b0; a1 = b1;
         b0 = load_key(j + 2, 0); b1 = load_key(j + 2, 1);
-        if (lane == 0 && (pw & 1) == 0) KB_TR(4 + (pw >> 1), 20);
+        if (lane == 0 && part == 0) KB_TR(4 + (is_v ? 1 : 0), 20);
         ok = mbar_wait(&bar_empty[st], ph, &give_up, is_v ? 12 : 11);
         if (!ok) break;
-        if (lane == 0 && (pw & 1) == 0) KB_TR(4 + (pw >> 1), 21);
+        if (lane == 0 && part == 0) KB_TR(4 + (is_v ? 1 : 0), 21);
         // Per copy: one shuffle (the row's key), one multiply-add (its address), one cp.async; the
         // swizzled destination of row (2 i + sub) repeats every four i, 1024 bytes further on.
-        const uint32_t dst = ring_s + st * kStageBytes + half_rows * 128;
+        const uint32_t dst = ring_s + st * kStageBytes + r_begin * 128;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int key = __shfl_sync(0xFFFFFFFFu, key0, i * 2 + sub);
           cp16(dst + (i >> 2) * 1024 + soff[i & 3], base + (int64_t)key * tok_bytes);
         }
+        if (has_tail) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int key = __shfl_sync(0xFFFFFFFFu, key1, i * 2 + sub);
-          cp16(dst + 4096 + (i >> 2) * 1024 + soff[i & 3], base + (int64_t)key * tok_bytes);
+          for (int i = 0; i < 8; ++i) {
+            const int key = __shfl_sync(0xFFFFFFFFu, key1, i * 2 + sub);
+            cp16(dst + 4096 + (i >> 2) * 1024 + soff[i & 3], base + (int64_t)key * tok_bytes);
+          }
         }
         cp_arrive_noinc(&bar_full[st]);
-        if (lane == 0 && (pw & 1) == 0) KB_TR(4 + (pw >> 1), 22);
+        if (lane == 0 && part == 0) KB_TR(4 + (is_v ? 1 : 0), 22);
         if (++st == n_st) { st = 0; ph ^= 1; }
       }
     }
@@ -1010,7 +1021,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   // Register hand-over (setmaxnreg).  The pool is what the CTA got at launch: the softmax warpgroups
   // can only take what the other warpgroups give back, and the warps that share an SM sub-partition
   // (w, w+4, w+8, w+12) must stay within 512 registers per thread slot.
-  //   sparse: 512 threads x 128 at launch; 256 x 200 + 128 x 64 + 128 x 48 = 65536; 2 x 200 + 64 + 48 = 512
+  //   sparse: 512 threads x 128 at launch; 256 x 200 + 256 x 56 = 65536; 2 x 200 + 2 x 56 = 512
   //   dense : 384 threads x 168 at launch; 256 x 200 + 128 x 96 = 63488 <= 64512; 2 x 200 + 96 <= 512
   // The instruction is warpgroup-wide: all four warps of a warpgroup execute the same one, and the role
   // code sits inside the branch that issued it.
@@ -1019,12 +1030,13 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     if (POOL) pool_role(); else if (HAS_V) softmax_role_v(); else softmax_role();
   } else if (GATHER) {
     if (warp < 12) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 64;\n");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
       producer_gather();
     } else {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 48;\n");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
       if (warp == kMmaWarp) mma_qk_v();
       else if (warp == kMmaWarp + 1) mma_pv_v();
+      else producer_gather();
     }
   } else {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 96;\n");
