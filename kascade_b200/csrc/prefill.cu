@@ -83,6 +83,24 @@ __device__ __forceinline__ void cp_arrive_noinc(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(umma::smem_addr(bar)) : "memory");
 }
 __device__ __forceinline__ void cp_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+// 2^x on the FMA pipes, for x <= 127: the special-function unit delivers 16 results per clock and SM,
+// which is what bounds the softmax; every fourth exponential goes this way instead.  x is rounded
+// to the nearest integer n by adding 1.5 * 2^23 (n lands in the low mantissa bits), 2^(x - n) on
+// [-0.5, 0.5] is a degree-4 polynomial (relative error 3e-6), and n is added to the exponent field.
+__device__ __forceinline__ float ex2_fma(float x) {
+#ifdef KB200_NO_FMA_EXP
+  return ex2(x);
+#endif
+  x = fmaxf(x, -120.0f);                               // also maps -inf (masked) to 2^-120 ~ 0
+  const float t = x + 12582912.0f;
+  const float f = x - (t - 12582912.0f);
+  float q = 0.009585312567651272f;
+  q = fmaf(q, f, 0.05590597912669182f);
+  q = fmaf(q, f, 0.24024048447608948f);
+  q = fmaf(q, f, 0.6931242942810059f);
+  q = fmaf(q, f, 1.0f);
+  return __uint_as_float(__float_as_uint(q) + (__float_as_uint(t) << 23));
+}
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -869,7 +887,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
               s0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -m_new));
               s1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -m_new));
               s2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -m_new));
-              s3 += ex2(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -m_new));
+              s3 += ex2_fma(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -m_new));
             }
         }
         l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
@@ -1008,7 +1026,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
             a0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -lse_s[part * 32 + i]));
             a1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -lse_s[part * 32 + i + 1]));
             a2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -lse_s[part * 32 + i + 2]));
-            a3 += ex2(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -lse_s[part * 32 + i + 3]));
+            a3 += ex2_fma(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -lse_s[part * 32 + i + 3]));
           }
         const int key = j * 128 + key_lane;
         if (key < it.tile_start) prow[key] = (a0 + a1) + (a2 + a3);
