@@ -251,7 +251,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh.tmem;
-  const uint32_t t_s0 = tmem, t_o = tmem + 256;
+  const uint32_t t_s0 = tmem;
 
   const int n_items = p.B * p.G * p.T;
   const int P = (int)gridDim.x;
@@ -403,11 +403,11 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     }
   };
 
-  // ================================ MMA issuer (one thread) ======================================
+  // ================================ MMA issuer, modes without V ===================================
+  // One warp issues Q.K^T one block ahead of the softmax, alternating between the two S buffers.
   auto mma_role = [&]() {
     constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
-    constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
-    int kc = 0, vc = 0, qn = 0, tiles_done = 0;
+    int kc = 0, qn = 0;
     int issued0 = 0, issued1 = 0;                      // Q.K^T blocks written into S buffer 0 / 1 so far
     int released0 = 0, released1 = 0;                  // ... and how many of them the softmax side consumed
     bool ok = true;
@@ -426,7 +426,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     auto issue_qk = [&](int w) -> bool {
       if (!wait_s_free(w)) return false;
       if (!mbar_wait(&bar_kfull[kc % kNK], (kc / kNK) & 1, &give_up, 22)) return false;
-      if (GATHER) fence_proxy_async_smem();            // cp.async bytes -> visible to the tensor core
       tc_fence_after();
       const uint32_t k_lo = desc_lo(k_s, 16) + (kc % kNK) * (kStageBytes >> 4);
       const uint32_t q_lo = desc_lo(q_s, 16);
@@ -453,56 +452,20 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (it.nb == 0) continue;
       ok = mbar_wait(&sh.bar_q, qn & 1, &give_up, 21);
       if (!ok) break;
-      if (GATHER) fence_proxy_async_smem();
       ++qn;
       ok = issue_qk(0);
       if (ok && it.nb == 1 && el) mma_commit(&sh.bar_qempty);  // the tile's last Q.K^T is queued: Q may be replaced
       for (int j = 0; j < it.nb && ok; ++j) {
-        const int w = j & 1;
         if (j + 1 < it.nb) {
           ok = issue_qk((j + 1) & 1);
           if (!ok) break;
           if (j + 2 == it.nb && el) mma_commit(&sh.bar_qempty);
         }
-        if (HAS_V) {
-          // P(j) is in tensor memory (and S(j) has been consumed)
-          int& rel = w ? released1 : released0;
-          ok = mbar_wait(&bar_pready[w], rel & 1, &give_up, 24);
-          if (!ok) break;
-          ++rel;
-          ok = mbar_wait(&bar_vfull[vc % kNV], (vc / kNV) & 1, &give_up, 25);
-          if (!ok) break;
-          if (j < 2 && tiles_done > 0) {
-            // the first P.V of a stream in a new tile overwrites O: the previous tile's epilogue must
-            // have read both accumulators
-            ok = mbar_wait(&sh.bar_ofree, (tiles_done - 1) & 1, &give_up, 26);
-            if (!ok) break;
-          }
-          if (GATHER) fence_proxy_async_smem();
-          tc_fence_after();
-          const uint32_t vs_addr = v_s + (vc % kNV) * kStageBytes;
-          const uint32_t a = t_s0 + w * 128;
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            mma_ts(t_o + w * 128, a + ks * 8, desc_mnmajor(vs_addr + ks * 2048, kStageBytes / 2), idesc_pv,
-                   (j > 1 || ks > 0) ? 1u : 0u);
-          }
-          mma_commit(&bar_vempty[vc % kNV]);
-          mma_commit(&bar_odone[w]);
-          ++vc;
-        }
       }
-      ++tiles_done;
     }
   };
 
-  // ================================ modes with V: one stream, three S buffers ======================
-  // With V, P(j) lives in the S buffer it was computed from until P.V(j) has read it, so a stream
-  // that owns one S buffer runs  softmax -> P.V -> Q.K^T -> softmax  strictly one after the other.
-  // Here all 256 softmax threads work on the same block (each thread one row and one half of the 128
-  // columns, row maximum exchanged through shared memory) and the blocks rotate through three S
-  // buffers (S0, S1, S2 = 384 columns, O = 128 columns): Q.K^T runs two blocks ahead of the softmax,
-  // P.V one block behind it, and the softmax of consecutive blocks is back to back.
+  // ================================ MMA issuers, modes with V ======================================
   // Tensor-memory columns with V: S0, S1 (fp32, 2 x 128) | P0, P1 (fp16 pairs, 2 x 64) | O (fp32, 128).
   // Even key blocks of a tile go through (S0, P0), odd ones through (S1, P1); there is ONE accumulator.
   //
@@ -800,18 +763,17 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     }
   };
 
-  // ================================ softmax ======================================================
+  // ================================ softmax statistics only (no V) ================================
   // Two warpgroups, two independent streams: warpgroup w owns the key blocks j = w, w+2, ... of every
-  // tile with its own S buffer, its own running (max, sum) per row and (with V) its own O
-  // accumulator, so the tcgen05.ld / max / ex2 phases of one stream overlap those of the other and
-  // nothing is exchanged per block.  The streams are merged like split-K partials in the epilogue.
+  // tile with its own S buffer and its own running (max, sum) per row, so the tcgen05.ld / max / ex2
+  // phases of one stream overlap those of the other and nothing is exchanged per block.  The two
+  // partial results of a row are merged like split-K partials in the epilogue.
   auto softmax_role = [&]() {
     const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane, q_local = row >> 2;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t ts = t_s0 + wg * 128 + lane_sel;   // this stream's S / P buffer
-    const uint32_t to = t_o + wg * 128 + lane_sel;    // this stream's O accumulator
-    int done_mine = 0, done_other = 0, tiles_done = 0; // blocks finished per stream, tiles finished
+    const uint32_t ts = t_s0 + wg * 128 + lane_sel;   // this stream's S buffer
+    int done_mine = 0, tiles_done = 0;                 // blocks finished by this stream, tiles finished
     bool ok = true;
     for (int k = 0; k < n_rounds && ok; ++k) {
       const int item = item_of(k);
@@ -819,8 +781,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       const TileItem it = decode_item<MODE>(p, item);
       if (it.nb == 0) continue;
       const int tok = it.tile_start + q_local;
-      const int off = GATHER ? it.count : it.tile_start;   // slot - off = key position inside the tile
-      const int n_mine = (it.nb - wg + 1) >> 1, n_other = it.nb - n_mine;
+      const int off = it.tile_start;                    // slot - off = key position inside the tile
+      const int n_mine = (it.nb - wg + 1) >> 1;
       float m_run = -INFINITY, l_run = 0.f;             // m_run in the scaled (log2) domain
       for (int j = wg, jj = 0; j < it.nb; j += 2, ++jj) {
         ok = mbar_wait(&bar_sfull[wg], (done_mine + jj) & 1, &give_up, 31);
@@ -833,10 +795,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
 #pragma unroll
         for (int part = 0; part < 4; ++part) tmem_ld32(ts + part * 32, sr[part]);
         tmem_wait_ld();
-        if (!HAS_V) {                                      // S is in registers: the buffer may be refilled
-          tc_fence_before();
-          mbar_arrive(&bar_pready[wg]);
-        }
+        tc_fence_before();
+        mbar_arrive(&bar_pready[wg]);                     // S is in registers: the buffer may be refilled
         if (need_mask) {
 #pragma unroll
           for (int part = 0; part < 4; ++part)
@@ -857,66 +817,26 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale2;
         // The reference point of the exponentials only moves when the row maximum has grown by more
-        // than 2^kRescaleLog2: probabilities then stay below 2^kRescaleLog2 (exact in fp32, harmless in
-        // fp16), and the O accumulator is rescaled only on those rare blocks.  lse2 = m + log2(l) holds
-        // for any reference point m.
+        // than 2^kRescaleLog2 (the terms then stay below 2^kRescaleLog2, exact in fp32);
+        // lse2 = m + log2(l) holds for any reference point m.
         const float m_new = (mx > m_run + kRescaleLog2) ? mx : m_run;
         const float alpha = ex2(m_run - m_new);
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-        if (HAS_V) {
 #pragma unroll
-          for (int part = 0; part < 4; ++part) {           // 32 keys -> 16 packed P columns
-            uint32_t pr[16];
+        for (int part = 0; part < 4; ++part)
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-              float a0 = ex2(fmaf(__uint_as_float(sr[part][2 * i]), p.scale2, -m_new));
-              float a1 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 1]), p.scale2, -m_new));
-              float a2 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 2]), p.scale2, -m_new));
-              float a3 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 3]), p.scale2, -m_new));
-              s0 += a0; s1 += a1; s2 += a2; s3 += a3;
-              pr[i] = pack2(a0, a1);
-              pr[i + 1] = pack2(a2, a3);
-            }
-            tmem_st16(ts + part * 16, pr);                 // P columns [part*16, +16) = keys [part*32, +32)
+          for (int i = 0; i < 32; i += 4) {
+            s0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -m_new));
+            s1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -m_new));
+            s2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -m_new));
+            s3 += ex2_fma(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -m_new));
           }
-        } else {
-#pragma unroll
-          for (int part = 0; part < 4; ++part)
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              s0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -m_new));
-              s1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -m_new));
-              s2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -m_new));
-              s3 += ex2_fma(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -m_new));
-            }
-        }
         l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
         m_run = m_new;
-        if (HAS_V) {
-          if (jj > 0 && !__all_sync(0xFFFFFFFFu, alpha == 1.0f)) {
-            // the previous P.V of this stream must have landed in O before O is rescaled
-            ok = mbar_wait(&bar_odone[wg], (done_mine + jj - 1) & 1, &give_up, 32);
-            if (!ok) break;
-            tc_fence_after();
-#pragma unroll 1
-            for (int part = 0; part < 4; ++part) {
-              uint32_t orr[32];
-              tmem_ld32(to + part * 32, orr);
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-              tmem_st32(to + part * 32, orr);
-            }
-          }
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(&bar_pready[wg]);
-        }
       }
       if (!ok) break;
       done_mine += n_mine;
-      done_other += n_other;
-      // ---- epilogue: merge the two streams, normalise, store -----------------------------------
+      // ---- epilogue: merge the two streams, store ------------------------------------------------
       // the exchange buffer is free once both warpgroups have finished the previous tile's epilogue
       if (tiles_done > 0) {
         ok = mbar_wait(&sh.bar_ofree, (tiles_done - 1) & 1, &give_up, 37);
@@ -932,47 +852,9 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       const float f_mine = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_tot);
       const float f_other = (m_o == -INFINITY) ? 0.f : ex2(m_o - m_tot);
       const float l_tot = l_run * f_mine + l_o * f_other;
-      if (HAS_V) {
-        if (n_mine > 0) ok = mbar_wait(&bar_odone[wg], (done_mine - 1) & 1, &give_up, 33);
-        if (ok && n_other > 0) ok = mbar_wait(&bar_odone[wg ^ 1], (done_other - 1) & 1, &give_up, 36);
-        if (!ok) break;
-        tc_fence_after();
-        const float inv = 1.0f / l_tot;
-        const float w_mine = f_mine * inv, w_other = f_other * inv;
-        // this warpgroup stores output columns [wg*64, +64) of its rows, from both accumulators
-        __half* orow = p.out + (((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)) * kD + wg * 64;
-        const uint32_t o_mine = t_o + wg * 128 + lane_sel + wg * 64;
-        const uint32_t o_other = t_o + (wg ^ 1) * 128 + lane_sel + wg * 64;
-#pragma unroll 1
-        for (int part = 0; part < 2; ++part) {
-          uint32_t oa[32], ob[32];
-          if (n_mine > 0) tmem_ld32(o_mine + part * 32, oa);
-          if (n_other > 0) tmem_ld32(o_other + part * 32, ob);
-          tmem_wait_ld();
-          if (tok < p.L) {
-            float v[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              float x = n_mine > 0 ? __uint_as_float(oa[i]) * w_mine : 0.f;
-              if (n_other > 0) x = fmaf(__uint_as_float(ob[i]), w_other, x);
-              v[i] = x;
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 w;
-              w.x = pack2(v[i * 8 + 0], v[i * 8 + 1]);
-              w.y = pack2(v[i * 8 + 2], v[i * 8 + 3]);
-              w.z = pack2(v[i * 8 + 4], v[i * 8 + 5]);
-              w.w = pack2(v[i * 8 + 6], v[i * 8 + 7]);
-              *reinterpret_cast<uint4*>(orow + part * 32 + i * 8) = w;
-            }
-          }
-        }
-      }
       if (wg == 0 && p.lse2 && tok < p.L)
         p.lse2[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)] = m_tot + log2f(l_tot);
-      // both accumulators and the exchange buffer have been read
-      tc_fence_before();
+      // the exchange buffer has been read
       mbar_arrive(&sh.bar_ofree);
       ++tiles_done;
     }

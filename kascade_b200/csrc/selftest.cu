@@ -69,13 +69,13 @@ selftest_umma_kernel(const __half* __restrict__ a, const __half* __restrict__ b,
       const uint32_t idesc = idesc_f16(128, 128, 0, b_mn ? 1 : 0);
 #pragma unroll 1
       for (int ks = 0; ks < 8; ++ks) {
-        uint64_t bd = b_mn ? desc_mnmajor(b_s + ks * 2048, 16384)
-                           : desc_kmajor(b_s + (ks >> 2) * 16384 + (ks & 3) * 32);
+        const uint32_t bd = b_mn ? desc_lo(b_s + ks * 2048, 16384)
+                                 : desc_lo(b_s + (ks >> 2) * 16384 + (ks & 3) * 32, 16);
         if (a_tmem) {
-          mma_ts(t_d, t_a + ks * 8, bd, idesc, ks > 0);
+          mma_ts_lo(t_d, t_a + ks * 8, bd, idesc, ks > 0);
         } else {
-          uint64_t ad = desc_kmajor(a_s + (ks >> 2) * 16384 + (ks & 3) * 32);
-          mma_ss(t_d, ad, bd, idesc, ks > 0);
+          const uint32_t ad = desc_lo(a_s + (ks >> 2) * 16384 + (ks & 3) * 32, 16);
+          mma_ss_lo(t_d, ad, bd, idesc, ks > 0);
         }
       }
       mma_commit(&bar);

@@ -167,16 +167,11 @@ __device__ __forceinline__ uint32_t tmem_lane_base(uint32_t taddr, int warp) {
 constexpr uint64_t kDescFixed = (1ull << 46) /* descriptor version for sm_100 */ |
                                 (2ull << 61) /* 128-byte swizzle */;
 
-// K-major operand half: rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
-  return kDescFixed | (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32);
-}
-// MN-major operand: 64-column halves `half_bytes` apart (leading offset), 8-row groups of the
-// reduction index 1024 bytes apart (stride offset).
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t half_bytes) {
-  return kDescFixed | (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(half_bytes >> 4) << 16) |
-         ((uint64_t)(1024 >> 4) << 32);
-}
+// Shared-memory operand descriptors, 128-byte swizzle, 8-row groups 1024 bytes apart (stride offset).
+//   K-major operand half: rows of 128 bytes; leading offset 16 (unused by the hardware in this mode).
+//   MN-major operand: the two 64-column halves lie `leading` bytes apart; a step of 16 along the
+//   reduction index is 2048 bytes.
+// The low word holds (address >> 4) and (leading offset >> 4) << 16; the high word is the same for all.
 
 // instruction descriptor: fp16 x fp16 -> fp32, M x N tile, operand majors (0 = K-major, 1 = MN)
 __host__ __device__ constexpr uint32_t idesc_f16(int M, int N, int a_mn, int b_mn) {
@@ -185,22 +180,6 @@ __host__ __device__ constexpr uint32_t idesc_f16(int M, int N, int a_mn, int b_m
 }
 
 // ---- MMA issue (one thread) ------------------------------------------------------------------------
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // The issuing thread's own instruction count matters (one thread feeds the tensor core): these take the
 // low descriptor word (address and leading offset; add (bytes >> 4) to step through a tile) and
 // attach the word that every operand here shares (stride offset 1024, version, 128-byte swizzle).
