@@ -1,0 +1,258 @@
+"""Benchmark-size checks (GPU): the full shapes of the prefill and decode configurations through the
+C ABI.  The CPU oracle cannot run these sizes, so every result is checked two ways:
+
+* sampled tiles / sequences against a plain fp32 torch evaluation of exactly those rows (on the GPU),
+  with the tolerances of the parity contract (outputs max-abs 2e-3 / rel 1e-2, index sets by the
+  tie-band rule, 2^-10 relative);
+* structural properties of ALL rows: budgets follow the reference's formulas, index rows are strictly
+  ascending, inside the causal range and have exactly the budgeted length.
+"""
+import math
+
+import pytest
+import torch
+
+from oracle.kascade_oracle import rolling_budget, topk_budget
+from tests.gpu_util import assert_close
+
+pytestmark = pytest.mark.gpu
+LOG2E = 1.4426950408889634
+H, G, D, TILE = 32, 8, 128, 32
+BAND = 2.0 ** -10
+
+
+def _status_ok():
+    from kascade_b200 import _native as nat
+    st = nat.read_status()
+    assert st == 0, f"a kernel gave up a bounded wait (code {st})"
+
+
+def _prefill_inputs(L, seed, qk_norm):
+    """[1, L, heads, D] fp16 on the GPU: N(0,1)/sqrt(D) with the heavy-hitter injection of the benchmark
+    (1 % of the key positions get +2.5 u, every query +0.5 u, u a shared unit vector); with qk_norm the
+    rows of Q and K are RMS-normalised (unit gain) like the long-prompt configuration."""
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    q = torch.randn(1, L, H, D, generator=gen, device=dev) / D ** 0.5
+    k = torch.randn(1, L, G, D, generator=gen, device=dev) / D ** 0.5
+    v = torch.randn(1, L, G, D, generator=gen, device=dev) / D ** 0.5
+    u = torch.randn(D, generator=gen, device=dev)
+    u = u / u.norm()
+    hot = torch.rand(1, L, G, 1, generator=gen, device=dev) < 0.01
+    k = k + 2.5 * u * hot
+    q = q + 0.5 * u
+    if qk_norm:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + 1e-6)
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + 1e-6)
+    return q.half(), k.half(), v.half()
+
+
+def _band_ok(ref_scores, chosen, k):
+    """Tie-band rule on one row: ref_scores fp32 [n] (valid keys only), chosen = selected positions."""
+    n = ref_scores.numel()
+    if k >= n:
+        return sorted(chosen.tolist()) == list(range(n)), "all valid keys must be selected"
+    tau = torch.topk(ref_scores, k).values[-1]
+    sel = torch.zeros(n, dtype=torch.bool, device=ref_scores.device)
+    sel[chosen.long()] = True
+    must = ref_scores > tau * (1 + BAND)
+    never = ref_scores < tau * (1 - BAND)
+    if bool((must & ~sel).any()):
+        return False, f"{int((must & ~sel).sum())} keys above the band were not selected"
+    if bool((never & sel).any()):
+        return False, f"{int((never & sel).sum())} keys below the band were selected"
+    return True, ""
+
+
+# ---------------------------------------------------------------------------------------------------
+# prefill: one anchor layer (dense + lse, lse-only, pooled scores, budgets, Top-k, sparse) at full size
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name,L,qk_norm,rolling", [("prefill_32k", 32768, False, True),
+                                                    ("prefill_131k_qknorm", 131072, True, True),
+                                                    ("prefill_32k_fixed_budget", 32768, False, False)])
+def test_prefill_anchor_layer_full_size(name, L, qk_norm, rolling):
+    from kascade_b200 import _native as nat
+    dev = torch.device("cuda")
+    pct = 10.0
+    scale = D ** -0.5
+    T = L // TILE
+    q, k, v = _prefill_inputs(L, seed=3, qk_norm=qk_norm)
+    out = torch.empty(1, L, H, D, dtype=torch.float16, device=dev)
+    lse = torch.empty(1, L, H, dtype=torch.float32, device=dev)
+    lse_only = torch.empty_like(lse)
+    nat.prefill_dense(q, k, v, scale, out, lse)
+    nat.prefill_dense(q, k, None, scale, None, lse_only)
+    pooled = torch.full((1, G, T, L), -1.0, dtype=torch.float32, device=dev)
+    nat.prefill_pool_scores(q, k, lse, scale, pooled)
+    k_max = topk_budget(pct, L, TILE)
+    n_valid = torch.empty(1, G, T, dtype=torch.int32, device=dev)
+    k_row = torch.empty(1, G, T, dtype=torch.int32, device=dev)
+    nat.prefill_budgets(n_valid, k_row, 1, G, T, k_max, pct, rolling)
+    idx = torch.full((1, G, T, k_max), -7, dtype=torch.int32, device=dev)
+    cnt = torch.empty(1, G, T, dtype=torch.int32, device=dev)
+    nat.topk_select(pooled, n_valid, k_row, k_max, idx, cnt, n_cols=L)
+    sparse = torch.empty_like(out)
+    nat.prefill_sparse(q, k, v, idx, cnt, None, scale, sparse)
+    _status_ok()
+
+    # ---- properties of all rows --------------------------------------------------------------------
+    assert (lse - lse_only).abs().max().item() < 1e-3, "the two passes disagree on the row statistics"
+    starts = torch.arange(T, device=dev, dtype=torch.int32) * TILE
+    assert bool((n_valid[0] == starts).all())
+    want_k = torch.tensor([min(k_max, rolling_budget(pct, t * TILE)) if rolling else k_max for t in range(T)],
+                          dtype=torch.int32, device=dev)
+    assert bool((k_row[0] == want_k).all()), "budgets differ from the reference's formula"
+    want_cnt = torch.minimum(want_k, starts)
+    assert bool((cnt[0] == want_cnt).all()), "row lengths differ from min(budget, keys before the tile)"
+    pos = torch.arange(k_max, device=dev)
+    live = pos < cnt[..., None]
+    assert bool((idx[live] >= 0).all()) and bool((idx < starts[None, None, :, None])[live].all())
+    asc = (idx[..., 1:] > idx[..., :-1]) | ~live[..., 1:]
+    assert bool(asc.all()), "index rows must be strictly ascending"
+    assert bool((idx[~live] == -7).all()), "entries beyond a row's length must not be written"
+    assert bool(torch.isfinite(out).all()) and bool(torch.isfinite(sparse).all())
+    # keys before the tile receive all probability mass except the tile's own part: 0 <= sum <= 128 rows
+    mass = torch.where(pooled >= 0, pooled, torch.zeros_like(pooled)).sum(-1)
+    assert float(mass.min()) >= 0.0 and float(mass.max()) <= 128.0 * (1 + 1e-4)
+    # early tiles (every earlier key fits the budget) attend to the whole causal range: sparse == dense there
+    n_dense_tiles = int((want_k >= starts).sum().item())
+    assert n_dense_tiles >= 4
+    assert_close(sparse[:, : n_dense_tiles * TILE], out[:, : n_dense_tiles * TILE], what=f"{name} dense-prefix tiles")
+
+    # ---- sampled tiles against fp32 torch ------------------------------------------------------------
+    for g, t in [(0, 0), (1, 1), (2, 5), (3, T // 3), (5, T // 2 + 1), (6, T - 2), (7, T - 1)]:
+        s0, s1 = t * TILE, (t + 1) * TILE
+        qt = q[0, s0:s1, g * 4:(g + 1) * 4].float().reshape(TILE * 4, D)              # row = 4 * query + head
+        logits = (qt @ k[0, :s1, g].float().t()) * scale                              # [128, s1]
+        qpos = (torch.arange(TILE * 4, device=dev) // 4) + s0
+        causal = torch.arange(s1, device=dev)[None, :] <= qpos[:, None]
+        logits = logits.masked_fill(~causal, float("-inf"))
+        ref_lse = torch.logsumexp(logits, -1)
+        p = torch.exp(logits - ref_lse[:, None])
+        ref_out = (p @ v[0, :s1, g].float()).view(TILE, 4, D)
+        assert_close(out[0, s0:s1, g * 4:(g + 1) * 4], ref_out, what=f"{name} dense tile {t} head {g}")
+        got_lse = lse[0, s0:s1, g * 4:(g + 1) * 4].reshape(-1)
+        assert (got_lse - ref_lse * LOG2E).abs().max().item() < 1e-3
+        if s0 == 0:
+            continue
+        ref_pool = p[:, :s0].sum(0)
+        got_pool = pooled[0, g, t, :s0]
+        err = ((got_pool - ref_pool).abs() / ref_pool.clamp_min(1e-30)).max().item()
+        assert err < 5e-4, f"{name} pooled scores tile {t} head {g}: rel err {err}"
+        assert bool((pooled[0, g, t, s0:] == -1.0).all()), "scores at or beyond the tile start must not be written"
+        n = int(cnt[0, g, t])
+        ok, why = _band_ok(ref_pool, idx[0, g, t, :n], int(want_k[t]))
+        assert ok, f"{name} Top-k tile {t} head {g}: {why}"
+        allowed = torch.zeros(s1, dtype=torch.bool, device=dev)
+        allowed[idx[0, g, t, :n].long()] = True
+        allowed[s0:] = True
+        sl = logits.masked_fill(~allowed[None, :], float("-inf"))
+        ref_sparse = (torch.softmax(sl, -1) @ v[0, :s1, g].float()).view(TILE, 4, D)
+        assert_close(sparse[0, s0:s1, g * 4:(g + 1) * 4], ref_sparse, what=f"{name} sparse tile {t} head {g}")
+
+
+# ---------------------------------------------------------------------------------------------------
+# paged decode at full size: batch 64, 16-token pages, random block table
+# ---------------------------------------------------------------------------------------------------
+def _decode_reference(q_b, k_b, v_b, scale):
+    """q_b [H,D], k_b / v_b [n,G,D] fp32 -> logits [H,n], probabilities, pooled [G,n], out [H,D]."""
+    kk = k_b.permute(1, 0, 2).repeat_interleave(4, 0)                 # [H,n,D]
+    vv = v_b.permute(1, 0, 2).repeat_interleave(4, 0)
+    logits = torch.einsum("hd,hnd->hn", q_b, kk) * scale
+    p = torch.softmax(logits, -1)
+    pooled = p.view(G, 4, -1).sum(1)
+    return logits, p, pooled, torch.einsum("hn,hnd->hd", p, vv)
+
+
+@pytest.mark.parametrize("name,ragged", [("decode_b64_ctx32k", False), ("decode_b64_ctx4k_64k", True)])
+def test_paged_decode_full_size(name, ragged):
+    from kascade_b200 import _native as nat
+    dev = torch.device("cuda")
+    B, page, pct = 64, 16, 10.0
+    scale = D ** -0.5
+    gen = torch.Generator(device=dev).manual_seed(11)
+    if ragged:
+        cpu_gen = torch.Generator().manual_seed(0)
+        lens = torch.randint(4096, 65537, (256,), generator=cpu_gen)[:B].tolist()     # the first 64 of the 256 draws
+    else:
+        lens = [32768] * B
+    Lmax = max(lens)
+    pages_per_seq = [-(-n // page) for n in lens]
+    max_pages = max(pages_per_seq)
+    total_pages = sum(pages_per_seq) + 5
+    k_cache = torch.randn(total_pages, page, G, D, generator=gen, device=dev, dtype=torch.float16)
+    v_cache = torch.randn(total_pages, page, G, D, generator=gen, device=dev, dtype=torch.float16)
+    # sink keys: the first four tokens of every sequence are louder (as in the reference's small config)
+    perm = torch.randperm(total_pages, generator=torch.Generator().manual_seed(5)).to(torch.int32)
+    block_table = torch.zeros(B, max_pages, dtype=torch.int32)
+    o = 0
+    for b, n in enumerate(pages_per_seq):
+        block_table[b, :n] = perm[o:o + n]
+        o += n
+    block_table = block_table.to(dev)
+    k_cache[block_table[:, 0].long(), :4] *= 3.0
+    q = (torch.randn(B, H, D, generator=gen, device=dev) / D ** 0.5).half()
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
+    kv = nat.kv_layout_paged(k_cache, v_cache, block_table)
+
+    stride = -(-Lmax // 4) * 4
+    logits = torch.empty(B, H, stride, dtype=torch.float32, device=dev)
+    pooled = torch.full((B, G, stride), -1.0, dtype=torch.float32, device=dev)
+    out0 = torch.empty(B, H, D, dtype=torch.float16, device=dev)
+    lse0 = torch.empty(B, H, dtype=torch.float32, device=dev)
+    splits = nat.decode_default_splits(B, G, Lmax)
+    ws = nat.decode_workspace(B, H, max(splits, 1), dev)
+    nat.decode_anchor_paged(q, kv, seq_lens, Lmax, scale, logits, pooled, out0, lse0, ws, 0)
+
+    # budgets per sequence (decode: the prefill formula on the current length, KascadeStrategy.py:127-129)
+    k_seq = [topk_budget(pct, n, TILE) for n in lens]
+    k_max = max(k_seq)
+    n_valid = seq_lens[:, None].expand(B, G).contiguous()
+    k_row = torch.tensor(k_seq, dtype=torch.int32, device=dev)[:, None].expand(B, G).contiguous()
+    idx = torch.full((B, G, k_max), -7, dtype=torch.int32, device=dev)
+    cnt = torch.empty(B, G, dtype=torch.int32, device=dev)
+    nat.topk_select(pooled, n_valid, k_row, k_max, idx, cnt, n_cols=Lmax)
+    head_map = torch.tensor([3, 3, 0, 7, 1, 6, 2, 5], dtype=torch.int32, device=dev)
+    out1 = torch.empty(B, H, D, dtype=torch.float16, device=dev)
+    lse1 = torch.empty(B, H, dtype=torch.float32, device=dev)
+    s2 = nat.decode_default_splits(B, G, k_max)
+    ws2 = nat.decode_workspace(B, H, max(s2, 1), dev)
+    nat.decode_sparse_paged(q, kv, idx, cnt, k_max, head_map, scale, out1, lse1, ws2, 0)
+    _status_ok()
+
+    # ---- properties of all rows --------------------------------------------------------------------
+    assert bool((cnt == k_row).all()), "row lengths differ from the budget"
+    pos = torch.arange(k_max, device=dev)
+    live = pos < cnt[..., None]
+    assert bool((idx[live] >= 0).all()) and bool((idx < seq_lens[:, None, None])[live].all())
+    assert bool(((idx[..., 1:] > idx[..., :-1]) | ~live[..., 1:]).all()), "index rows must be strictly ascending"
+    assert bool((idx[~live] == -7).all())
+    inside = torch.arange(stride, device=dev)[None, None, :] < seq_lens[:, None, None]
+    assert bool((pooled[~inside.expand_as(pooled)] == -1.0).all()), "entries beyond a sequence must not be written"
+    mass = torch.where(inside, pooled, torch.zeros_like(pooled)).sum(-1)
+    assert (mass - 4.0).abs().max().item() < 1e-3, "pooled probabilities of a KV head's four query heads sum to 4"
+    assert bool(torch.isfinite(out0).all()) and bool(torch.isfinite(out1).all())
+
+    # ---- sampled sequences against fp32 torch ---------------------------------------------------------
+    for b in (0, B // 2 + 1, B - 1):
+        n = lens[b]
+        pg = block_table[b, : pages_per_seq[b]].long()
+        k_b = k_cache[pg].reshape(-1, G, D)[:n].float()
+        v_b = v_cache[pg].reshape(-1, G, D)[:n].float()
+        ref_logits, p, ref_pool, ref_out = _decode_reference(q[b].float(), k_b, v_b, scale)
+        assert_close(out0[b], ref_out, what=f"{name} dense decode seq {b}")
+        assert (lse0[b] - torch.logsumexp(ref_logits, -1) * LOG2E).abs().max().item() < 1e-3
+        err = ((pooled[b, :, :n] - ref_pool).abs() / ref_pool.clamp_min(1e-30)).max().item()
+        assert err < 5e-4, f"{name} pooled scores seq {b}: rel err {err}"
+        for g in range(G):
+            ok, why = _band_ok(ref_pool[g], idx[b, g, : int(cnt[b, g])], k_seq[b])
+            assert ok, f"{name} Top-k seq {b} head {g}: {why}"
+        # reuse layer: KV head g attends only to the keys that anchor head head_map[g] selected
+        for g in range(G):
+            src = int(head_map[g])
+            rows = idx[b, src, : int(cnt[b, src])].long()
+            hs = slice(g * 4, g * 4 + 4)
+            sl = (q[b, hs].float() @ k_b[rows, g].t()) * scale
+            ref = torch.softmax(sl, -1) @ v_b[rows, g]
+            assert_close(out1[b, hs], ref, what=f"{name} sparse decode seq {b} head {g}")
+            assert (lse1[b, hs] - torch.logsumexp(sl, -1) * LOG2E).abs().max().item() < 1e-3
