@@ -252,6 +252,8 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-dense", action="store_true")
+    ap.add_argument("--no-peer-store", action="store_true",
+                    help="N > 1: all-gather the per-head outputs with NCCL instead of storing them into the peers from the kernel")
     ap.add_argument("--decode-only", action="store_true", help="profiling aid: run only the decode configuration")
     ap.add_argument("--decode-batch", type=int, default=None, help="profiling aid: decode batch (default 64)")
     args = ap.parse_args()
@@ -286,7 +288,8 @@ def main():
     my_heads = list(range(rank * gpr, (rank + 1) * gpr))
     strat = EfficientKascadeStrategy(list(wl.anchors), "synthetic/llama31-8b-shape", k=wl.pct, tile_size=wl.tile,
                                      rolling_prefill=wl.rolling, head_mapping=wl.head_mapping(), register=False,
-                                     shard=(rank, world) if world > 1 else None)
+                                     shard=(rank, world) if world > 1 else None,
+                                     peer_store=world > 1 and not args.no_peer_store)
     inputs = [wl.layer_inputs(l, dev, my_heads if world > 1 else None) for l in range(wl.layers)]
     scaling = wl.D ** -0.5
     mods = [_Module(l) for l in range(wl.layers)]
@@ -466,7 +469,8 @@ def main():
                            else f"llama31_8b_prefill_attention_stack_{args.seq_len}",
                            "layers": wl.layers, "anchors": list(wl.anchors), "seq_len": wl.seq_len, "batch": wl.B,
                            "q_heads": wl.H, "kv_heads": wl.G, "head_dim": wl.D, "topk_pct": wl.pct, "tile": wl.tile,
-                           "rolling": wl.rolling, "parallelism": f"kv-head shard x{world}",
+                           "rolling": wl.rolling,
+                           "parallelism": f"kv-head shard x{world}" + ("" if world == 1 else (", outputs all-gathered by NCCL" if args.no_peer_store else ", outputs stored into the peers by the kernel epilogue")),
                            "cache_policy": "inputs larger than L2 (402 MB per layer, 32 distinct layers)"},
                 "algorithmic_tflop_per_step": wl.flops_stack() / 1e12,
                 "achieved_tflops": wl.flops_stack() / (ms_step * 1e-3) / 1e12,

@@ -210,6 +210,33 @@ int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_layout* k,
                          void* out, float* lse2, int batch, int seq_len, int num_q_heads,
                          int num_kv_heads, int idx_kv_heads, void* stream);
 
+/* Output fan-out for prompts whose KV heads are sharded over GPUs: the rows a call computes (its
+ * num_q_heads heads) are stored by the kernel's epilogue into `count` buffers, each
+ * [B, L, total_heads, D] fp16 contiguous, at heads [head_offset, head_offset + num_q_heads).  out[0] is
+ * normally this GPU's own buffer, the others are peer GPUs' buffers mapped into this process (CUDA IPC
+ * or symmetric memory; plain stores over NVLink, no multicast).  Every GPU then holds all heads of a
+ * layer once all GPUs' kernels have finished — the caller synchronises the GPUs before reading.
+ * The reference all-gathers nothing (single GPU); this replaces the all-gather of per-head outputs. */
+#define KB200_MAX_FANOUT 8
+typedef struct kb200_out_fanout {
+  void* out[KB200_MAX_FANOUT];
+  int32_t count;
+  int32_t total_heads;
+  int32_t head_offset;
+} kb200_out_fanout;
+
+/* kb200_prefill_dense / kb200_prefill_sparse with the output rows fanned out (see kb200_out_fanout);
+ * all other arguments as in the plain entry points, lse2 (if given) stays local [B, L, num_q_heads]. */
+int kb200_prefill_dense_fanout(const kb200_act_layout* q, const kb200_act_layout* k,
+                               const kb200_act_layout* v, float softmax_scale,
+                               const kb200_out_fanout* fan, float* lse2, int batch, int seq_len,
+                               int num_q_heads, int num_kv_heads, void* stream);
+int kb200_prefill_sparse_fanout(const kb200_act_layout* q, const kb200_act_layout* k,
+                                const kb200_act_layout* v, const int32_t* tile_idx, int64_t idx_stride,
+                                const int32_t* tile_count, const int32_t* head_map, float softmax_scale,
+                                const kb200_out_fanout* fan, float* lse2, int batch, int seq_len,
+                                int num_q_heads, int num_kv_heads, int idx_kv_heads, void* stream);
+
 /* Per-tile budgets of an anchor prefill layer, written on the device for kb200_topk_select:
  *   n_valid[b,g,t] = 32*t,
  *   k_row[b,g,t]   = rolling ? min(k_max, max(128, floor(pct * 32*t / 100))) : k_max

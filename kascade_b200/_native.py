@@ -23,7 +23,7 @@ EXPORTS = [
     "kb200_decode_workspace_bytes", "kb200_decode_default_splits", "kb200_decode_sparse_paged",
     "kb200_decode_anchor_paged", "kb200_prefill_dense", "kb200_prefill_pool_scores",
     "kb200_prefill_sparse", "kb200_prefill_budgets", "kb200_selftest_umma", "kb200_read_status",
-    "kb200_decode_sparse_paged_noalloc",
+    "kb200_decode_sparse_paged_noalloc", "kb200_prefill_dense_fanout", "kb200_prefill_sparse_fanout",
 ]
 
 
@@ -41,6 +41,26 @@ class KvLayout(C.Structure):
 class ActLayout(C.Structure):
     _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_t", C.c_int64),
                 ("stride_h", C.c_int64)]
+
+
+MAX_FANOUT = 8
+
+
+class OutFanout(C.Structure):
+    """kb200_out_fanout: the output rows of a call go into `count` buffers [B, L, total_heads, D]."""
+    _fields_ = [("out", C.c_void_p * MAX_FANOUT), ("count", C.c_int32), ("total_heads", C.c_int32),
+                ("head_offset", C.c_int32)]
+
+
+def out_fanout(pointers, total_heads: int, head_offset: int) -> OutFanout:
+    """pointers: device addresses (ints) of the [B, L, total_heads, D] fp16 buffers, own buffer first."""
+    if not 1 <= len(pointers) <= MAX_FANOUT:
+        raise KascadeNativeError(f"fan-out of {len(pointers)} outputs (1..{MAX_FANOUT} supported)")
+    f = OutFanout()
+    for i, ptr in enumerate(pointers):
+        f.out[i] = int(ptr)
+    f.count, f.total_heads, f.head_offset = len(pointers), int(total_heads), int(head_offset)
+    return f
 
 
 _lib = None
@@ -82,6 +102,10 @@ def load() -> C.CDLL:
         lib.kb200_prefill_pool_scores.argtypes = [AL, AL, vp, f32, vp, i64, i32, i32, i32, i32, vp]
         lib.kb200_prefill_sparse.argtypes = [AL, AL, AL, vp, i64, vp, vp, f32, vp, vp, i32, i32, i32,
                                              i32, i32, vp]
+        FO = C.POINTER(OutFanout)
+        lib.kb200_prefill_dense_fanout.argtypes = [AL, AL, AL, f32, FO, vp, i32, i32, i32, i32, vp]
+        lib.kb200_prefill_sparse_fanout.argtypes = [AL, AL, AL, vp, i64, vp, vp, f32, FO, vp, i32, i32, i32,
+                                                    i32, i32, vp]
         lib.kb200_prefill_budgets.argtypes = [vp, vp, i32, i32, i32, i32, f32, i32, vp]
         lib.kb200_selftest_umma.argtypes = [vp, vp, vp, vp, vp]
         _lib = lib
@@ -245,13 +269,19 @@ def act_layout(x: torch.Tensor) -> ActLayout:
     return ActLayout(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2))
 
 
-def prefill_dense(q, k, v, scale, out, lse2):
-    """q [B,L,H,D], k/v [B,L,G,D] (views allowed); out [B,L,H,D] fp16 contiguous or None; lse2 [B,L,H] fp32 or None."""
+def prefill_dense(q, k, v, scale, out, lse2, fanout: Optional[OutFanout] = None):
+    """q [B,L,H,D], k/v [B,L,G,D] (views allowed); out [B,L,H,D] fp16 contiguous or None; lse2 [B,L,H] fp32 or None.
+    With `fanout` (see out_fanout) the rows go into several [B,L,total_heads,D] buffers instead of `out`."""
     lib = init(q.device.index)
     B, L, H, _ = q.shape
     G = k.shape[2]
     ql, kl = act_layout(q), act_layout(k)
     vl = act_layout(v) if v is not None else ActLayout(0, 0, 0, 0)
+    if fanout is not None:
+        _check(lib.kb200_prefill_dense_fanout(C.byref(ql), C.byref(kl), C.byref(vl), float(scale), C.byref(fanout),
+                                              _ptr(lse2), B, L, H, G, _stream()), "kb200_prefill_dense_fanout")
+        _launched(1)
+        return
     if out is not None:
         _want(out, torch.float16, "out")
         assert out.is_contiguous()
@@ -274,16 +304,25 @@ def prefill_pool_scores(q, k, lse2, scale, pooled):
     _launched(1)
 
 
-def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=None):
-    """tile_idx [B,G,T,kstride] int32, tile_count [B,G,T] int32, out [B,L,H,D] fp16 contiguous."""
+def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=None, fanout: Optional[OutFanout] = None):
+    """tile_idx [B,G,T,kstride] int32, tile_count [B,G,T] int32, out [B,L,H,D] fp16 contiguous.
+    With `fanout` (see out_fanout) the rows go into several [B,L,total_heads,D] buffers instead of `out`."""
     lib = init(q.device.index)
     B, L, H, _ = q.shape
     G = k.shape[2]
     ql, kl, vl = act_layout(q), act_layout(k), act_layout(v)
     _want(tile_idx, torch.int32, "tile_idx")
     _want(tile_count, torch.int32, "tile_count")
+    assert tile_idx.is_contiguous() and tile_count.is_contiguous()
+    if fanout is not None:
+        _check(lib.kb200_prefill_sparse_fanout(C.byref(ql), C.byref(kl), C.byref(vl), _ptr(tile_idx),
+                                               tile_idx.shape[-1], _ptr(tile_count), _ptr(head_map), float(scale),
+                                               C.byref(fanout), _ptr(lse2), B, L, H, G, tile_idx.shape[1],
+                                               _stream()), "kb200_prefill_sparse_fanout")
+        _launched(1)
+        return
     _want(out, torch.float16, "out")
-    assert tile_idx.is_contiguous() and tile_count.is_contiguous() and out.is_contiguous()
+    assert out.is_contiguous()
     _check(lib.kb200_prefill_sparse(C.byref(ql), C.byref(kl), C.byref(vl), _ptr(tile_idx), tile_idx.shape[-1],
                                     _ptr(tile_count), _ptr(head_map), float(scale), _ptr(out), _ptr(lse2), B, L, H,
                                     G, tile_idx.shape[1], _stream()), "kb200_prefill_sparse")

@@ -58,7 +58,9 @@ struct PrefillParams {
   const int32_t* tile_count;
   const int32_t* head_map;
   float scale2;
-  __half* out;
+  __half* out;                    // == out_fan[0] unless the output goes to several GPUs
+  __half* out_fan[KB200_MAX_FANOUT];   // outputs [B, L, H_out, D]: this GPU's own buffer and its peers'
+  int n_fan, H_out, h_off;        // number of outputs, heads of an output row, first head written by this call
   float* lse2;
   const float* lse2_in;
   float* pooled; int64_t pooled_stride;
@@ -736,22 +738,55 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       tc_fence_after();
       const float inv = 1.0f / l_tot;
       // this warpgroup stores output columns [wg*64, +64) of its rows
-      __half* orow = p.out + (((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)) * kD + wg * 64;
-#pragma unroll 1
+      // With KV heads sharded over GPUs the rows go straight into every GPU's [B, L, H_out, D] buffer
+      // (plain peer stores over NVLink: the all-gather of the outputs is this epilogue).  A thread
+      // holds 128 bytes of ITS row; eight neighbouring lanes transpose their eight 16-byte chunks so
+      // that every store instruction writes 128 contiguous bytes per row instead of 16.
+      uint4 w[8];
+#pragma unroll
       for (int part = 0; part < 2; ++part) {
         uint32_t oa[32];
         tmem_ld32(t_acc + wg * 64 + part * 32, oa);
         tmem_wait_ld();
-        if (tok < p.L) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            uint4 w;
-            w.x = pack2(__uint_as_float(oa[e * 8 + 0]) * inv, __uint_as_float(oa[e * 8 + 1]) * inv);
-            w.y = pack2(__uint_as_float(oa[e * 8 + 2]) * inv, __uint_as_float(oa[e * 8 + 3]) * inv);
-            w.z = pack2(__uint_as_float(oa[e * 8 + 4]) * inv, __uint_as_float(oa[e * 8 + 5]) * inv);
-            w.w = pack2(__uint_as_float(oa[e * 8 + 6]) * inv, __uint_as_float(oa[e * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + part * 32 + e * 8) = w;
-          }
+        for (int e = 0; e < 4; ++e) {
+          w[part * 4 + e].x = pack2(__uint_as_float(oa[e * 8 + 0]) * inv, __uint_as_float(oa[e * 8 + 1]) * inv);
+          w[part * 4 + e].y = pack2(__uint_as_float(oa[e * 8 + 2]) * inv, __uint_as_float(oa[e * 8 + 3]) * inv);
+          w[part * 4 + e].z = pack2(__uint_as_float(oa[e * 8 + 4]) * inv, __uint_as_float(oa[e * 8 + 5]) * inv);
+          w[part * 4 + e].w = pack2(__uint_as_float(oa[e * 8 + 6]) * inv, __uint_as_float(oa[e * 8 + 7]) * inv);
+        }
+      }
+#pragma unroll
+      for (int bit = 1; bit < 8; bit <<= 1) {
+        const bool up = (lane & bit) != 0;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          if (c & bit) continue;
+          const uint4 send = up ? w[c] : w[c | bit];
+          uint4 recv;
+          recv.x = __shfl_xor_sync(0xFFFFFFFFu, send.x, bit);
+          recv.y = __shfl_xor_sync(0xFFFFFFFFu, send.y, bit);
+          recv.z = __shfl_xor_sync(0xFFFFFFFFu, send.z, bit);
+          recv.w = __shfl_xor_sync(0xFFFFFFFFu, send.w, bit);
+          if (up) w[c] = recv; else w[c | bit] = recv;
+        }
+      }
+      // now w[j] is chunk (lane & 7) of row (row & ~7) + j
+      {
+        const int row0 = row & ~7, chunk = lane & 7;
+        int64_t offs[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int rj = row0 + j, tj = it.tile_start + (rj >> 2);
+          offs[j] = tj < p.L ? (((int64_t)it.b * p.L + tj) * p.H_out + p.h_off + it.g * kHg + (rj & 3)) * kD + wg * 64 + chunk * 8
+                             : -1;
+        }
+#pragma unroll 1
+        for (int f = 0; f < p.n_fan; ++f) {
+          __half* base = p.out_fan[f];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (offs[j] >= 0) *reinterpret_cast<uint4*>(base + offs[j]) = w[j];
         }
       }
       if (wg == 0 && p.lse2 && tok < p.L)
@@ -1017,6 +1052,36 @@ static int fill_act(const kb200_act_layout* a, const __half** ptr, int64_t* sb, 
   return 0;
 }
 
+// Where the output rows go: one buffer of this call's heads, or (fan != NULL) the same rows into
+// several [B, L, total_heads, D] buffers at head_offset.
+static int set_outputs(PrefillParams* p, void* out, const kb200_out_fanout* fan, int num_q_heads, const char* what) {
+  if (!fan) {
+    KB_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15) == 0, "%s: out must be 16-byte aligned", what);
+    p->out = static_cast<__half*>(out);
+    p->out_fan[0] = p->out;
+    p->n_fan = 1;
+    p->H_out = num_q_heads;
+    p->h_off = 0;
+    return 0;
+  }
+  KB_REQUIRE(fan->count >= 1 && fan->count <= KB200_MAX_FANOUT, "%s: fan-out of %d outputs (1..%d supported)", what,
+             fan->count, KB200_MAX_FANOUT);
+  KB_REQUIRE(fan->head_offset >= 0 && fan->total_heads >= num_q_heads &&
+                 fan->head_offset <= fan->total_heads - num_q_heads,
+             "%s: heads [%d, %d) do not fit an output row of %d heads", what, fan->head_offset,
+             fan->head_offset + num_q_heads, fan->total_heads);
+  for (int i = 0; i < fan->count; ++i) {
+    KB_REQUIRE(fan->out[i] && (reinterpret_cast<uintptr_t>(fan->out[i]) & 15) == 0,
+               "%s: fan-out output %d is null or not 16-byte aligned", what, i);
+    p->out_fan[i] = static_cast<__half*>(fan->out[i]);
+  }
+  p->out = p->out_fan[0];
+  p->n_fan = fan->count;
+  p->H_out = fan->total_heads;
+  p->h_off = fan->head_offset;
+  return 0;
+}
+
 // one CTA per SM (the kernels are persistent), fewer when there are fewer tiles than SMs
 static unsigned persistent_grid(const PrefillParams& p) {
   int64_t items = (int64_t)p.B * p.G * p.T;
@@ -1053,20 +1118,20 @@ extern "C" int kb200_read_status(int* host_out) {
   return 0;
 }
 
-extern "C" int kb200_prefill_dense(const kb200_act_layout* q, const kb200_act_layout* k,
-                                   const kb200_act_layout* v, float softmax_scale, void* out, float* lse2,
-                                   int batch, int seq_len, int num_q_heads, int num_kv_heads, void* stream) {
-  using namespace kb200;
+namespace kb200 {
+static int prefill_dense_impl(const kb200_act_layout* q, const kb200_act_layout* k, const kb200_act_layout* v,
+                              float softmax_scale, void* out, const kb200_out_fanout* fan, float* lse2, int batch,
+                              int seq_len, int num_q_heads, int num_kv_heads, void* stream) {
   if (check_shape(batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
+  if (fan) out = fan->count >= 1 ? fan->out[0] : nullptr;
   KB_REQUIRE(out || lse2, "prefill_dense: nothing to compute (out and lse2 are both null)");
   if (batch == 0 || seq_len == 0) return 0;
   PrefillParams p{};
   if (fill_act(q, &p.q, &p.q_sb, &p.q_st, &p.q_sh, "q") != 0) return -1;
   if (fill_act(k, &p.k, &p.k_sb, &p.k_st, &p.k_sh, "k") != 0) return -1;
   if (out && fill_act(v, &p.v, &p.v_sb, &p.v_st, &p.v_sh, "v") != 0) return -1;
-  KB_REQUIRE(!out || (reinterpret_cast<uintptr_t>(out) & 15) == 0, "prefill_dense: out must be 16-byte aligned");
+  if (out && set_outputs(&p, out, fan, num_q_heads, "prefill_dense") != 0) return -1;
   p.scale2 = softmax_scale * kLog2e;
-  p.out = static_cast<__half*>(out);
   p.lse2 = lse2;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
   CUtensorMap tq, tk, tv;
@@ -1081,6 +1146,24 @@ extern "C" int kb200_prefill_dense(const kb200_act_layout* q, const kb200_act_la
     tile_prefill_kernel<kDenseLse><<<grid, PfCfg<kDenseLse>::kThreads, kSmemNoV, (cudaStream_t)stream>>>(p, tq, tk, tv);
   KB_CHECK_LAUNCH("tile_prefill_kernel<dense>");
   return 0;
+}
+}  // namespace kb200
+
+extern "C" int kb200_prefill_dense(const kb200_act_layout* q, const kb200_act_layout* k,
+                                   const kb200_act_layout* v, float softmax_scale, void* out, float* lse2,
+                                   int batch, int seq_len, int num_q_heads, int num_kv_heads, void* stream) {
+  return kb200::prefill_dense_impl(q, k, v, softmax_scale, out, nullptr, lse2, batch, seq_len, num_q_heads,
+                                   num_kv_heads, stream);
+}
+
+extern "C" int kb200_prefill_dense_fanout(const kb200_act_layout* q, const kb200_act_layout* k,
+                                          const kb200_act_layout* v, float softmax_scale,
+                                          const kb200_out_fanout* fan, float* lse2, int batch, int seq_len,
+                                          int num_q_heads, int num_kv_heads, void* stream) {
+  using namespace kb200;
+  KB_REQUIRE(fan, "prefill_dense_fanout: fan is null");
+  return prefill_dense_impl(q, k, v, softmax_scale, nullptr, fan, lse2, batch, seq_len, num_q_heads, num_kv_heads,
+                            stream);
 }
 
 extern "C" int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_act_layout* k,
@@ -1110,18 +1193,18 @@ extern "C" int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_
   return 0;
 }
 
-extern "C" int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_layout* k,
-                                    const kb200_act_layout* v, const int32_t* tile_idx, int64_t idx_stride,
-                                    const int32_t* tile_count, const int32_t* head_map, float softmax_scale,
-                                    void* out, float* lse2, int batch, int seq_len, int num_q_heads,
-                                    int num_kv_heads, int idx_kv_heads, void* stream) {
-  using namespace kb200;
+namespace kb200 {
+static int prefill_sparse_impl(const kb200_act_layout* q, const kb200_act_layout* k, const kb200_act_layout* v,
+                               const int32_t* tile_idx, int64_t idx_stride, const int32_t* tile_count,
+                               const int32_t* head_map, float softmax_scale, void* out, const kb200_out_fanout* fan,
+                               float* lse2, int batch, int seq_len, int num_q_heads, int num_kv_heads,
+                               int idx_kv_heads, void* stream) {
   if (check_shape(batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
+  if (fan) out = fan->count >= 1 ? fan->out[0] : nullptr;
   KB_REQUIRE(tile_idx && tile_count && out, "prefill_sparse: null pointer");
   KB_REQUIRE(idx_stride >= 0, "prefill_sparse: negative idx_stride");
   KB_REQUIRE(idx_kv_heads == 0 || head_map || idx_kv_heads == num_kv_heads,
              "prefill_sparse: idx_kv_heads differs from num_kv_heads, so a head_map is required");
-  KB_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15) == 0, "prefill_sparse: out must be 16-byte aligned");
   if (batch == 0 || seq_len == 0) return 0;
   PrefillParams p{};
   if (fill_act(q, &p.q, &p.q_sb, &p.q_st, &p.q_sh, "q") != 0) return -1;
@@ -1136,7 +1219,7 @@ extern "C" int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_l
   p.tile_count = tile_count;
   p.head_map = head_map;
   p.scale2 = softmax_scale * kLog2e;
-  p.out = static_cast<__half*>(out);
+  if (set_outputs(&p, out, fan, num_q_heads, "prefill_sparse") != 0) return -1;
   p.lse2 = lse2;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
   CUtensorMap none{};                                    // the gather path uses no tensor maps
@@ -1144,4 +1227,25 @@ extern "C" int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_l
   tile_prefill_kernel<kSparse><<<grid, PfCfg<kSparse>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, none, none, none);
   KB_CHECK_LAUNCH("tile_prefill_kernel<sparse>");
   return 0;
+}
+}  // namespace kb200
+
+extern "C" int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_layout* k,
+                                    const kb200_act_layout* v, const int32_t* tile_idx, int64_t idx_stride,
+                                    const int32_t* tile_count, const int32_t* head_map, float softmax_scale,
+                                    void* out, float* lse2, int batch, int seq_len, int num_q_heads,
+                                    int num_kv_heads, int idx_kv_heads, void* stream) {
+  return kb200::prefill_sparse_impl(q, k, v, tile_idx, idx_stride, tile_count, head_map, softmax_scale, out, nullptr,
+                                    lse2, batch, seq_len, num_q_heads, num_kv_heads, idx_kv_heads, stream);
+}
+
+extern "C" int kb200_prefill_sparse_fanout(const kb200_act_layout* q, const kb200_act_layout* k,
+                                           const kb200_act_layout* v, const int32_t* tile_idx, int64_t idx_stride,
+                                           const int32_t* tile_count, const int32_t* head_map, float softmax_scale,
+                                           const kb200_out_fanout* fan, float* lse2, int batch, int seq_len,
+                                           int num_q_heads, int num_kv_heads, int idx_kv_heads, void* stream) {
+  using namespace kb200;
+  KB_REQUIRE(fan, "prefill_sparse_fanout: fan is null");
+  return prefill_sparse_impl(q, k, v, tile_idx, idx_stride, tile_count, head_map, softmax_scale, nullptr, fan, lse2,
+                             batch, seq_len, num_q_heads, num_kv_heads, idx_kv_heads, stream);
 }

@@ -93,11 +93,14 @@ class EfficientKascadeStrategy(Strategy):
     HF registration (for use without transformers), ``shard=(rank, world)`` makes this instance
     compute only its slice of the KV heads of every prefill layer (batch 1): the caller passes the
     local heads' q/k/v, anchor index rows are all-gathered over torch.distributed, and the per-head
-    outputs of every layer are all-gathered into ``self.gathered_out`` ([world, B, L, H/world, D])."""
+    outputs of every layer are all-gathered into ``self.gathered_out`` ([world, B, L, H/world, D]).
+    With ``peer_store=True`` there is no output all-gather: the prefill kernels store their rows
+    straight into every rank's [B, L, H, D] buffer over NVLink (``gathered_out`` then has that shape,
+    two buffers are used in turn, and it is complete after ``wait_gathers()``)."""
 
     def __init__(self, recompute_layers: List[int], model_name: str, k=1, tile_size=1, rolling_prefill=False,
                  block_size=12288, *, head_mapping: Optional[Sequence[Sequence[int]]] = None,
-                 register: bool = True, shard: Optional[tuple] = None):
+                 register: bool = True, shard: Optional[tuple] = None, peer_store: bool = False):
         if recompute_layers is None:
             raise ValueError("recompute_layers cannot be None for EfficientKascadeStrategy")
         if not (0 <= k <= 100):
@@ -115,6 +118,9 @@ class EfficientKascadeStrategy(Strategy):
             else self.get_head_mapping(model_name)
         self._register = register
         self._shard = tuple(shard) if shard is not None else None
+        self._peer_store = bool(peer_store) and self._shard is not None and self._shard[1] > 1
+        self._peer = None                       # kascade_b200.peer.PeerBuffers, allocated at the first prefill
+        self._peer_copy = 0
         self.gathered_out: Optional[torch.Tensor] = None
         self._pending = []
         # cross-layer state written by anchor layers (strategies/KascadeStrategy.py:95,133)
@@ -221,11 +227,15 @@ class EfficientKascadeStrategy(Strategy):
         G = k.shape[2]
         dev = q.device
         T = -(-L // self.tile_size)
-        out = torch.empty(B, L, H, D, dtype=torch.float16, device=dev)
+        fan = self._next_fanout(B, L, H, D, dev) if self._peer_store else None
+        out = torch.empty(B, L, H, D, dtype=torch.float16, device=dev) if fan is None else None
         if self.is_anchor(layer):
             kk = topk_budget(self.k, L, self.tile_size)
             lse2 = self._scratch("lse2", (B, L, H), torch.float32, dev)
-            nat.prefill_dense(q, k, v if layer == 0 else None, scaling, out if layer == 0 else None, lse2)
+            if layer == 0 and fan is not None:
+                nat.prefill_dense(q, k, v, scaling, None, lse2, fanout=fan)
+            else:
+                nat.prefill_dense(q, k, v if layer == 0 else None, scaling, out if layer == 0 else None, lse2)
             stride = -(-L // 128) * 128
             pooled = self._scratch("pooled", (B, G, T, stride), torch.float32, dev)
             nat.prefill_pool_scores(q, k, lse2, scaling, pooled)
@@ -244,7 +254,7 @@ class EfficientKascadeStrategy(Strategy):
             if self._tile_idx is None:
                 raise RuntimeError("reuse layer called before any anchor layer")
             head_map = self._mapping(layer, dev)
-        nat.prefill_sparse(q, k, v, self._tile_idx, self._tile_count, head_map, scaling, out)
+        nat.prefill_sparse(q, k, v, self._tile_idx, self._tile_count, head_map, scaling, out, fanout=fan)
         return self._publish(out)
 
     def _publish(self, out: torch.Tensor) -> torch.Tensor:
@@ -252,6 +262,11 @@ class EfficientKascadeStrategy(Strategy):
         the communicator's stream) and return the local slice."""
         if self._shard is None:
             return out
+        if self._peer_store:
+            # the kernel has written this rank's heads into every rank's buffer; hand back the local slice
+            full = self.gathered_out
+            h = full.shape[2] // self._shard[1]
+            return full[:, :, self._shard[0] * h:(self._shard[0] + 1) * h]
         import torch.distributed as dist
         world = self._shard[1]
         self._pending = [w for w in self._pending if not w[0].is_completed()]
@@ -262,10 +277,29 @@ class EfficientKascadeStrategy(Strategy):
         return out
 
     def wait_gathers(self):
-        """Block the current stream until every output all-gather started so far has finished."""
+        """Block the current stream until every rank's outputs started so far have arrived."""
+        if self._peer_store:
+            if self._peer is not None:
+                import torch.distributed as dist
+                # stream-ordered after this rank's kernels; completes once every rank has got here
+                dist.all_reduce(self._scratch("peer_sync", (1,), torch.int32, self._peer.tensors[0].device))
+            return
         for work, _, _ in self._pending:
             work.wait()
         self._pending = []
+
+    def _next_fanout(self, B: int, L: int, H: int, D: int, dev):
+        """Peer-store mode: the output buffers of this layer (two sets used in turn) as a kb200_out_fanout."""
+        rank, world = self._shard
+        shape = (B, L, H * world, D)
+        if self._peer is None or tuple(self._peer.tensors[0].shape) != shape:
+            from .peer import alloc_peer_buffers
+            self._peer = alloc_peer_buffers(shape, torch.float16, dev, copies=2)
+            self._peer_fans = [nat.out_fanout(self._peer.fanout_pointers(c, rank), H * world, rank * H)
+                               for c in range(2)]
+        self._peer_copy ^= 1
+        self.gathered_out = self._peer.tensors[self._peer_copy]
+        return self._peer_fans[self._peer_copy]
 
     # -- decode ------------------------------------------------------------------------------------
     def _decode_budgets(self, seq_lens: torch.Tensor, max_len: int):

@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, ret, peer_store):
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import torch.distributed as dist
@@ -27,7 +27,8 @@ def _worker(rank, world, port, ret):
     full = EfficientKascadeStrategy(list(c.anchors), "x/y", k=c.pct, tile_size=c.tile, rolling_prefill=c.rolling,
                                     head_mapping=c.head_mapping(), register=False)
     part = EfficientKascadeStrategy(list(c.anchors), "x/y", k=c.pct, tile_size=c.tile, rolling_prefill=c.rolling,
-                                    head_mapping=c.head_mapping(), register=False, shard=(rank, world))
+                                    head_mapping=c.head_mapping(), register=False, shard=(rank, world),
+                                    peer_store=peer_store)
     heads = shard_kv_heads(c.G, rank, world)
     hg = c.H // c.G
     qh = [g * hg + i for g in heads for i in range(hg)]
@@ -42,21 +43,25 @@ def _worker(rank, world, port, ret):
         part.wait_gathers()
         torch.cuda.synchronize()
         worst = max(worst, (out.float() - ref[:, :, qh].float()).abs().max().item())
-        gathered = part.gathered_out                                                    # [world,B,L,H/world,D]
-        whole = torch.cat([gathered[r] for r in range(world)], dim=2)
+        gathered = part.gathered_out
+        if peer_store:                                                                  # [B,L,H,D], written by both ranks' kernels
+            whole = gathered
+        else:                                                                           # [world,B,L,H/world,D]
+            whole = torch.cat([gathered[r] for r in range(world)], dim=2)
         worst = max(worst, (whole.float() - ref.float()).abs().max().item())
     ret[rank] = (worst, nat.read_status())
     dist.destroy_process_group()
 
 
-def test_sharded_prefill_matches_unsharded():
+@pytest.mark.parametrize("peer_store", [False, True], ids=["all_gather", "peer_store"])
+def test_sharded_prefill_matches_unsharded(peer_store):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
-    port = 29600 + (os.getpid() % 1000)
+    port = 29600 + (os.getpid() % 1000) + (500 if peer_store else 0)
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, ret, peer_store), nprocs=world, join=True)
     for r in range(world):
         worst, status = ret[r]
         assert status == 0
