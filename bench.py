@@ -116,9 +116,9 @@ def _time_cuda(fn, reps: int):
 # ------------------------------------------------------------------------------------------------
 # CPU baseline: the oracle port (oracle/kascade_oracle.py) on the host cores
 # ------------------------------------------------------------------------------------------------
-def cpu_prefill_sample(seq_len: int):
+def cpu_prefill_sample(seq_len: int, target_len: int = 32768, n_anchor: int = 4, n_reuse: int = 27):
     """Times one anchor-0, one reuse and one anchor>0 layer of the oracle at `seq_len`, fp32, and
-    extrapolates the 32-layer stack at 32 768 tokens by the L^2 work ratio."""
+    extrapolates the stack (1 + n_anchor + n_reuse layers) at `target_len` tokens by the L^2 work ratio."""
     from oracle.kascade_oracle import KascadeOracle
     from kascade_b200.workloads import PrefillWorkload
     wl = PrefillWorkload(seq_len=seq_len, layers=3, anchors=(0, 2))
@@ -131,8 +131,8 @@ def cpu_prefill_sample(seq_len: int):
         t0 = time.perf_counter()
         orc.attention_forward(layer, q, k, v, 128 ** -0.5)
         times.append(time.perf_counter() - t0)
-    scale = (32768 / seq_len) ** 2
-    stack_ms = (times[0] + 4 * times[2] + 27 * times[1]) * scale * 1e3
+    scale = (target_len / seq_len) ** 2
+    stack_ms = (times[0] + n_anchor * times[2] + n_reuse * times[1]) * scale * 1e3
     return stack_ms, times
 
 
@@ -161,21 +161,24 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def bench_decode(args, dev, world, peaks, batch=None):
+def bench_decode(args, dev, world, peaks, batch=None, ragged=False, rank=0):
     """Paged sparse decode, Llama-3.1-8B shape: batch 64 (split over the ranks), every sequence at context
     32 768, 16-token pages behind a seeded random block table, 32 layers with anchors {0,2,8,13,14}."""
     import torch.distributed as dist
     from kascade_b200 import EfficientKascadeStrategy, _native as nat
     from kascade_b200.workloads import DecodeWorkload
     scaling = 128 ** -0.5
-    dw = DecodeWorkload() if batch is None else DecodeWorkload(batch=batch)
-    assert dw.batch % world == 0
-    dw.batch //= world                                            # batch-sharded across ranks
+    if ragged:                                                    # 256 sequences, contexts uniform in [4096, 65536]
+        dw = DecodeWorkload.ragged(rank=rank, world=world, distinct_caches=2)
+    else:
+        dw = DecodeWorkload() if batch is None else DecodeWorkload(batch=batch)
+        assert dw.batch % world == 0
+        dw.batch //= world                                        # batch-sharded across ranks
     dstrat = EfficientKascadeStrategy(list(dw.anchors), "synthetic/llama31-8b-shape", k=dw.pct, tile_size=32,
                                       rolling_prefill=True, head_mapping=dw.head_mapping(), register=False)
     caches = [dw.make_cache(i, dev) for i in range(dw.distinct_caches)]
     qs = [dw.query(l, dev) for l in range(dw.layers)]
-    seq_lens = torch.full((dw.batch,), dw.context, dtype=torch.int32, device=dev)
+    seq_lens = torch.tensor(dw.seq_lens(), dtype=torch.int32, device=dev)
     dout = {}
 
     def dstep(_i=0):
@@ -192,7 +195,24 @@ def bench_decode(args, dev, world, peaks, batch=None):
     dl = (nat.launch_count - n0) // max(args.steps, 1)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    us_step = float(t.item()) * 1e3
+    us_eager = float(t.item()) * 1e3
+    # the same step captured once into a CUDA graph and replayed (every buffer of the step exists after
+    # the warm-up; the library allocates nothing and never synchronises)
+    us_graph, graph_note = None, None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            dstep()
+        for _ in range(max(args.warmup, 1)):
+            graph.replay()
+        tg = torch.tensor([_time_cuda(lambda i: graph.replay(), args.steps)], device=dev)
+        if world > 1:
+            dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        us_graph = float(tg.item()) * 1e3
+    except Exception as e:                                         # noqa: BLE001 - reported in the JSON line
+        graph_note = f"{type(e).__name__}: {e}"[:200]
+        torch.cuda.synchronize()
+    us_step = min(us_graph, us_eager) if us_graph is not None else us_eager
     # reuse-layer kernel alone (the dominant decode kernel by launches: 27 of 32 layers)
     kc, vc, bt = caches[0]
     kv = nat.kv_layout_paged(kc, vc, bt)
@@ -222,7 +242,10 @@ def bench_decode(args, dev, world, peaks, batch=None):
     dense_dec(0)
     t_dense = _time_cuda(dense_dec, 8) * 1e3
     gbs_reuse = dw.bytes_reuse() / (t_reuse * 1e-6) / 1e9
-    decode = {"us_per_step": us_step, "layers": dw.layers, "batch_per_gpu": dw.batch, "context": dw.context,
+    decode = {"us_per_step": us_step, "us_per_step_eager": us_eager, "us_per_step_graph": us_graph,
+              "cuda_graph": us_graph is not None,
+              "cuda_graph_note": graph_note, "layers": dw.layers, "batch_per_gpu": dw.batch,
+              "context": dw.context if dw.contexts is None else f"ragged, {min(dw.contexts)}..{max(dw.contexts)}",
               "page": dw.page, "topk": dw.budget(), "distinct_layer_caches": dw.distinct_caches,
               "gpu_launches": dl,
               "algorithmic_gb_per_step": dw.bytes_step() / 1e9,
@@ -248,6 +271,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seq-len", type=int, default=32768, help="prefill length (default: the benchmark's 32768)")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 4, 5],
+                    help="2 (default): the headline, prefill stack @32k + paged decode B=64; 4: the 131 072-token "
+                         "prefill stack (36 layers, QK-norm, KV heads sharded over the GPUs); 5: attention of the "
+                         "long-reasoning decode (256 sequences, contexts 4096..65536, batch-sharded)")
     ap.add_argument("--skip-decode", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -280,9 +307,30 @@ def main():
         if rank == 0:
             print(json.dumps({"metric": "decode only (profiling aid)", "decode": decode}), flush=True)
         return
+    if args.config == 5:
+        decode = bench_decode(args, dev, world, peaks, ragged=True, rank=rank)
+        if rank == 0:
+            print(json.dumps({"metric": "decode attention us/step, 256 sequences with contexts 4096..65536, 10% top-k",
+                              "value": decode["us_per_step"], "unit": "us", "n_gpus": world, "steps": args.steps,
+                              "warmup": args.warmup, "ms_per_step": decode["us_per_step"] / 1e3,
+                              "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+                              "data": "synthetic",
+                              "config": {"workload": "llama31_8b_decode_attention_ragged_b256", "parallelism":
+                                         f"batch shard x{world}", "cache_policy": "caches larger than L2"},
+                              "gpu_launches": decode["gpu_launches"], "device_status": nat.read_status(),
+                              "decode": decode}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---------------- prefill stack (headline) -----------------------------------------------------
-    wl = PrefillWorkload(seq_len=args.seq_len)
+    if args.config == 4:
+        from kascade_b200.workloads import QWEN3_ANCHORS
+        wl = PrefillWorkload(seq_len=131072 if args.seq_len == 32768 else args.seq_len, layers=36,
+                             anchors=QWEN3_ANCHORS, qk_norm=True)
+        args.skip_decode = True
+    else:
+        wl = PrefillWorkload(seq_len=args.seq_len)
     assert wl.G % world == 0, "KV heads must divide over the ranks"
     gpr = wl.G // world
     my_heads = list(range(rank * gpr, (rank + 1) * gpr))
@@ -456,22 +504,27 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         L = 4096
-        stack_ms, times = cpu_prefill_sample(L)
+        n_anchor = len([a for a in wl.anchors if a != 0])
+        n_reuse = wl.layers - n_anchor - 1
+        stack_ms, times = cpu_prefill_sample(L, wl.seq_len, n_anchor, n_reuse)
         cpu = {"value": stack_ms, "unit": "ms", "cores": torch.get_num_threads(), "kind": "port",
                "sample": (f"oracle port fp32: anchor-0 {times[0]:.1f}s, reuse {times[1]:.1f}s, anchor>0 {times[2]:.1f}s at "
-                          f"L={L}; 32-layer stack at 32768 extrapolated by (32768/{L})^2 with 1/27/4 layer weights")}
+                          f"L={L}; {wl.layers}-layer stack at {wl.seq_len} extrapolated by ({wl.seq_len}/{L})^2 with "
+                          f"1/{n_reuse}/{n_anchor} layer weights")}
 
     if rank == 0:
         line = {"metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": {"workload": "llama31_8b_prefill_attention_stack_32k" if args.seq_len == 32768
-                           else f"llama31_8b_prefill_attention_stack_{args.seq_len}",
+                "config": {"workload": (f"qwen3_8b_prefill_attention_stack_{wl.seq_len}_qknorm" if args.config == 4 else
+                                        "llama31_8b_prefill_attention_stack_32k" if wl.seq_len == 32768
+                                        else f"llama31_8b_prefill_attention_stack_{wl.seq_len}"),
                            "layers": wl.layers, "anchors": list(wl.anchors), "seq_len": wl.seq_len, "batch": wl.B,
                            "q_heads": wl.H, "kv_heads": wl.G, "head_dim": wl.D, "topk_pct": wl.pct, "tile": wl.tile,
                            "rolling": wl.rolling,
                            "parallelism": f"kv-head shard x{world}" + ("" if world == 1 else (", outputs all-gathered by NCCL" if args.no_peer_store else ", outputs stored into the peers by the kernel epilogue")),
-                           "cache_policy": "inputs larger than L2 (402 MB per layer, 32 distinct layers)"},
+                           "cache_policy": f"inputs larger than L2 ({wl.seq_len * (wl.H + 2 * wl.G) * wl.D * 2 / 1e6:.0f} MB "
+                                           f"per layer, {wl.layers} distinct layers)"},
                 "algorithmic_tflop_per_step": wl.flops_stack() / 1e12,
                 "achieved_tflops": wl.flops_stack() / (ms_step * 1e-3) / 1e12,
                 "gpu_launches": launches, "device_status": status, "clocks": clocks}

@@ -10,6 +10,7 @@ from typing import List, Sequence, Tuple
 import torch
 
 LLAMA_ANCHORS = (0, 2, 8, 13, 14)
+QWEN3_ANCHORS = (0, 3, 9, 17, 25)          # the long-prompt configuration (36 layers, QK-norm)
 
 
 @dataclass
@@ -25,6 +26,7 @@ class PrefillWorkload:
     tile: int = 32
     rolling: bool = True
     B: int = 1
+    qk_norm: bool = False             # RMS-normalise the rows of Q and K (unit gain), as Qwen3 does per head
 
     def head_mapping(self, seed: int = 1234) -> List[List[int]]:
         g = torch.Generator().manual_seed(seed)
@@ -51,6 +53,9 @@ class PrefillWorkload:
             pos = torch.randperm(L, generator=gen, device=device)[:n_hot]
             k[:, pos, g] += 2.5 * u
         q += 0.5 * u
+        if self.qk_norm:
+            q *= torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + 1e-6)
+            k *= torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + 1e-6)
         q, k, v = q.half(), k.half(), v.half()
         if heads is not None:                       # a KV-head shard: its KV heads and their query heads
             hg = H // G
@@ -101,6 +106,18 @@ class DecodeWorkload:
     pct: float = 10
     page: int = 16
     distinct_caches: int = 4          # layer caches held in HBM and cycled over the 32 layers
+    contexts: Sequence[int] = None    # per-sequence contexts (ragged batch); None: every sequence at `context`
+
+    def seq_lens(self) -> List[int]:
+        return [self.context] * self.batch if self.contexts is None else [int(c) for c in self.contexts]
+
+    @staticmethod
+    def ragged(batch_total: int = 256, lo: int = 4096, hi: int = 65536, seed: int = 0, rank: int = 0, world: int = 1,
+               **kw) -> "DecodeWorkload":
+        """The long-reasoning decode configuration: contexts uniform in [lo, hi] from `seed`, batch-sharded."""
+        lens = torch.randint(lo, hi + 1, (batch_total,), generator=torch.Generator().manual_seed(seed)).tolist()
+        mine = lens[rank::world]
+        return DecodeWorkload(batch=len(mine), context=max(mine), contexts=mine, **kw)
 
     def head_mapping(self, seed: int = 4321) -> List[List[int]]:
         return PrefillWorkload(layers=self.layers, anchors=self.anchors, G=self.G).head_mapping(seed)
@@ -109,7 +126,8 @@ class DecodeWorkload:
         """(k_cache, v_cache [pages, 16, G, D] fp16, block_table [B, pages_per_seq] int32)."""
         gen = torch.Generator(device=device).manual_seed(1000 + idx)
         pps = -(-self.context // self.page)
-        n_pages = self.batch * pps
+        per_seq = [-(-n // self.page) for n in self.seq_lens()]
+        n_pages = sum(per_seq)
         shape = (n_pages, self.page, self.G, self.D)
         k = torch.empty(shape, dtype=torch.float16, device=device)
         v = torch.empty(shape, dtype=torch.float16, device=device)
@@ -119,7 +137,13 @@ class DecodeWorkload:
             k[s:e] = (torch.randn((e - s,) + shape[1:], generator=gen, device=device) / self.D ** 0.5).half()
             v[s:e] = (torch.randn((e - s,) + shape[1:], generator=gen, device=device) / self.D ** 0.5).half()
         cpu_gen = torch.Generator().manual_seed(2000 + idx)
-        table = torch.randperm(n_pages, generator=cpu_gen).view(self.batch, pps).to(torch.int32).to(device)
+        perm = torch.randperm(n_pages, generator=cpu_gen).to(torch.int32)
+        table = torch.zeros(self.batch, pps, dtype=torch.int32)
+        o = 0
+        for b, n in enumerate(per_seq):
+            table[b, :n] = perm[o:o + n]
+            o += n
+        table = table.to(device)
         # sink keys at positions 0..3 of every sequence (K += 3 N(0,1))
         first = table[:, 0].long()
         k[first, :4] += (3 * torch.randn(self.batch, 4, self.G, self.D, generator=gen, device=device)).half()
@@ -135,11 +159,12 @@ class DecodeWorkload:
 
     # ---- algorithmic bytes per layer kind ---------------------------------------------------------
     def bytes_reuse(self) -> float:
-        k = self.budget()
-        return self.batch * self.G * k * (2 * self.D * 2 + 4) + 2 * self.batch * self.H * self.D * 2
+        from .strategy import topk_budget
+        keys = sum(topk_budget(self.pct, n, 32) for n in self.seq_lens())
+        return self.G * keys * (2 * self.D * 2 + 4) + 2 * self.batch * self.H * self.D * 2
 
     def bytes_dense_k(self) -> float:
-        return self.batch * self.G * self.context * self.D * 2
+        return self.G * sum(self.seq_lens()) * self.D * 2
 
     def bytes_step(self) -> float:
         n_anchor = len([a for a in self.anchors if a != 0])

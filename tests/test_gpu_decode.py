@@ -152,3 +152,53 @@ def test_anchor_decode_topk_band(case):
         for g in range(c.G):
             ok, msg = band_check(ref_pool[b, g], idx[b, g].tolist(), kk, L)
             assert ok, f"b{b} g{g}: {msg}"
+
+
+def test_decode_step_replays_from_a_cuda_graph():
+    """A whole decode step (anchor and reuse layers through the strategy's paged entry) captured into a
+    CUDA graph gives the same outputs as the eager step, also after the cache content changed: the
+    library allocates nothing, never synchronises and keeps no host-side state per call."""
+    from kascade_b200 import EfficientKascadeStrategy
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(23)
+    B, G, H, D, L, layers = 4, 8, 32, 128, 3000, 4
+    anchors = [0, 2]
+    hm = [list(range(G)), [3, 3, 0, 7, 1, 6, 2, 5], list(range(G)), [1, 0, 3, 2, 5, 4, 7, 6]]
+    strat = EfficientKascadeStrategy(anchors, "x/y", k=10, tile_size=32, rolling_prefill=True, head_mapping=hm,
+                                     register=False)
+    k = torch.randn(B, G, L, D, generator=g).half().to(dev)
+    v = torch.randn(B, G, L, D, generator=g).half().to(dev)
+    kc, vc, bt = paged_from_contiguous(k, v, seed=9)
+    qs = [(torch.randn(B, H, D, generator=g) / D ** 0.5).half().to(dev) for _ in range(layers)]
+    seq_lens = torch.tensor([L, L - 17, 2048, 1500], dtype=torch.int32, device=dev)
+    outs = [torch.zeros(B, H, D, dtype=torch.float16, device=dev) for _ in range(layers)]
+
+    def step():
+        for l in range(layers):
+            outs[l].copy_(strat.paged_decode_forward(l, qs[l], kc, vc, bt, seq_lens, D ** -0.5, L))
+
+    step()                                        # allocates every scratch buffer
+    torch.cuda.synchronize()
+    eager = [o.clone() for o in outs]
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for o in outs:
+        o.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    for l in range(layers):
+        assert torch.equal(outs[l], eager[l]), f"layer {l}: graph replay differs from the eager step"
+    # new cache content and queries, same addresses: the replay must follow the data
+    kc.mul_(0.5)
+    for q in qs:
+        q.neg_()
+    step()
+    torch.cuda.synchronize()
+    eager2 = [o.clone() for o in outs]
+    graph.replay()
+    torch.cuda.synchronize()
+    for l in range(layers):
+        assert torch.equal(outs[l], eager2[l]), f"layer {l}: graph replay did not pick up the new cache content"
+    from kascade_b200 import _native as nat
+    assert nat.read_status() == 0
