@@ -34,6 +34,8 @@
 #include <cuda.h>
 #include <stdlib.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "umma.cuh"
 
@@ -66,6 +68,7 @@ struct PrefillParams {
   float* pooled; int64_t pooled_stride;
   int B, L, H, G, T;
   int G_idx;                      // KV heads in the index tensors (>= G when heads are sharded)
+  int group;                      // (sequence, KV head) pairs whose tiles are walked together, divides B * G
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -133,10 +136,14 @@ struct TileItem {
 template <int MODE>
 __device__ __forceinline__ TileItem decode_item(const PrefillParams& p, int item) {
   TileItem it;
-  // items are ordered by descending tile index over all (sequence, KV head) pairs, i.e. by
-  // descending cost, so the boustrophedon hand-out gives every CTA the same amount of work
-  const int nbg = p.B * p.G;
-  const int r = item / nbg, bg = item - r * nbg;
+  // items are ordered by descending tile index, i.e. by descending cost, so the boustrophedon
+  // hand-out gives every CTA the same amount of work
+  // The (sequence, KV head) pairs are taken `p.group` at a time: all tiles of one group before the
+  // next, so that the K/V a group streams (group x L x 256 or 512 bytes) stay resident in L2 while
+  // the CTAs sweep them; the host picks the group size from L (all pairs together for short prompts).
+  const int per = p.group * p.T;
+  const int hi = item / per, lo = item - hi * per;
+  const int r = lo / p.group, bg = hi * p.group + (lo - r * p.group);
   it.t = p.T - 1 - r;
   it.b = bg / p.G;
   it.g = bg - it.b * p.G;
@@ -1082,6 +1089,16 @@ static int set_outputs(PrefillParams* p, void* out, const kb200_out_fanout* fan,
   return 0;
 }
 
+// How many (sequence, KV head) pairs to walk together: as many as keep their K (and V) within about
+// half of the 126 MB L2, at least one, a divisor of B * G.
+static int pick_group(int batch, int groups, int seq_len, bool with_v) {
+  const int64_t per_pair = (int64_t)seq_len * kD * 2 * (with_v ? 2 : 1);
+  const int nbg = batch * groups;
+  int want = (int)std::max<int64_t>(1, std::min<int64_t>(nbg, (64ll << 20) / std::max<int64_t>(per_pair, 1)));
+  while (nbg % want != 0) --want;
+  return want;
+}
+
 // one CTA per SM (the kernels are persistent), fewer when there are fewer tiles than SMs
 static unsigned persistent_grid(const PrefillParams& p) {
   int64_t items = (int64_t)p.B * p.G * p.T;
@@ -1134,6 +1151,7 @@ static int prefill_dense_impl(const kb200_act_layout* q, const kb200_act_layout*
   p.scale2 = softmax_scale * kLog2e;
   p.lse2 = lse2;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
+  p.group = pick_group(batch, num_kv_heads, seq_len, out != nullptr);
   CUtensorMap tq, tk, tv;
   if (make_act_map(&tq, p.q, p.q_sb, p.q_st, p.q_sh, num_q_heads, seq_len, batch, kHg, kTile, "q") != 0) return -1;
   if (make_act_map(&tk, p.k, p.k_sb, p.k_st, p.k_sh, num_kv_heads, seq_len, batch, 1, 128, "k") != 0) return -1;
@@ -1184,6 +1202,7 @@ extern "C" int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_
   p.pooled = pooled;
   p.pooled_stride = row_stride;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
+  p.group = pick_group(batch, num_kv_heads, seq_len, false);
   CUtensorMap tq, tk;
   if (make_act_map(&tq, p.q, p.q_sb, p.q_st, p.q_sh, num_q_heads, seq_len, batch, kHg, kTile, "q") != 0) return -1;
   if (make_act_map(&tk, p.k, p.k_sb, p.k_st, p.k_sh, num_kv_heads, seq_len, batch, 1, 128, "k") != 0) return -1;
@@ -1222,6 +1241,7 @@ static int prefill_sparse_impl(const kb200_act_layout* q, const kb200_act_layout
   if (set_outputs(&p, out, fan, num_q_heads, "prefill_sparse") != 0) return -1;
   p.lse2 = lse2;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
+  p.group = pick_group(batch, num_kv_heads, seq_len, true);
   CUtensorMap none{};                                    // the gather path uses no tensor maps
   dim3 grid(persistent_grid(p));
   tile_prefill_kernel<kSparse><<<grid, PfCfg<kSparse>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, none, none, none);
