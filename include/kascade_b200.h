@@ -244,6 +244,29 @@ int kb200_prefill_sparse_fanout(const kb200_act_layout* q, const kb200_act_layou
 int kb200_prefill_budgets(int32_t* n_valid, int32_t* k_row, int batch, int num_kv_heads,
                           int num_tiles, int k_max, float pct, int rolling, void* stream);
 
+/* ---- KV-cache write path ----------------------------------------------------------------------
+ * One pass over the new tokens of every sequence: optional per-head RMS norm of Q and K (Qwen3),
+ * rotary position embedding of Q and K, and the append of the new K / V rows to the cache in the layout
+ * the attention kernels read.  The reference has no such kernel: it receives rotated q/k/v from the
+ * Hugging Face attention module and pays transposes and `.contiguous()` copies before every kernel
+ * call (strategies/EfficientKascadeStrategy.py:144-150).  Arithmetic follows the Hugging Face modules
+ * step by step (LlamaRMSNorm, LlamaRotaryEmbedding, apply_rotary_pos_emb: fp32 norm rounded to fp16,
+ * fp16 gain, cos / sin in fp32 rounded to fp16, fp16 products and sum).
+ *   q_in        [B, T, H, D] fp16 view, or NULL (then q_out is ignored); q_out [B, T, H, D] fp16 contiguous
+ *   k_new/v_new [B, T, G, D] fp16 views: the rows to append (T = max_new)
+ *   start_pos   [B] int32: cache length of each sequence before the append (position of its first new token)
+ *   n_new       [B] int32 number of new tokens per sequence (<= max_new), or NULL (= max_new)
+ *   kv          the cache (written): paged with a block table that already covers the new positions, or contiguous
+ *   q_norm_gain / k_norm_gain  [D] fp16 or NULL (no norm);  norm_eps
+ *   inv_freq    [D/2] fp32 inverse frequencies of the model's rotary embedding (device memory), or NULL
+ *               (no rotary);  rope_scale multiplies cos and sin (1 for the default rope type)
+ */
+int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const kb200_act_layout* k_new,
+                   const kb200_act_layout* v_new, const int32_t* start_pos, const int32_t* n_new,
+                   const kb200_kv_layout* kv, const void* q_norm_gain, const void* k_norm_gain,
+                   float norm_eps, const float* inv_freq, float rope_scale, int batch, int max_new,
+                   int num_q_heads, int num_kv_heads, void* stream);
+
 /* ---- diagnostics ----------------------------------------------------------------------------- */
 
 /* Runs four 128x128x128 fp16 products through the tensor-core paths the prefill kernels rely on

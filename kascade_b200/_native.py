@@ -24,6 +24,7 @@ EXPORTS = [
     "kb200_decode_anchor_paged", "kb200_prefill_dense", "kb200_prefill_pool_scores",
     "kb200_prefill_sparse", "kb200_prefill_budgets", "kb200_selftest_umma", "kb200_read_status",
     "kb200_decode_sparse_paged_noalloc", "kb200_prefill_dense_fanout", "kb200_prefill_sparse_fanout",
+    "kb200_kv_write",
 ]
 
 
@@ -107,6 +108,8 @@ def load() -> C.CDLL:
         lib.kb200_prefill_sparse_fanout.argtypes = [AL, AL, AL, vp, i64, vp, vp, f32, FO, vp, i32, i32, i32,
                                                     i32, i32, vp]
         lib.kb200_prefill_budgets.argtypes = [vp, vp, i32, i32, i32, i32, f32, i32, vp]
+        lib.kb200_kv_write.argtypes = [AL, vp, AL, AL, vp, vp, C.POINTER(KvLayout), vp, vp, f32, vp, f32, i32, i32,
+                                       i32, i32, vp]
         lib.kb200_selftest_umma.argtypes = [vp, vp, vp, vp, vp]
         _lib = lib
     return _lib
@@ -326,6 +329,28 @@ def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=Non
     _check(lib.kb200_prefill_sparse(C.byref(ql), C.byref(kl), C.byref(vl), _ptr(tile_idx), tile_idx.shape[-1],
                                     _ptr(tile_count), _ptr(head_map), float(scale), _ptr(out), _ptr(lse2), B, L, H,
                                     G, tile_idx.shape[1], _stream()), "kb200_prefill_sparse")
+    _launched(1)
+
+
+def kv_write(q_in, q_out, k_new, v_new, start_pos, n_new, kv: KvLayout, q_gain=None, k_gain=None, eps=1e-6,
+             inv_freq=None, rope_scale=1.0):
+    """q_in [B,T,H,D] (or None), k_new / v_new [B,T,G,D] fp16 views; start_pos [B] int32; n_new [B] int32 or None;
+    kv: the cache to append to (kv_layout_paged / kv_layout_contiguous); inv_freq [D/2] fp32 or None."""
+    lib = init(k_new.device.index)
+    B, T, G, _ = k_new.shape
+    kl, vl = act_layout(k_new), act_layout(v_new)
+    ql = act_layout(q_in) if q_in is not None else ActLayout(0, 0, 0, 0)
+    H = q_in.shape[2] if q_in is not None else 0
+    if q_in is not None:
+        _want(q_out, torch.float16, "q_out")
+        assert q_out.is_contiguous() and q_out.shape == q_in.shape
+    _want(start_pos, torch.int32, "start_pos")
+    if inv_freq is not None:
+        _want(inv_freq, torch.float32, "inv_freq")
+        assert inv_freq.is_contiguous() and inv_freq.numel() == HEAD_DIM // 2
+    _check(lib.kb200_kv_write(C.byref(ql), _ptr(q_out), C.byref(kl), C.byref(vl), _ptr(start_pos), _ptr(n_new),
+                              C.byref(kv), _ptr(q_gain), _ptr(k_gain), float(eps), _ptr(inv_freq), float(rope_scale),
+                              B, T, H, G, _stream()), "kb200_kv_write")
     _launched(1)
 
 

@@ -1,0 +1,157 @@
+// KV-cache write path: optional per-head RMS norm of Q and K (Qwen3), rotary position embedding of Q
+// and K (the half-rotation convention of the Hugging Face Llama / Qwen3 models), and the append of the
+// new K / V rows into the paged (or contiguous) cache — one pass over the new tokens, so that the
+// attention kernels find the cache in the layout they read, without the transposes and
+// `.contiguous()` copies the reference's strategy pays before every kernel call
+// (strategies/EfficientKascadeStrategy.py:144-150).  Bound by HBM: each new row is read once and
+// written once.
+//
+// Arithmetic follows the Hugging Face modules step by step so that results agree to the last fp16
+// bit wherever sin / cos round the same way: the norm is computed in fp32 and rounded to fp16 before
+// the gain is applied (LlamaRMSNorm / Qwen3RMSNorm), cos and sin are computed in fp32 from
+// position * inv_freq[i] (the model's own inverse-frequency table, so every rope-scaling variant is
+// covered), scaled and rounded to fp16, and  x * cos + rotate_half(x) * sin  is evaluated in fp16 with
+// a rounding after each product and after the sum (apply_rotary_pos_emb).
+#include "common.cuh"
+
+namespace kb200 {
+
+struct KvWriteParams {
+  const __half* q_in; __half* q_out; int64_t q_sb, q_st, q_sh;      // [B, T, H, D] views (q_out contiguous)
+  const __half* k_new; int64_t k_sb, k_st, k_sh;                     // [B, T, G, D]
+  const __half* v_new; int64_t v_sb, v_st, v_sh;
+  const int32_t* start_pos;                                           // [B] cache length before the append
+  const int32_t* n_new;                                               // [B] or null (= T)
+  __half* k_cache; __half* v_cache;
+  int64_t c_sb, c_sp, c_st, c_sh;                                     // cache strides (batch, page, token, head)
+  const int32_t* block_table; int bt_stride; int page_shift, page_mask;
+  const __half* q_gain; const __half* k_gain; float eps;              // RMS-norm gains [D] or null
+  const float* inv_freq; float rope_scale;                            // [D/2] inverse frequencies or null (no rotary)
+  int B, T, H, G;
+};
+
+// One warp per (sequence, new token, head): lane l holds elements 2l, 2l+1 of the first half and
+// 2l, 2l+1 of the second half (the two elements a rotation pairs up sit in the same lane).
+__global__ void __launch_bounds__(256) kv_write_kernel(const KvWriteParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int heads = p.H + 2 * p.G;                                   // Q heads, K heads, V heads
+  const int64_t total = (int64_t)p.B * p.T * heads;
+  if (wid >= total) return;
+  const int h = (int)(wid % heads);
+  const int t = (int)((wid / heads) % p.T);
+  const int b = (int)(wid / ((int64_t)heads * p.T));
+  const int n = p.n_new ? p.n_new[b] : p.T;
+  if (t >= n) return;
+  const int pos = p.start_pos[b] + t;
+  const int kind = h < p.H ? 0 : (h < p.H + p.G ? 1 : 2);            // 0 = Q, 1 = K, 2 = V
+  const int hh = kind == 0 ? h : (kind == 1 ? h - p.H : h - p.H - p.G);
+  if (kind == 0 && !p.q_in) return;
+  const __half* src = kind == 0 ? p.q_in + b * p.q_sb + t * p.q_st + hh * p.q_sh
+                    : kind == 1 ? p.k_new + b * p.k_sb + t * p.k_st + hh * p.k_sh
+                                : p.v_new + b * p.v_sb + t * p.v_st + hh * p.v_sh;
+  __half2 lo = reinterpret_cast<const __half2*>(src)[lane];          // elements 2l, 2l+1
+  __half2 hi = reinterpret_cast<const __half2*>(src + kD / 2)[lane];  // elements 64+2l, 64+2l+1
+  if (kind != 2) {
+    const __half* gain = kind == 0 ? p.q_gain : p.k_gain;
+    if (gain) {
+      // x.float() * rsqrt(mean(x^2) + eps), rounded to fp16, times the gain (fp16 product)
+      const float2 a = __half22float2(lo), c = __half22float2(hi);
+      float ss = a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+      const float r = rsqrtf(ss / kD + p.eps);
+      const __half2 g_lo = reinterpret_cast<const __half2*>(gain)[lane];
+      const __half2 g_hi = reinterpret_cast<const __half2*>(gain + kD / 2)[lane];
+      lo = __hmul2_rn(g_lo, __floats2half2_rn(a.x * r, a.y * r));
+      hi = __hmul2_rn(g_hi, __floats2half2_rn(c.x * r, c.y * r));
+    }
+    if (p.inv_freq) {
+      // angle_i = pos * inv_freq[i], i = 2l and 2l+1 (the same i serves element i and element i + D/2)
+      const float2 f = reinterpret_cast<const float2*>(p.inv_freq)[lane];
+      float s0, c0, s1, c1;
+      sincosf((float)pos * f.x, &s0, &c0);
+      sincosf((float)pos * f.y, &s1, &c1);
+      const __half2 cs = __floats2half2_rn(c0 * p.rope_scale, c1 * p.rope_scale);
+      const __half2 sn = __floats2half2_rn(s0 * p.rope_scale, s1 * p.rope_scale);
+      // first half:  x_lo * cos + (-x_hi) * sin ; second half:  x_hi * cos + x_lo * sin
+      // (the _rn forms are never contracted into a fused multiply-add, which would skip a rounding)
+      const __half2 new_lo = __hadd2_rn(__hmul2_rn(lo, cs), __hmul2_rn(__hneg2(hi), sn));
+      const __half2 new_hi = __hadd2_rn(__hmul2_rn(hi, cs), __hmul2_rn(lo, sn));
+      lo = new_lo;
+      hi = new_hi;
+    }
+  }
+  __half* dst;
+  if (kind == 0) {
+    dst = p.q_out + (((int64_t)b * p.T + t) * p.H + hh) * kD;
+  } else {
+    const int page = pos >> p.page_shift, slot = pos & p.page_mask;
+    const int64_t phys = p.block_table ? (int64_t)p.block_table[(int64_t)b * p.bt_stride + page] : page;
+    dst = (kind == 1 ? p.k_cache : p.v_cache) + b * p.c_sb + phys * p.c_sp + slot * p.c_st + hh * p.c_sh;
+  }
+  reinterpret_cast<__half2*>(dst)[lane] = lo;
+  reinterpret_cast<__half2*>(dst + kD / 2)[lane] = hi;
+}
+
+}  // namespace kb200
+
+extern "C" int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const kb200_act_layout* k_new,
+                              const kb200_act_layout* v_new, const int32_t* start_pos, const int32_t* n_new,
+                              const kb200_kv_layout* kv, const void* q_norm_gain, const void* k_norm_gain,
+                              float norm_eps, const float* inv_freq, float rope_scale, int batch, int max_new,
+                              int num_q_heads, int num_kv_heads, void* stream) {
+  using namespace kb200;
+  KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
+  KB_REQUIRE(k_new && k_new->ptr && v_new && v_new->ptr && start_pos && kv && kv->k && kv->v,
+             "kv_write: null pointer");
+  KB_REQUIRE(batch >= 0 && max_new >= 0 && num_kv_heads > 0 && num_q_heads >= 0, "kv_write: bad sizes");
+  KB_REQUIRE(kv->page_size >= 1 && (kv->page_size & (kv->page_size - 1)) == 0,
+             "kv_write: page_size must be a power of two (got %d)", kv->page_size);
+  KB_REQUIRE(!inv_freq || (reinterpret_cast<uintptr_t>(inv_freq) & 7) == 0, "kv_write: inv_freq must be 8-byte aligned");
+  const bool with_q = q_in && q_in->ptr;
+  KB_REQUIRE(!with_q || q_out, "kv_write: q_in given without q_out");
+  auto aligned = [](const void* ptr, int64_t a, int64_t b2, int64_t c) {
+    return (reinterpret_cast<uintptr_t>(ptr) & 3) == 0 && a % 2 == 0 && b2 % 2 == 0 && c % 2 == 0;
+  };
+  KB_REQUIRE(aligned(k_new->ptr, k_new->stride_b, k_new->stride_t, k_new->stride_h) &&
+                 aligned(v_new->ptr, v_new->stride_b, v_new->stride_t, v_new->stride_h) &&
+                 (!with_q || aligned(q_in->ptr, q_in->stride_b, q_in->stride_t, q_in->stride_h)) &&
+                 aligned(kv->k, kv->stride_batch, kv->stride_page, kv->stride_token) &&
+                 aligned(kv->v, kv->stride_head, 0, 0),
+             "kv_write: pointers must be 4-byte aligned and strides even");
+  if (batch == 0 || max_new == 0) return 0;
+  KvWriteParams p{};
+  if (with_q) {
+    p.q_in = static_cast<const __half*>(q_in->ptr);
+    p.q_sb = q_in->stride_b; p.q_st = q_in->stride_t; p.q_sh = q_in->stride_h;
+    p.q_out = static_cast<__half*>(q_out);
+  }
+  p.k_new = static_cast<const __half*>(k_new->ptr);
+  p.k_sb = k_new->stride_b; p.k_st = k_new->stride_t; p.k_sh = k_new->stride_h;
+  p.v_new = static_cast<const __half*>(v_new->ptr);
+  p.v_sb = v_new->stride_b; p.v_st = v_new->stride_t; p.v_sh = v_new->stride_h;
+  p.start_pos = start_pos;
+  p.n_new = n_new;
+  p.k_cache = static_cast<__half*>(const_cast<void*>(kv->k));
+  p.v_cache = static_cast<__half*>(const_cast<void*>(kv->v));
+  p.c_sb = kv->stride_batch; p.c_sp = kv->stride_page; p.c_st = kv->stride_token; p.c_sh = kv->stride_head;
+  p.block_table = kv->block_table;
+  p.bt_stride = kv->block_table_stride;
+  int shift = 0;
+  while ((1 << shift) < kv->page_size) ++shift;
+  p.page_shift = shift;
+  p.page_mask = kv->page_size - 1;
+  p.q_gain = static_cast<const __half*>(q_norm_gain);
+  p.k_gain = static_cast<const __half*>(k_norm_gain);
+  p.eps = norm_eps;
+  p.inv_freq = inv_freq;
+  p.rope_scale = rope_scale;
+  p.B = batch; p.T = max_new; p.H = with_q ? num_q_heads : 0; p.G = num_kv_heads;
+  const int64_t warps = (int64_t)batch * max_new * (p.H + 2 * p.G);
+  const int64_t blocks = (warps + 7) / 8;
+  KB_REQUIRE(blocks < (1ll << 31), "kv_write: too many rows for one launch");
+  kv_write_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+  KB_CHECK_LAUNCH("kv_write_kernel");
+  return 0;
+}

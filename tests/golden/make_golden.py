@@ -90,7 +90,7 @@ def run_case(KS, case, workdir):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of microsoft/kascade (read only)")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     KS = load_reference(args.reference)

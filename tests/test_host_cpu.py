@@ -90,3 +90,32 @@ def test_workload_accounting():
     dw = DecodeWorkload()
     assert dw.budget() == 3244
     assert abs(dw.bytes_dense_k() / 1e9 - 4.295) < 0.01
+
+
+def test_ragged_decode_workload_accounting():
+    """The long-reasoning decode configuration: 256 seeded contexts in [4096, 65536], batch-sharded round-robin;
+    algorithmic bytes are sums over the sequences (budgets follow the reference's formula per sequence)."""
+    from kascade_b200.strategy import topk_budget
+    from kascade_b200.workloads import DecodeWorkload
+    whole = DecodeWorkload.ragged()
+    assert whole.batch == 256 and min(whole.contexts) >= 4096 and max(whole.contexts) <= 65536
+    assert whole.context == max(whole.contexts)
+    parts = [DecodeWorkload.ragged(rank=r, world=4) for r in range(4)]
+    assert sorted(sum((list(p.contexts) for p in parts), [])) == sorted(whole.contexts)
+    assert abs(sum(p.bytes_step() for p in parts) - whole.bytes_step()) < 1e-6 * whole.bytes_step()
+    keys = sum(topk_budget(10, n, 32) for n in whole.contexts)
+    assert whole.bytes_reuse() == 8 * keys * (2 * 128 * 2 + 4) + 2 * 256 * 32 * 128 * 2
+    uniform = DecodeWorkload()
+    assert uniform.seq_lens() == [32768] * 64
+    assert uniform.bytes_dense_k() == 64 * 8 * 32768 * 128 * 2
+
+
+def test_long_prompt_workload_is_normalised():
+    from kascade_b200.workloads import PrefillWorkload, QWEN3_ANCHORS
+    wl = PrefillWorkload(seq_len=256, layers=36, anchors=QWEN3_ANCHORS, qk_norm=True)
+    q, k, v = wl.layer_inputs(3, "cpu")
+    rms_q = q.float().pow(2).mean(-1).sqrt()
+    rms_k = k.float().pow(2).mean(-1).sqrt()
+    assert (rms_q - 1).abs().max() < 5e-3 and (rms_k - 1).abs().max() < 5e-3
+    hm = wl.head_mapping()
+    assert len(hm) == 36 and all(hm[a] == list(range(8)) for a in QWEN3_ANCHORS)
