@@ -166,3 +166,42 @@ def test_strategy_prefill_end_to_end(case):
         else:
             ref = sparse_prefill_output(q, k, v, rows[:, c.head_mapping()[layer]], scaling, c.tile)
         assert_close(out, ref, what=f"{c.name} strategy layer {layer}")
+
+
+@pytest.mark.parametrize("direction", ["growing", "shrinking"])
+def test_row_reference_moves_across_blocks(direction):
+    """Scores whose maximum grows (or shrinks) by far more than 2^8 from one 128-key block to the next: the
+    shared accumulator of the two softmax streams has to be rescaled on nearly every block (or never), with
+    the reference handed from one stream to the other in block order."""
+    from kascade_b200 import _native as nat
+    g = torch.Generator().manual_seed(7)
+    B, H, G, L, D = 1, 8, 2, 1024 + 32, 128
+    u = torch.randn(D, generator=g)
+    u = u / u.norm()
+    q = (0.05 * torch.randn(B, H, L, D, generator=g) + 4.0 * u).half().float()
+    ramp = (torch.arange(L) // 128).float()
+    if direction == "shrinking":
+        ramp = ramp.max() - ramp
+    # logit of key j ~ 4 * ramp_j * 4 / sqrt(128) * ... : steps of about 12 in log2 units between blocks
+    k = (0.05 * torch.randn(B, G, L, D, generator=g) + (2.1 * ramp)[None, None, :, None] * u).half().float()
+    v = torch.randn(B, G, L, D, generator=g).half().float()
+    scale = 1.0
+    ref_o, ref_lse = _dense_ref(q, k, v, scale)
+    qd, kd, vd = (_dev(x).transpose(1, 2) for x in (q, k, v))
+    out = torch.zeros(B, L, H, D, dtype=torch.float16, device="cuda")
+    lse = torch.zeros(B, L, H, dtype=torch.float32, device="cuda")
+    nat.prefill_dense(qd, kd, vd, scale, out, lse)
+    _status_ok()
+    assert_close(out, ref_o, what=f"dense prefill, {direction} maxima")
+    assert (lse.cpu() - ref_lse).abs().max() < 2e-3
+    lse_only = torch.zeros_like(lse)
+    nat.prefill_dense(qd, kd, None, scale, None, lse_only)
+    assert (lse_only.cpu() - ref_lse).abs().max() < 2e-3
+    # sparse path over all earlier keys (budget = everything): same result as dense
+    T = -(-L // 32)
+    idx = torch.arange(L, dtype=torch.int32).repeat(B, G, T, 1).contiguous().cuda()
+    cnt = (torch.arange(T, dtype=torch.int32) * 32).repeat(B, G, 1).contiguous().cuda()
+    sp = torch.zeros_like(out)
+    nat.prefill_sparse(qd, kd, vd, idx, cnt, None, scale, sp)
+    _status_ok()
+    assert_close(sp, ref_o, what=f"sparse prefill over all keys, {direction} maxima")
