@@ -1,0 +1,43 @@
+"""The strategy as a Hugging Face attention implementation (GPU): a small random-init Llama with the
+benchmark's attention shape (32 query / 8 KV heads of 128) runs its prefill through `efficient_kascade`.
+With k = 100 % every earlier key fits the budget, so the prefill must reproduce dense attention."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_llama_prefill_and_decode_through_the_registry():
+    transformers = pytest.importorskip("transformers")
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from kascade_b200 import EfficientKascadeStrategy, _native as nat
+    torch.manual_seed(0)
+    layers = 3
+    cfg = LlamaConfig(hidden_size=4096, intermediate_size=512, num_hidden_layers=layers, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=128, vocab_size=320, max_position_embeddings=4096,
+                      attn_implementation="sdpa")
+    model = LlamaForCausalLM(cfg).to("cuda", torch.float16).eval()
+    ids = torch.randint(0, 320, (1, 480), device="cuda")
+    with torch.no_grad():
+        ref = model(ids, use_cache=True)
+    strat = EfficientKascadeStrategy([0, 2], "x/y", k=100, tile_size=32, rolling_prefill=False,
+                                     head_mapping=[list(range(8)), [3, 3, 0, 7, 1, 6, 2, 5], list(range(8))])
+    model.config._attn_implementation = strat.name
+    with torch.no_grad():
+        got = model(ids, use_cache=True)
+    assert nat.read_status() == 0
+    assert nat.launch_count > 0, "the model did not go through the library"
+    err = (got.logits.float() - ref.logits.float()).abs().max().item()
+    scale = ref.logits.float().abs().max().item()
+    assert err < 2e-2 * max(scale, 1.0), f"prefill logits differ from dense attention by {err} (scale {scale})"
+    # one decode step on the cache the prefill produced: anchors select all but the 32 weakest keys, reuse layers
+    # attend to exactly those keys, so the step stays close to dense attention
+    nxt = torch.randint(0, 320, (1, 1), device="cuda")
+    with torch.no_grad():
+        step = model(nxt, past_key_values=got.past_key_values, use_cache=True)
+        model.config._attn_implementation = "sdpa"
+        step_ref = model(nxt, past_key_values=ref.past_key_values, use_cache=True)
+    assert nat.read_status() == 0
+    assert bool(torch.isfinite(step.logits).all())
+    rel = (step.logits.float() - step_ref.logits.float()).abs().max().item() / max(step_ref.logits.float().abs().max().item(), 1.0)
+    assert rel < 0.25, f"decode logits far from dense attention: {rel}"
