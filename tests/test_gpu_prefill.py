@@ -205,3 +205,34 @@ def test_row_reference_moves_across_blocks(direction):
     nat.prefill_sparse(qd, kd, vd, idx, cnt, None, scale, sp)
     _status_ok()
     assert_close(sp, ref_o, what=f"sparse prefill over all keys, {direction} maxima")
+
+
+def test_rejected_arguments_name_the_problem():
+    """Bad calls return an error with a message (nothing is launched): fan-out limits, head ranges, strides."""
+    from kascade_b200 import _native as nat
+    dev = torch.device("cuda")
+    B, L, H, G, D = 1, 64, 8, 2, 128
+    q = torch.zeros(B, L, H, D, dtype=torch.float16, device=dev)
+    k = torch.zeros(B, L, G, D, dtype=torch.float16, device=dev)
+    out = torch.zeros(B, L, H, D, dtype=torch.float16, device=dev)
+    with pytest.raises(nat.KascadeNativeError, match="1..8"):
+        nat.out_fanout([out.data_ptr()] * 9, H, 0)
+    fan = nat.out_fanout([out.data_ptr()], H, 4)                       # heads [4, 12) of an 8-head row
+    with pytest.raises(nat.KascadeNativeError, match="do not fit"):
+        nat.prefill_dense(q, k, k, 0.1, None, None, fanout=fan)
+    fan = nat.out_fanout([out.data_ptr() + 2], H, 0)                   # misaligned
+    with pytest.raises(nat.KascadeNativeError, match="aligned"):
+        nat.prefill_dense(q, k, k, 0.1, None, None, fanout=fan)
+    with pytest.raises(nat.KascadeNativeError, match="nothing to compute"):
+        nat.prefill_dense(q, k, k, 0.1, None, None)
+    with pytest.raises(nat.KascadeNativeError, match="query heads"):
+        nat.prefill_dense(q[:, :, :6], k, k, 0.1, out[:, :, :6].contiguous(), None)
+    idx = torch.zeros(B, G, 2, 4, dtype=torch.int32, device=dev)
+    cnt = torch.zeros(B, G, 2, dtype=torch.int32, device=dev)
+    with pytest.raises(nat.KascadeNativeError, match="head_map"):
+        nat.prefill_sparse(q[:, :, :4], k[:, :, :1], k[:, :, :1], idx, cnt, None, 0.1, out[:, :, :4].contiguous())
+    kc = torch.zeros(4, 12, G, D, dtype=torch.float16, device=dev)      # page size 12 is not a power of two
+    bt = torch.zeros(B, 4, dtype=torch.int32, device=dev)
+    with pytest.raises(nat.KascadeNativeError, match="power of two"):
+        nat.kv_write(None, None, k, k, torch.zeros(B, dtype=torch.int32, device=dev), None, nat.kv_layout_paged(kc, kc, bt))
+    assert nat.read_status() == 0
