@@ -115,7 +115,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 // the 7 x 32 KB tiles, the alignment padding and this block together stay inside the 227 KB limit.
 struct PfShared {
   uint64_t bar_q, bar_qempty, bar_kfull[kNKMax], bar_kempty[kNKMax], bar_vfull[kNV], bar_vempty[kNV];
-  uint64_t bar_sfull[3], bar_pready[3], bar_odone[3], bar_x, bar_ofree, bar_lse[2], bar_sfree[2];
+  uint64_t bar_sfull[3], bar_pready[3], bar_odone[3], bar_x, bar_ofree, bar_lse[3], bar_sfree[2];
   uint32_t tmem;
   int give_up;
   union {
@@ -125,7 +125,9 @@ struct PfShared {
 };
 static_assert(sizeof(PfShared) <= 2560, "PfShared grew");
 constexpr int kSmemAttn = kStageBytes * (1 + 3 + kNV) + kPadAllowance + 2560;   // = 232448, the sm_100 limit
-constexpr int kSmemNoV = kStageBytes * (1 + kNKMax) + kPadAllowance + 2560;
+constexpr int kNKNoV = 5;                     // K ring of the modes without V
+constexpr int kXchgNoV = 3 * 2 * 128 * 4;     // their exchange area behind PfShared: three streams x two values x 128 rows
+constexpr int kSmemNoV = kStageBytes * (1 + kNKNoV) + kPadAllowance + 2560 + kXchgNoV;
 
 // One work item = one query tile of one KV head of one sequence.
 struct TileItem {
@@ -172,12 +174,15 @@ struct PfCfg {
   static constexpr bool kHasV = MODE == kDenseAttn || MODE == kSparse;
   static constexpr bool kIsPool = MODE == kPool;
   static constexpr bool kGather = MODE == kSparse;
-  static constexpr int kThreads = kGather ? 512 : 384;
-  static constexpr int kNK = kHasV ? 3 : kNKMax;
+  // softmax warpgroups (streams): two with V; three without V, where nothing but latency limits them
+  static constexpr int kStreams = kHasV ? 2 : 3;
+  static constexpr int kSoftmaxWarps = 4 * kStreams;
+  static constexpr int kThreads = (kGather || !kHasV) ? 512 : 384;
+  static constexpr int kNK = kHasV ? 3 : kNKNoV;
   static constexpr int kProducerArrivals = kGather ? 128 : 1;   // Q tile: all gather threads
   static constexpr int kRingArrivals = kGather ? 96 : 1;        // K / V stage: three gather warps each
-  static constexpr int kProducerWarp0 = 8;
-  static constexpr int kMmaWarp = kGather ? 12 : 9;
+  static constexpr int kProducerWarp0 = kHasV ? 8 : 12;
+  static constexpr int kMmaWarp = kGather ? 12 : (kHasV ? 9 : 13);
 };
 
 // Optional timeline tracing (compile with -DKB200_TRACE): up to six roles of CTA 0 record
@@ -223,6 +228,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   uint8_t* smem = smem_raw + pad;
   constexpr int kTiles = 1 + kNK + (HAS_V ? kNV : 0);
   PfShared& sh = *reinterpret_cast<PfShared*>(smem + kTiles * kStageBytes);
+  // modes without V: [3 streams][2][128] floats behind PfShared (partial row statistics / staged lse values)
+  float* const xchg3 = reinterpret_cast<float*>(smem + kTiles * kStageBytes + 2560);
   uint64_t* bar_kfull = sh.bar_kfull;
   uint64_t* bar_kempty = sh.bar_kempty;
   uint64_t* bar_vfull = sh.bar_vfull;
@@ -246,9 +253,10 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       mbar_init(&bar_pready[i], 128);
       mbar_init(&bar_odone[i], 1);
     }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sh.bar_lse[i], 128); mbar_init(&sh.bar_sfree[i], 128); }
-    mbar_init(&sh.bar_x, kSoftmaxThreads);
-    mbar_init(&sh.bar_ofree, kSoftmaxThreads);
+    for (int i = 0; i < 3; ++i) mbar_init(&sh.bar_lse[i], 128);
+    for (int i = 0; i < 2; ++i) mbar_init(&sh.bar_sfree[i], 128);
+    mbar_init(&sh.bar_x, Cfg::kSoftmaxWarps * 32);
+    mbar_init(&sh.bar_ofree, Cfg::kSoftmaxWarps * 32);
     mbar_fence_init();
     give_up = 0;
   }
@@ -413,47 +421,18 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   };
 
   // ================================ MMA issuer, modes without V ===================================
-  // One warp issues Q.K^T one block ahead of the softmax, alternating between the two S buffers.
+  // One warp issues Q.K^T as far ahead of the softmax as the S buffers allow, block j into buffer j mod 3.
   auto mma_role = [&]() {
     constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
-    int kc = 0, qn = 0;
-    int issued0 = 0, issued1 = 0;                      // Q.K^T blocks written into S buffer 0 / 1 so far
-    int released0 = 0, released1 = 0;                  // ... and how many of them the softmax side consumed
+    constexpr int NS = Cfg::kStreams;                   // S buffers = softmax streams; block j goes to buffer j % NS
+    int k_st = 0, k_ph = 0, qn = 0;
+    int issued[NS], released[NS];                      // blocks written into / consumed from each S buffer so far
+#pragma unroll
+    for (int i = 0; i < NS; ++i) issued[i] = released[i] = 0;
     bool ok = true;
     // the whole warp runs this role with uniform control flow; one elected lane issues
     const bool el = elect_one();
-    // S buffer w may be overwritten once every block issued into it has been consumed
-    auto wait_s_free = [&](int w) -> bool {
-      int& rel = w ? released1 : released0;
-      const int iss = w ? issued1 : issued0;
-      while (rel < iss) {
-        if (!mbar_wait(&bar_pready[w], rel & 1, &give_up, 23)) return false;
-        ++rel;
-      }
-      return true;
-    };
-    auto issue_qk = [&](int w) -> bool {
-      if (!wait_s_free(w)) return false;
-      if (!mbar_wait(&bar_kfull[kc % kNK], (kc / kNK) & 1, &give_up, 22)) return false;
-      tc_fence_after();
-      const uint32_t k_lo = desc_lo(k_s, 16) + (kc % kNK) * (kStageBytes >> 4);
-      const uint32_t q_lo = desc_lo(q_s, 16);
-      const uint32_t d = t_s0 + w * 128;
-      if (el) {
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * (kStageBytes / 2 / 16) + (ks & 3) * 2;
-          if (POOL) mma_ss_lo(d, k_lo + off, q_lo + off, idesc_qk, ks > 0);     // S^T: lanes = keys
-          else mma_ss_lo(d, q_lo + off, k_lo + off, idesc_qk, ks > 0);          // S: lanes = (query, head) rows
-        }
-        mma_commit(&bar_kempty[kc % kNK]);
-        mma_commit(&bar_sfull[w]);
-      }
-      __syncwarp();
-      ++kc;
-      if (w) ++issued1; else ++issued0;
-      return true;
-    };
+    const uint32_t q_lo = desc_lo(q_s, 16), k_lo0 = desc_lo(k_s, 16);
     for (int k = 0; k < n_rounds && ok; ++k) {
       const int item = item_of(k);
       if (item >= n_items) continue;
@@ -462,14 +441,38 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       ok = mbar_wait(&sh.bar_q, qn & 1, &give_up, 21);
       if (!ok) break;
       ++qn;
-      ok = issue_qk(0);
-      if (ok && it.nb == 1 && el) mma_commit(&sh.bar_qempty);  // the tile's last Q.K^T is queued: Q may be replaced
+      int w = 0;
       for (int j = 0; j < it.nb && ok; ++j) {
-        if (j + 1 < it.nb) {
-          ok = issue_qk((j + 1) & 1);
-          if (!ok) break;
-          if (j + 2 == it.nb && el) mma_commit(&sh.bar_qempty);
+        // S buffer w may be overwritten once the block issued into it before has been consumed
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+          if (i == w && released[i] < issued[i]) {
+            ok = mbar_wait(&bar_pready[i], released[i] & 1, &give_up, 23);
+            ++released[i];
+          }
         }
+        if (!ok) break;
+        ok = mbar_wait(&bar_kfull[k_st], k_ph, &give_up, 22);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t k_lo = k_lo0 + k_st * (kStageBytes >> 4);
+        const uint32_t d = t_s0 + w * 128;
+        if (el) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t off = (ks >> 2) * (kStageBytes / 2 / 16) + (ks & 3) * 2;
+            if (POOL) mma_ss_lo(d, k_lo + off, q_lo + off, idesc_qk, ks > 0);     // S^T: lanes = keys
+            else mma_ss_lo(d, q_lo + off, k_lo + off, idesc_qk, ks > 0);          // S: lanes = (query, head) rows
+          }
+          mma_commit(&bar_kempty[k_st]);
+          mma_commit(&bar_sfull[w]);
+          if (j + 1 == it.nb) mma_commit(&sh.bar_qempty);    // the tile's last Q.K^T is queued: Q may be replaced
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < NS; ++i) if (i == w) ++issued[i];
+        if (++k_st == kNK) { k_st = 0; k_ph ^= 1; }
+        if (++w == NS) w = 0;
       }
     }
   };
@@ -806,15 +809,19 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   };
 
   // ================================ softmax statistics only (no V) ================================
-  // Two warpgroups, two independent streams: warpgroup w owns the key blocks j = w, w+2, ... of every
-  // tile with its own S buffer and its own running (max, sum) per row, so the tcgen05.ld / max / ex2
-  // phases of one stream overlap those of the other and nothing is exchanged per block.  The two
-  // partial results of a row are merged like split-K partials in the epilogue.
+  // Three warpgroups, three independent streams: warpgroup w owns the key blocks j = w, w+3, ... of
+  // every tile with its own S buffer and its own running (max, sum) per row, so the tcgen05.ld / max /
+  // ex2 phases of one stream overlap those of the others and nothing is exchanged per block (with two
+  // streams no unit was busy more than 64 %: three warps per SM sub-partition hide each other's
+  // latencies better).  The partial results of a row are merged like split-K partials in the epilogue.
   auto softmax_role = [&]() {
     const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane, q_local = row >> 2;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t ts = t_s0 + wg * 128 + lane_sel;   // this stream's S buffer
+    constexpr int NS = Cfg::kStreams;
+    float* const xm = xchg3;                           // [NS][128] partial maxima
+    float* const xl = xchg3 + NS * 128;                // [NS][128] partial sums
     int done_mine = 0, tiles_done = 0;                 // blocks finished by this stream, tiles finished
     bool ok = true;
     for (int k = 0; k < n_rounds && ok; ++k) {
@@ -824,9 +831,9 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (it.nb == 0) continue;
       const int tok = it.tile_start + q_local;
       const int off = it.tile_start;                    // slot - off = key position inside the tile
-      const int n_mine = (it.nb - wg + 1) >> 1;
+      const int n_mine = it.nb > wg ? (it.nb - wg + NS - 1) / NS : 0;
       float m_run = -INFINITY, l_run = 0.f;             // m_run in the scaled (log2) domain
-      for (int j = wg, jj = 0; j < it.nb; j += 2, ++jj) {
+      for (int j = wg, jj = 0; j < it.nb; j += NS, ++jj) {
         ok = mbar_wait(&bar_sfull[wg], (done_mine + jj) & 1, &give_up, 31);
         if (!ok) break;
         tc_fence_after();
@@ -884,18 +891,23 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         ok = mbar_wait(&sh.bar_ofree, (tiles_done - 1) & 1, &give_up, 37);
         if (!ok) break;
       }
-      sh.xchg[0][wg][row] = m_run;
-      sh.xchg[1][wg][row] = l_run;
+      xm[wg * 128 + row] = m_run;
+      xl[wg * 128 + row] = l_run;
       mbar_arrive(&sh.bar_x);
       ok = mbar_wait(&sh.bar_x, tiles_done & 1, &give_up, 35);
       if (!ok) break;
-      const float m_o = sh.xchg[0][wg ^ 1][row], l_o = sh.xchg[1][wg ^ 1][row];
-      const float m_tot = fmaxf(m_run, m_o);
-      const float f_mine = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_tot);
-      const float f_other = (m_o == -INFINITY) ? 0.f : ex2(m_o - m_tot);
-      const float l_tot = l_run * f_mine + l_o * f_other;
-      if (wg == 0 && p.lse2 && tok < p.L)
+      if (wg == 0 && p.lse2 && tok < p.L) {
+        float m_tot = -INFINITY;
+#pragma unroll
+        for (int s2 = 0; s2 < NS; ++s2) m_tot = fmaxf(m_tot, xm[s2 * 128 + row]);
+        float l_tot = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < NS; ++s2) {
+          const float ms = xm[s2 * 128 + row];
+          if (ms != -INFINITY) l_tot += xl[s2 * 128 + row] * ex2(ms - m_tot);
+        }
         p.lse2[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)] = m_tot + log2f(l_tot);
+      }
       // the exchange buffer has been read
       mbar_arrive(&sh.bar_ofree);
       ++tiles_done;
@@ -903,7 +915,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   };
 
   // ================================ pooled-score reducer =========================================
-  // warpgroup w owns the key blocks j = w, w+2, ... of every tile; thread = key lane, sums over the
+  // warpgroup w owns the key blocks j = w, w+3, ... of every tile; thread = key lane, sums over the
   // tile's 128 (query, head) rows, i.e. over the 128 columns of S^T
   auto pool_role = [&]() {
     const int wg = warp >> 2;
@@ -917,11 +929,12 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (item >= n_items) continue;
       const TileItem it = decode_item<MODE>(p, item);
       if (it.nb == 0) continue;
-      const int n_mine = (it.nb - wg + 1) >> 1;
+      constexpr int NS = Cfg::kStreams;
+      const int n_mine = it.nb > wg ? (it.nb - wg + NS - 1) / NS : 0;
       // this warpgroup's copy of the tile's 128 lse2 values (row = 4 * query + head), double-buffered
       // by tile parity: a thread that runs ahead must not overwrite values that a slower thread of
       // the warpgroup still reads for the previous tile
-      float* lse_s = sh.lse[wg][tiles_seen & 1];
+      float* lse_s = xchg3 + (wg * 2 + (tiles_seen & 1)) * 128;
       {
         const int tok = it.tile_start + (key_lane >> 2);
         lse_s[key_lane] =
@@ -932,7 +945,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         ++tiles_seen;
       }
       float* prow = p.pooled + (((int64_t)it.b * p.G + it.g) * p.T + it.t) * p.pooled_stride;
-      for (int j = wg, jj = 0; j < it.nb; j += 2, ++jj) {
+      for (int j = wg, jj = 0; j < it.nb; j += NS, ++jj) {
         ok = mbar_wait(&bar_sfull[wg], (done_mine + jj) & 1, &give_up, 41);
         if (!ok) break;
         tc_fence_after();
@@ -967,9 +980,23 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   //   dense : 384 threads x 168 at launch; 256 x 200 + 128 x 96 = 63488 <= 64512; 2 x 200 + 96 <= 512
   // The instruction is warpgroup-wide: all four warps of a warpgroup execute the same one, and the role
   // code sits inside the branch that issued it.
-  if (warp < 8) {
+  if (!HAS_V) {
+    //   no V : 512 threads x 128 at launch; 384 x 152 + 128 x 56 = 65536; 3 x 152 + 56 = 512
+    if (warp < Cfg::kSoftmaxWarps) {
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 152;\n");
+      if (POOL) pool_role(); else softmax_role();
+    } else {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
+      if (warp == Cfg::kProducerWarp0) {
+        if (lane == 0) producer_tma();
+        __syncwarp();
+      } else if (warp == kMmaWarp) {
+        mma_role();
+      }
+    }
+  } else if (warp < 8) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 200;\n");
-    if (POOL) pool_role(); else if (HAS_V) softmax_role_v(); else softmax_role();
+    softmax_role_v();
   } else if (GATHER) {
     if (warp < 12) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
@@ -986,11 +1013,11 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       if (lane == 0) producer_tma();
       __syncwarp();
     } else if (warp == kMmaWarp) {
-      if (HAS_V) mma_qk_v(); else mma_role();
-    } else if (HAS_V && warp == kMmaWarp + 1) {
+      mma_qk_v();
+    } else if (warp == kMmaWarp + 1) {
       if (lane == 0) producer_tma_v();
       __syncwarp();
-    } else if (HAS_V && warp == kMmaWarp + 2) {
+    } else if (warp == kMmaWarp + 2) {
       mma_pv_v();
     }
   }
