@@ -409,8 +409,8 @@ def main():
         achieved = flops / (t_ms * 1e-3) / 1e12
         # dram__bytes_read + dram__bytes_write per launch from the ncu capture at 16 384 tokens
         # (profiles/tile_prefill_kernels_16k_ncu.md), scaled linearly in L: every operand grows linearly
-        ncu_mb_16k = {"prefill_dense_attn": 465.5, "prefill_dense_lse": 169.5, "prefill_pool_scores": 285.4,
-                      "prefill_sparse": 309.3}
+        ncu_mb_16k = {"prefill_dense_attn": 493.1, "prefill_dense_lse": 170.7, "prefill_pool_scores": 286.7,
+                      "prefill_sparse": 312.1}
         traffic = ncu_mb_16k.get(top)
         traffic = None if traffic is None else traffic * 1e6 * (L / 16384)
         roof = {"kernel": "tile_prefill_kernel<%s>" % top, "bound": "tensor", "achieved": achieved,
