@@ -522,7 +522,7 @@ def main():
                            "layers": wl.layers, "anchors": list(wl.anchors), "seq_len": wl.seq_len, "batch": wl.B,
                            "q_heads": wl.H, "kv_heads": wl.G, "head_dim": wl.D, "topk_pct": wl.pct, "tile": wl.tile,
                            "rolling": wl.rolling,
-                           "parallelism": f"kv-head shard x{world}" + ("" if world == 1 else (", outputs all-gathered by NCCL" if args.no_peer_store else ", outputs stored into the peers by the kernel epilogue")),
+                           "parallelism": f"kv-head shard x{world}" + ("" if world == 1 else (", outputs stored into the peers by the kernel epilogue (" + strat._peer.how + ")" if strat._peer_store and strat._peer is not None else ", outputs all-gathered by NCCL")),
                            "cache_policy": f"inputs larger than L2 ({wl.seq_len * (wl.H + 2 * wl.G) * wl.D * 2 / 1e6:.0f} MB "
                                            f"per layer, {wl.layers} distinct layers)"},
                 "algorithmic_tflop_per_step": wl.flops_stack() / 1e12,

@@ -227,7 +227,7 @@ class EfficientKascadeStrategy(Strategy):
         G = k.shape[2]
         dev = q.device
         T = -(-L // self.tile_size)
-        fan = self._next_fanout(B, L, H, D, dev) if self._peer_store else None
+        fan = self._next_fanout(B, L, H, D, dev) if self._peer_store else None      # None: not in use (or not available)
         out = torch.empty(B, L, H, D, dtype=torch.float16, device=dev) if fan is None else None
         if self.is_anchor(layer):
             kk = topk_budget(self.k, L, self.tile_size)
@@ -294,7 +294,15 @@ class EfficientKascadeStrategy(Strategy):
         shape = (B, L, H * world, D)
         if self._peer is None or tuple(self._peer.tensors[0].shape) != shape:
             from .peer import alloc_peer_buffers
-            self._peer = alloc_peer_buffers(shape, torch.float16, dev, copies=2)
+            try:
+                self._peer = alloc_peer_buffers(shape, torch.float16, dev, copies=2)
+            except RuntimeError as e:
+                # no peer mapping in this job (every rank gets here together): keep the sharded prefill
+                # running with the NCCL all-gather of the outputs
+                import warnings
+                warnings.warn(f"peer_store disabled, outputs are all-gathered with NCCL instead: {e}")
+                self._peer_store = False
+                return None
             self._peer_fans = [nat.out_fanout(self._peer.fanout_pointers(c, rank), H * world, rank * H)
                                for c in range(2)]
         self._peer_copy ^= 1
