@@ -18,19 +18,22 @@
 // handed out boustrophedon-wise), ring stages and barrier phases keep counting across tiles, so the
 // next tile's Q/K/V are already on their way while the current tile is being finished.
 //
-// Warp roles.  Warps 0-7: softmax / reducer, two warpgroups, warpgroup w owns every key block
-// j = w (mod 2) of a tile with its own S buffer and O accumulator (thread = tensor-memory lane = row).
-// Dense modes (384 threads): warp 8 lane 0 issues TMA box copies (4-D tiled tensor maps, 128-byte
-// swizzle, no multicast), warp 9 lane 0 issues the MMAs, warps 10-11 only complete the warpgroup.
-// Sparse mode (512 threads): warps 8-11 gather the selected K/V rows with cp.async (16-byte chunks,
-// 16 lanes per 256-byte row, written directly in the 128-byte-swizzled operand layout of umma.cuh),
-// warp 12 lane 0 issues the MMAs, warps 13-15 complete its warpgroup.  setmaxnreg moves registers from
-// the producer / MMA warpgroups to the softmax warpgroups.
+// Warp roles (whole warps run their role with uniform control flow; one elected lane issues MMAs).
+//   with V, dense (384 threads):  warps 0-7 two softmax warpgroups (key blocks j = w mod 2, thread =
+//     tensor-memory lane = row); warp 8 lane 0 TMA box copies of Q and the K ring, warp 10 lane 0 of the
+//     V ring (4-D tiled tensor maps, 128-byte swizzle, no multicast); warp 9 issues Q.K^T, warp 11 P.V.
+//   with V, sparse (512 threads): warps 8-10 gather the selected K rows and warps 11, 14, 15 the V rows
+//     with cp.async (16-byte chunks, 16 lanes per 256-byte row, written directly in the
+//     128-byte-swizzled operand layout of umma.cuh); warp 12 issues Q.K^T, warp 13 P.V.
+//   without V (512 threads):      warps 0-11 three softmax / reducer warpgroups (key blocks j = w mod 3);
+//     warp 12 lane 0 TMA copies, warp 13 issues Q.K^T.
+// setmaxnreg moves registers from the producer / MMA warpgroups to the softmax warpgroups.
 // Hand-offs are mbarriers; every wait is bounded (umma::mbar_wait) and a kernel that gives up
 // records a code in the device status word, drains its copies, frees its tensor memory and returns.
 //
-// Tensor memory (512 columns): S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512).  P (fp16)
-// overwrites the first 64 columns of the S buffer it was computed from and is the A operand of P.V.
+// Tensor memory (512 columns).  With V: S0 [0,128), S1 [128,256), P0 [256,320), P1 [320,384) (fp16 pairs,
+// the A operand of P.V), O [384,512) - one accumulator for both streams, see the softmax role.
+// Without V: S0, S1, S2.
 #include <cuda.h>
 #include <stdlib.h>
 
@@ -43,7 +46,6 @@ namespace kb200 {
 
 enum PrefillMode { kDenseAttn = 0, kDenseLse = 1, kSparse = 2, kPool = 3 };
 
-constexpr int kSoftmaxThreads = 256;          // warps 0-7
 constexpr int kStageBytes = 128 * kD * 2;     // one 128-row operand tile (32 KB)
 constexpr int kNKMax = 6;                     // K ring: 3 stages with a V ring, 6 without
 constexpr int kNV = 3;
