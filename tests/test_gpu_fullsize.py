@@ -69,20 +69,22 @@ def _band_ok(ref_scores, chosen, k):
 # ---------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("name,L,qk_norm,rolling", [("prefill_32k", 32768, False, True),
                                                     ("prefill_131k_qknorm", 131072, True, True),
-                                                    ("prefill_32k_fixed_budget", 32768, False, False)])
+                                                    ("prefill_32k_fixed_budget", 32768, False, False),
+                                                    ("prefill_33333_ragged", 33333, False, True)])
 def test_prefill_anchor_layer_full_size(name, L, qk_norm, rolling):
     from kascade_b200 import _native as nat
     dev = torch.device("cuda")
     pct = 10.0
     scale = D ** -0.5
-    T = L // TILE
+    T = -(-L // TILE)                                   # the last tile may be partial
+    stride = -(-L // 128) * 128
     q, k, v = _prefill_inputs(L, seed=3, qk_norm=qk_norm)
     out = torch.empty(1, L, H, D, dtype=torch.float16, device=dev)
     lse = torch.empty(1, L, H, dtype=torch.float32, device=dev)
     lse_only = torch.empty_like(lse)
     nat.prefill_dense(q, k, v, scale, out, lse)
     nat.prefill_dense(q, k, None, scale, None, lse_only)
-    pooled = torch.full((1, G, T, L), -1.0, dtype=torch.float32, device=dev)
+    pooled = torch.full((1, G, T, stride), -1.0, dtype=torch.float32, device=dev)
     nat.prefill_pool_scores(q, k, lse, scale, pooled)
     k_max = topk_budget(pct, L, TILE)
     n_valid = torch.empty(1, G, T, dtype=torch.int32, device=dev)
@@ -121,15 +123,16 @@ def test_prefill_anchor_layer_full_size(name, L, qk_norm, rolling):
 
     # ---- sampled tiles against fp32 torch ------------------------------------------------------------
     for g, t in [(0, 0), (1, 1), (2, 5), (3, T // 3), (5, T // 2 + 1), (6, T - 2), (7, T - 1)]:
-        s0, s1 = t * TILE, (t + 1) * TILE
-        qt = q[0, s0:s1, g * 4:(g + 1) * 4].float().reshape(TILE * 4, D)              # row = 4 * query + head
-        logits = (qt @ k[0, :s1, g].float().t()) * scale                              # [128, s1]
-        qpos = (torch.arange(TILE * 4, device=dev) // 4) + s0
+        s0, s1 = t * TILE, min((t + 1) * TILE, L)
+        nq = s1 - s0                                                                   # queries of this tile (32, fewer in a partial last tile)
+        qt = q[0, s0:s1, g * 4:(g + 1) * 4].float().reshape(nq * 4, D)                # row = 4 * query + head
+        logits = (qt @ k[0, :s1, g].float().t()) * scale                              # [4 nq, s1]
+        qpos = (torch.arange(nq * 4, device=dev) // 4) + s0
         causal = torch.arange(s1, device=dev)[None, :] <= qpos[:, None]
         logits = logits.masked_fill(~causal, float("-inf"))
         ref_lse = torch.logsumexp(logits, -1)
         p = torch.exp(logits - ref_lse[:, None])
-        ref_out = (p @ v[0, :s1, g].float()).view(TILE, 4, D)
+        ref_out = (p @ v[0, :s1, g].float()).view(nq, 4, D)
         assert_close(out[0, s0:s1, g * 4:(g + 1) * 4], ref_out, what=f"{name} dense tile {t} head {g}")
         got_lse = lse[0, s0:s1, g * 4:(g + 1) * 4].reshape(-1)
         assert (got_lse - ref_lse * LOG2E).abs().max().item() < 1e-3
@@ -147,7 +150,7 @@ def test_prefill_anchor_layer_full_size(name, L, qk_norm, rolling):
         allowed[idx[0, g, t, :n].long()] = True
         allowed[s0:] = True
         sl = logits.masked_fill(~allowed[None, :], float("-inf"))
-        ref_sparse = (torch.softmax(sl, -1) @ v[0, :s1, g].float()).view(TILE, 4, D)
+        ref_sparse = (torch.softmax(sl, -1) @ v[0, :s1, g].float()).view(nq, 4, D)
         assert_close(sparse[0, s0:s1, g * 4:(g + 1) * 4], ref_sparse, what=f"{name} sparse tile {t} head {g}")
 
 
