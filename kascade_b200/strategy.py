@@ -192,13 +192,18 @@ class EfficientKascadeStrategy(Strategy):
     def attention_forward(self, module, query, key, value, attention_mask, scaling, dropout=0.0, **kwargs):
         """query [B,H,Lq,D], key/value [B,G,Lk,D] -> (out [B,Lq,H,D], None).
 
-        Like the reference (strategies/EfficientKascadeStrategy.py:126-161) the mask is not read:
-        prompts are causal and unpadded, a decode step attends to the whole cache."""
+        The reference (strategies/EfficientKascadeStrategy.py:126-161) never reads the mask: prompts are
+        causal and unpadded, a decode step attends to the whole cache.  Here the mask is read for one
+        thing only, LEFT padding of a batch (leading key positions that no query may see): every
+        sequence then goes through the kernels on its own unpadded views, with its own index rows."""
         if query.dtype != torch.float16:
             raise nat.KascadeNativeError(f"efficient_kascade computes in fp16; got {query.dtype}")
         B, H, Lq, D = query.shape
         G, Lk = key.shape[1], key.shape[2]
         layer = int(module.layer_idx)
+        pads = self._left_padding(attention_mask, B, Lk) if self._shard is None else None
+        if pads is not None:
+            return self._forward_left_padded(pads, module, query, key, value, scaling), None
         if Lq == 1:
             kv = nat.kv_layout_contiguous(*self._cache_views(key, value))
             seq_lens = self._scratch("seq_lens_full", (B,), torch.int32, query.device)
@@ -214,6 +219,46 @@ class EfficientKascadeStrategy(Strategy):
             nat.prefill_dense(q, k, v, scaling, out, None)
             return out, None
         return self._prefill(layer, q, k, v, scaling), None
+
+    # -- left-padded batches ----------------------------------------------------------------------
+    def _left_padding(self, attention_mask, B: int, Lk: int):
+        """Per-sequence number of leading key positions that the mask hides from the last query row, or
+        None if there is no such padding.  HF hands the same mask tensor to every layer of a forward, so
+        the (synchronising) look at it happens once per forward."""
+        if attention_mask is None or attention_mask.dim() != 4 or attention_mask.shape[0] != B \
+                or attention_mask.shape[-1] != Lk:
+            return None
+        ref = getattr(self, "_pad_ref", None)
+        if ref is None or ref() is not attention_mask or self._pad_version != attention_mask._version:
+            import weakref
+            last = attention_mask[:, 0, -1, :]                                    # [B, Lk]
+            hidden = ~last if last.dtype == torch.bool else last != 0
+            lead = torch.cumprod(hidden.to(torch.int32), dim=-1).sum(-1)          # length of the hidden prefix
+            pads = [int(x) for x in lead.tolist()]
+            self._pad_ref, self._pad_version = weakref.ref(attention_mask), attention_mask._version
+            self._pads = pads if any(pads) else None
+        return self._pads
+
+    def _forward_left_padded(self, pads, module, query, key, value, scaling) -> torch.Tensor:
+        B, H, Lq, D = query.shape
+        Lk = key.shape[2]
+        if getattr(self, "_children", None) is None or len(self._children) != B:
+            self._children = [EfficientKascadeStrategy(self.recompute_layers, "", k=self.k, tile_size=self.tile_size,
+                                                       rolling_prefill=self.rolling_prefill,
+                                                       head_mapping=self._head_mapping, register=False)
+                              for _ in range(B)]
+        out = torch.zeros(B, Lq, H, D, dtype=torch.float16, device=query.device)
+        for b, (pad, child) in enumerate(zip(pads, self._children)):
+            if pad >= Lk:
+                continue                                                           # nothing to attend to
+            kb, vb = key[b:b + 1, :, pad:], value[b:b + 1, :, pad:]
+            if Lq == 1:
+                ob, _ = child.attention_forward(module, query[b:b + 1], kb, vb, None, scaling)
+                out[b:b + 1] = ob
+            else:                                                                  # prefill: queries pad.. are the prompt
+                ob, _ = child.attention_forward(module, query[b:b + 1, :, pad:], kb, vb, None, scaling)
+                out[b:b + 1, pad:] = ob
+        return out
 
     @staticmethod
     def _cache_views(key, value):
