@@ -41,3 +41,35 @@ def test_llama_prefill_and_decode_through_the_registry():
     assert bool(torch.isfinite(step.logits).all())
     rel = (step.logits.float() - step_ref.logits.float()).abs().max().item() / max(step_ref.logits.float().abs().max().item(), 1.0)
     assert rel < 0.25, f"decode logits far from dense attention: {rel}"
+
+
+def test_llama_left_padded_batch_through_the_registry():
+    """Two prompts of different length, left-padded by the tokenizer convention (attention_mask of 0 / 1 per
+    token): at k = 100 % the valid positions must reproduce dense attention with the same mask."""
+    pytest.importorskip("transformers")
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from kascade_b200 import EfficientKascadeStrategy, _native as nat
+    torch.manual_seed(1)
+    cfg = LlamaConfig(hidden_size=4096, intermediate_size=512, num_hidden_layers=2, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=128, vocab_size=320, max_position_embeddings=4096,
+                      attn_implementation="sdpa")
+    model = LlamaForCausalLM(cfg).to("cuda", torch.float16).eval()
+    # lengths that are multiples of the tile: only then does a 100 % budget (L - 32 keys) cover every tile's past
+    L, pads = 352, [0, 128]
+    ids = torch.randint(0, 320, (2, L), device="cuda")
+    am = torch.ones(2, L, dtype=torch.long, device="cuda")
+    for b, pad in enumerate(pads):
+        am[b, :pad] = 0
+    with torch.no_grad():
+        ref = model(ids, attention_mask=am).logits
+    strat = EfficientKascadeStrategy([0], "x/y", k=100, tile_size=32, rolling_prefill=False,
+                                     head_mapping=[list(range(8)), [3, 3, 0, 7, 1, 6, 2, 5]])
+    model.config._attn_implementation = strat.name
+    n0 = nat.launch_count
+    with torch.no_grad():
+        got = model(ids, attention_mask=am).logits
+    assert nat.launch_count > n0 and nat.read_status() == 0
+    for b, pad in enumerate(pads):
+        err = (got[b, pad:].float() - ref[b, pad:].float()).abs().max().item()
+        scale = ref[b, pad:].float().abs().max().item()
+        assert err < 2e-2 * max(scale, 1.0), f"sequence {b}: logits differ from dense attention by {err} (scale {scale})"
