@@ -403,6 +403,22 @@ class EfficientKascadeStrategy(Strategy):
         nat.decode_sparse_paged(q, kv, self._dec_idx, self._dec_count, kmax, head_map, scaling, out, None, ws, splits)
         return out
 
+    @staticmethod
+    def append_kv(key_new, value_new, key_cache, value_cache, block_table, start_pos, n_new=None, *, query=None,
+                  q_norm_weight=None, k_norm_weight=None, norm_eps: float = 1e-6, inv_freq=None,
+                  rope_scale: float = 1.0):
+        """Prefill -> decode hand-off: write the new tokens' K / V rows (key_new / value_new [B,T,G,D] views,
+        positions start_pos[b] + t) into the paged cache the decode kernels read, in one kernel; with
+        `inv_freq` (the model's rotary table) and / or the norm weights the rows (and `query` [B,T,H,D], returned
+        transformed) are normalised and rotated on the way, as the Hugging Face module would have done.
+        The reference has no counterpart (it receives rotated tensors and copies them per call,
+        strategies/EfficientKascadeStrategy.py:144-150)."""
+        kv = nat.kv_layout_paged(key_cache, value_cache, block_table)
+        q_out = torch.empty_like(query, memory_format=torch.contiguous_format) if query is not None else None
+        nat.kv_write(query, q_out, key_new, value_new, start_pos, n_new, kv, q_norm_weight, k_norm_weight, norm_eps,
+                     inv_freq, rope_scale)
+        return q_out
+
     def paged_decode_forward(self, layer_idx: int, query, key_cache, value_cache, block_table, seq_lens, scaling,
                              max_seq_len: Optional[int] = None) -> torch.Tensor:
         """Paged-attention backend entry: query [B,H,D] fp16, key/value cache

@@ -103,3 +103,43 @@ def test_kv_write_contiguous_cache_then_decode_reads_it():
     p = torch.softmax(torch.einsum("bhd,bhld->bhl", q.float(), kk) * D ** -0.5, -1)
     ref = torch.einsum("bhl,bhld->bhd", p, vv)
     assert (out.float() - ref).abs().max().item() < 2e-3
+
+
+def test_prefill_to_paged_decode_hand_off():
+    """The prompt's K / V rows are appended to a paged cache with `append_kv`, then a decode step appends its
+    own row and attends through the block table: same outputs as the same strategy fed the contiguous
+    Hugging Face cache."""
+    from kascade_b200 import EfficientKascadeStrategy, _native as nat
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(21)
+    B, H, G, L, page, layers = 2, 32, 8, 700, 16, 3
+    hm = [list(range(G)), [3, 3, 0, 7, 1, 6, 2, 5], list(range(G))]
+
+    def make():
+        return EfficientKascadeStrategy([0, 2], "x/y", k=10, tile_size=32, rolling_prefill=True, head_mapping=hm,
+                                        register=False)
+
+    class M:
+        num_key_value_groups = H // G
+
+    pps = -(-(L + 1) // page)
+    n_pages = B * pps + 3
+    bt = torch.randperm(n_pages, generator=g)[: B * pps].view(B, pps).to(torch.int32).to(dev)
+    paged, contig = make(), make()
+    zero = torch.zeros(B, dtype=torch.int32, device=dev)
+    full = torch.full((B,), L, dtype=torch.int32, device=dev)
+    for l in range(layers):
+        k = torch.randn(B, G, L + 1, D, generator=g).half().to(dev)                 # HF layout [B, G, L, D]
+        v = torch.randn(B, G, L + 1, D, generator=g).half().to(dev)
+        q = (torch.randn(B, H, 1, D, generator=g) / D ** 0.5).half().to(dev)
+        kc = torch.zeros(n_pages, page, G, D, dtype=torch.float16, device=dev)
+        vc = torch.zeros_like(kc)
+        # prompt rows, then the decode token's row (token-major views of the HF tensors, no copies)
+        paged.append_kv(k[:, :, :L].transpose(1, 2), v[:, :, :L].transpose(1, 2), kc, vc, bt, zero)
+        paged.append_kv(k[:, :, L:].transpose(1, 2), v[:, :, L:].transpose(1, 2), kc, vc, bt, full)
+        m = M()
+        m.layer_idx = l
+        want, _ = contig.attention_forward(m, q, k, v, None, D ** -0.5)             # [B, 1, H, D]
+        got = paged.paged_decode_forward(l, q[:, :, 0], kc, vc, bt, full + 1, D ** -0.5, L + 1)
+        assert torch.equal(got, want[:, 0]), f"layer {l}: paged decode differs from the contiguous cache"
+    assert nat.read_status() == 0
