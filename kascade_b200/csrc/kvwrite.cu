@@ -30,68 +30,93 @@ struct KvWriteParams {
   int B, T, H, G;
 };
 
-// One warp per (sequence, new token, head): lane l holds elements 2l, 2l+1 of the first half and
-// 2l, 2l+1 of the second half (the two elements a rotation pairs up sit in the same lane).
-__global__ void __launch_bounds__(256) kv_write_kernel(const KvWriteParams p) {
-  const int lane = threadIdx.x & 31;
-  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int heads = p.H + 2 * p.G;                                   // Q heads, K heads, V heads
-  const int64_t total = (int64_t)p.B * p.T * heads;
-  if (wid >= total) return;
-  const int h = (int)(wid % heads);
-  const int t = (int)((wid / heads) % p.T);
-  const int b = (int)(wid / ((int64_t)heads * p.T));
+// One CTA per (sequence, new token): the token's 64 (cos, sin) pairs are computed once and shared by all
+// its heads; a row of 128 values is handled by 8 lanes (lane c holds elements 8c..8c+7 and
+// 64+8c..64+8c+7: the two elements a rotation pairs up sit in the same lane, 16-byte loads and stores),
+// a warp takes four rows at a time.
+constexpr int kKvWriteThreads = 192;
+
+__global__ void __launch_bounds__(kKvWriteThreads) kv_write_kernel(const KvWriteParams p) {
+  __shared__ __align__(16) __half cos_s[kD / 2];
+  __shared__ __align__(16) __half sin_s[kD / 2];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b = blockIdx.x / p.T, t = blockIdx.x - b * p.T;
   const int n = p.n_new ? p.n_new[b] : p.T;
   if (t >= n) return;
   const int pos = p.start_pos[b] + t;
-  const int kind = h < p.H ? 0 : (h < p.H + p.G ? 1 : 2);            // 0 = Q, 1 = K, 2 = V
-  const int hh = kind == 0 ? h : (kind == 1 ? h - p.H : h - p.H - p.G);
-  if (kind == 0 && !p.q_in) return;
-  const __half* src = kind == 0 ? p.q_in + b * p.q_sb + t * p.q_st + hh * p.q_sh
-                    : kind == 1 ? p.k_new + b * p.k_sb + t * p.k_st + hh * p.k_sh
-                                : p.v_new + b * p.v_sb + t * p.v_st + hh * p.v_sh;
-  __half2 lo = reinterpret_cast<const __half2*>(src)[lane];          // elements 2l, 2l+1
-  __half2 hi = reinterpret_cast<const __half2*>(src + kD / 2)[lane];  // elements 64+2l, 64+2l+1
-  if (kind != 2) {
-    const __half* gain = kind == 0 ? p.q_gain : p.k_gain;
+  if (p.inv_freq && tid < kD / 2) {
+    float sn, cs;
+    sincosf((float)pos * p.inv_freq[tid], &sn, &cs);
+    cos_s[tid] = __float2half_rn(cs * p.rope_scale);
+    sin_s[tid] = __float2half_rn(sn * p.rope_scale);
+  }
+  __syncthreads();
+  const int heads = p.H + 2 * p.G;                                   // Q heads, K heads, V heads
+  const int c = lane & 7;
+  for (int h0 = warp * 4; h0 < heads; h0 += (kKvWriteThreads / 32) * 4) {   // uniform per warp
+    const int h = min(h0 + (lane >> 3), heads - 1);
+    const bool active = h0 + (lane >> 3) < heads;                    // the last group of rows may be partial
+    const int kind = h < p.H ? 0 : (h < p.H + p.G ? 1 : 2);          // 0 = Q, 1 = K, 2 = V
+    const int hh = kind == 0 ? h : (kind == 1 ? h - p.H : h - p.H - p.G);
+    const __half* src = kind == 0 ? p.q_in + b * p.q_sb + t * p.q_st + hh * p.q_sh
+                      : kind == 1 ? p.k_new + b * p.k_sb + t * p.k_st + hh * p.k_sh
+                                  : p.v_new + b * p.v_sb + t * p.v_st + hh * p.v_sh;
+    uint4 lo4 = reinterpret_cast<const uint4*>(src)[c];              // elements 8c .. 8c+7
+    uint4 hi4 = reinterpret_cast<const uint4*>(src + kD / 2)[c];     // elements 64+8c .. 64+8c+7
+    __half2* lo = reinterpret_cast<__half2*>(&lo4);
+    __half2* hi = reinterpret_cast<__half2*>(&hi4);
+    const __half* gain = kind == 0 ? p.q_gain : (kind == 1 ? p.k_gain : nullptr);
+    // sum of squares of the row: all lanes of the warp take part in the shuffles, whatever their row is
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __half22float2(lo[e]), d2 = __half22float2(hi[e]);
+      ss += a.x * a.x + a.y * a.y + d2.x * d2.x + d2.y * d2.y;
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
     if (gain) {
       // x.float() * rsqrt(mean(x^2) + eps), rounded to fp16, times the gain (fp16 product)
-      const float2 a = __half22float2(lo), c = __half22float2(hi);
-      float ss = a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
       const float r = rsqrtf(ss / kD + p.eps);
-      const __half2 g_lo = reinterpret_cast<const __half2*>(gain)[lane];
-      const __half2 g_hi = reinterpret_cast<const __half2*>(gain + kD / 2)[lane];
-      lo = __hmul2_rn(g_lo, __floats2half2_rn(a.x * r, a.y * r));
-      hi = __hmul2_rn(g_hi, __floats2half2_rn(c.x * r, c.y * r));
+      const uint4 g_lo4 = reinterpret_cast<const uint4*>(gain)[c];
+      const uint4 g_hi4 = reinterpret_cast<const uint4*>(gain + kD / 2)[c];
+      const __half2* g_lo = reinterpret_cast<const __half2*>(&g_lo4);
+      const __half2* g_hi = reinterpret_cast<const __half2*>(&g_hi4);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __half22float2(lo[e]), d2 = __half22float2(hi[e]);
+        lo[e] = __hmul2_rn(g_lo[e], __floats2half2_rn(a.x * r, a.y * r));
+        hi[e] = __hmul2_rn(g_hi[e], __floats2half2_rn(d2.x * r, d2.y * r));
+      }
     }
-    if (p.inv_freq) {
-      // angle_i = pos * inv_freq[i], i = 2l and 2l+1 (the same i serves element i and element i + D/2)
-      const float2 f = reinterpret_cast<const float2*>(p.inv_freq)[lane];
-      float s0, c0, s1, c1;
-      sincosf((float)pos * f.x, &s0, &c0);
-      sincosf((float)pos * f.y, &s1, &c1);
-      const __half2 cs = __floats2half2_rn(c0 * p.rope_scale, c1 * p.rope_scale);
-      const __half2 sn = __floats2half2_rn(s0 * p.rope_scale, s1 * p.rope_scale);
-      // first half:  x_lo * cos + (-x_hi) * sin ; second half:  x_hi * cos + x_lo * sin
-      // (the _rn forms are never contracted into a fused multiply-add, which would skip a rounding)
-      const __half2 new_lo = __hadd2_rn(__hmul2_rn(lo, cs), __hmul2_rn(__hneg2(hi), sn));
-      const __half2 new_hi = __hadd2_rn(__hmul2_rn(hi, cs), __hmul2_rn(lo, sn));
-      lo = new_lo;
-      hi = new_hi;
+    if (kind != 2 && p.inv_freq) {
+      const uint4 cs4 = reinterpret_cast<const uint4*>(cos_s)[c];
+      const uint4 sn4 = reinterpret_cast<const uint4*>(sin_s)[c];
+      const __half2* cs = reinterpret_cast<const __half2*>(&cs4);
+      const __half2* sn = reinterpret_cast<const __half2*>(&sn4);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        // first half:  x_lo * cos + (-x_hi) * sin ; second half:  x_hi * cos + x_lo * sin
+        // (the _rn forms are never contracted into a fused multiply-add, which would skip a rounding)
+        const __half2 new_lo = __hadd2_rn(__hmul2_rn(lo[e], cs[e]), __hmul2_rn(__hneg2(hi[e]), sn[e]));
+        const __half2 new_hi = __hadd2_rn(__hmul2_rn(hi[e], cs[e]), __hmul2_rn(lo[e], sn[e]));
+        lo[e] = new_lo;
+        hi[e] = new_hi;
+      }
+    }
+    __half* dst;
+    if (kind == 0) {
+      dst = p.q_out + (((int64_t)b * p.T + t) * p.H + hh) * kD;
+    } else {
+      const int page = pos >> p.page_shift, slot = pos & p.page_mask;
+      const int64_t phys = p.block_table ? (int64_t)p.block_table[(int64_t)b * p.bt_stride + page] : page;
+      dst = (kind == 1 ? p.k_cache : p.v_cache) + b * p.c_sb + phys * p.c_sp + slot * p.c_st + hh * p.c_sh;
+    }
+    if (active) {
+      reinterpret_cast<uint4*>(dst)[c] = lo4;
+      reinterpret_cast<uint4*>(dst + kD / 2)[c] = hi4;
     }
   }
-  __half* dst;
-  if (kind == 0) {
-    dst = p.q_out + (((int64_t)b * p.T + t) * p.H + hh) * kD;
-  } else {
-    const int page = pos >> p.page_shift, slot = pos & p.page_mask;
-    const int64_t phys = p.block_table ? (int64_t)p.block_table[(int64_t)b * p.bt_stride + page] : page;
-    dst = (kind == 1 ? p.k_cache : p.v_cache) + b * p.c_sb + phys * p.c_sp + slot * p.c_st + hh * p.c_sh;
-  }
-  reinterpret_cast<__half2*>(dst)[lane] = lo;
-  reinterpret_cast<__half2*>(dst + kD / 2)[lane] = hi;
 }
 
 }  // namespace kb200
@@ -112,14 +137,14 @@ extern "C" int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const k
   const bool with_q = q_in && q_in->ptr;
   KB_REQUIRE(!with_q || q_out, "kv_write: q_in given without q_out");
   auto aligned = [](const void* ptr, int64_t a, int64_t b2, int64_t c) {
-    return (reinterpret_cast<uintptr_t>(ptr) & 3) == 0 && a % 2 == 0 && b2 % 2 == 0 && c % 2 == 0;
+    return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && a % 8 == 0 && b2 % 8 == 0 && c % 8 == 0;
   };
   KB_REQUIRE(aligned(k_new->ptr, k_new->stride_b, k_new->stride_t, k_new->stride_h) &&
                  aligned(v_new->ptr, v_new->stride_b, v_new->stride_t, v_new->stride_h) &&
                  (!with_q || aligned(q_in->ptr, q_in->stride_b, q_in->stride_t, q_in->stride_h)) &&
                  aligned(kv->k, kv->stride_batch, kv->stride_page, kv->stride_token) &&
                  aligned(kv->v, kv->stride_head, 0, 0),
-             "kv_write: pointers must be 4-byte aligned and strides even");
+             "kv_write: pointers must be 16-byte aligned and strides multiples of 8 elements");
   if (batch == 0 || max_new == 0) return 0;
   KvWriteParams p{};
   if (with_q) {
@@ -148,10 +173,9 @@ extern "C" int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const k
   p.inv_freq = inv_freq;
   p.rope_scale = rope_scale;
   p.B = batch; p.T = max_new; p.H = with_q ? num_q_heads : 0; p.G = num_kv_heads;
-  const int64_t warps = (int64_t)batch * max_new * (p.H + 2 * p.G);
-  const int64_t blocks = (warps + 7) / 8;
-  KB_REQUIRE(blocks < (1ll << 31), "kv_write: too many rows for one launch");
-  kv_write_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+  const int64_t blocks = (int64_t)batch * max_new;                   // one CTA per (sequence, new token)
+  KB_REQUIRE(blocks < (1ll << 31), "kv_write: too many tokens for one launch");
+  kv_write_kernel<<<(unsigned)blocks, kKvWriteThreads, 0, (cudaStream_t)stream>>>(p);
   KB_CHECK_LAUNCH("kv_write_kernel");
   return 0;
 }
