@@ -141,6 +141,7 @@ def run_reference(args, rank):
     reference itself cannot travel to the GPU box) on all host threads, same metric and unit."""
     if rank != 0:
         return
+    torch.set_num_threads(max(os.cpu_count() or 1, 1))     # a launcher may have pinned OMP_NUM_THREADS to 1
     cores = torch.get_num_threads()
     L = 2048
     for _ in range(args.warmup):
