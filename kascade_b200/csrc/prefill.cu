@@ -962,10 +962,12 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         for (int part = 0; part < 4; ++part)
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            a0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -lse_s[part * 32 + i]));
-            a1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -lse_s[part * 32 + i + 1]));
-            a2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -lse_s[part * 32 + i + 2]));
-            a3 += ex2_fma(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -lse_s[part * 32 + i + 3]));
+            // the four rows' lse2 with one 16-byte shared-memory load (the same address for the whole warp)
+            const float4 l4 = reinterpret_cast<const float4*>(lse_s)[part * 8 + (i >> 2)];
+            a0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -l4.x));
+            a1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -l4.y));
+            a2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -l4.z));
+            a3 += ex2_fma(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -l4.w));
           }
         const int key = j * 128 + key_lane;
         if (key < it.tile_start) prow[key] = (a0 + a1) + (a2 + a3);
