@@ -265,6 +265,46 @@ def bench_decode(args, dev, world, peaks, batch=None, ragged=False, rank=0):
 
 
 # ------------------------------------------------------------------------------------------------
+def bench_kv_write(dev, peaks, seq_len=32768, H=32, G=8, D=128, page=16):
+    """KV-cache write path (RoPE of Q and K, paged append of K and V) for one layer of a prefill at seq_len
+    and for one decode append at batch 64; bytes = every operand read once and written once."""
+    from kascade_b200 import _native as nat
+    g = torch.Generator(device="cpu").manual_seed(7)
+    q = torch.randn(1, seq_len, H, D, generator=g).half().to(dev)
+    k = torch.randn(1, seq_len, G, D, generator=g).half().to(dev)
+    v = torch.randn(1, seq_len, G, D, generator=g).half().to(dev)
+    pps = seq_len // page
+    kc = torch.empty(pps + 4, page, G, D, dtype=torch.float16, device=dev)
+    vc = torch.empty_like(kc)
+    bt = torch.randperm(pps + 4, generator=g)[:pps].view(1, pps).to(torch.int32).to(dev)
+    qo = torch.empty_like(q)
+    inv = (1.0 / (500000.0 ** (torch.arange(0, D, 2).float() / D))).to(dev)
+    zero = torch.zeros(1, dtype=torch.int32, device=dev)
+    kv = nat.kv_layout_paged(kc, vc, bt)
+    fn = lambda i: nat.kv_write(q, qo, k, v, zero, None, kv, inv_freq=inv)
+    _time_cuda(fn, 3)
+    ms = _time_cuda(fn, 20)
+    byts = 2 * 2 * (q.numel() + k.numel() + v.numel())
+    gbs = byts / (ms * 1e-3) / 1e9
+    B2, ctx = 64, 32768
+    q1 = torch.randn(B2, 1, H, D, generator=g).half().to(dev)
+    k1 = torch.randn(B2, 1, G, D, generator=g).half().to(dev)
+    v1 = torch.randn(B2, 1, G, D, generator=g).half().to(dev)
+    q1o = torch.empty_like(q1)
+    kc2 = torch.empty(B2 * 4, page, G, D, dtype=torch.float16, device=dev)     # only the page being appended to
+    vc2 = torch.empty_like(kc2)
+    bt2 = (torch.arange(B2, dtype=torch.int32) * 4).view(B2, 1).repeat(1, ctx // page + 1).to(dev)
+    pos = torch.full((B2,), ctx, dtype=torch.int32, device=dev)
+    kv2 = nat.kv_layout_paged(kc2, vc2, bt2)
+    fn2 = lambda i: nat.kv_write(q1, q1o, k1, v1, pos, None, kv2, inv_freq=inv)
+    _time_cuda(fn2, 3)
+    us = _time_cuda(fn2, 50) * 1e3
+    return {"kernel": "kv_write_kernel", "workload": f"one layer, {seq_len} tokens, RoPE + paged append ({page}-token pages)",
+            "ms": ms, "bytes": byts, "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": gbs / peaks["hbm_gbs"], "bound": "hbm", "peak_source": peaks["source"],
+            "decode_append_us": us, "decode_append_workload": f"batch {B2}, one token each at context {ctx}"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -499,6 +539,7 @@ def main():
     torch.cuda.empty_cache()
 
     decode = None if args.skip_decode else bench_decode(args, dev, world, peaks)
+    kvw = bench_kv_write(dev, peaks) if (world == 1 and rank == 0 and not args.skip_decode) else None
     status |= nat.read_status()
 
     # ---------------- CPU baseline (rank 0, N = 1) --------------------------------------------------
@@ -539,6 +580,8 @@ def main():
             line["dense"] = dense
         if decode:
             line["decode"] = decode
+        if kvw:
+            line["kv_write"] = kvw
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
