@@ -323,6 +323,7 @@ def main():
     ap.add_argument("--no-peer-store", action="store_true",
                     help="N > 1: all-gather the per-head outputs with NCCL instead of storing them into the peers from the kernel")
     ap.add_argument("--decode-only", action="store_true", help="profiling aid: run only the decode configuration")
+    ap.add_argument("--kv-write-only", action="store_true", help="profiling aid: run only the KV-cache write path")
     ap.add_argument("--decode-batch", type=int, default=None, help="profiling aid: decode batch (default 64)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -343,6 +344,10 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     peaks = _peaks()
+    if args.kv_write_only:
+        if rank == 0:
+            print(json.dumps({"metric": "kv write only (profiling aid)", "kv_write": bench_kv_write(dev, peaks)}), flush=True)
+        return
     if args.decode_only:
         decode = bench_decode(args, dev, world, peaks, args.decode_batch)
         if rank == 0:
