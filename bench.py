@@ -114,52 +114,161 @@ def _time_cuda(fn, reps: int):
 
 
 # ------------------------------------------------------------------------------------------------
-# CPU baseline: the oracle port (oracle/kascade_oracle.py) on the host cores
+# CPU baseline: the reference's own PyTorch KascadeStrategy (staged by oracle/make_ref.py into the
+# git-ignored oracle/_ref/) on the host cores; the oracle port only where those files are absent
 # ------------------------------------------------------------------------------------------------
-def cpu_prefill_sample(seq_len: int, target_len: int = 32768, n_anchor: int = 4, n_reuse: int = 27):
-    """Times one anchor-0, one reuse and one anchor>0 layer of the oracle at `seq_len`, fp32, and
-    extrapolates the stack (1 + n_anchor + n_reuse layers) at `target_len` tokens by the L^2 work ratio."""
+class _RefModule:
+    training = False
+
+    def __init__(self, layer_idx, groups):
+        self.layer_idx = layer_idx
+        self.num_key_value_groups = groups
+
+
+def _reference_strategy(wl, block_size=512):
+    """The reference's unmodified KascadeStrategy for workload `wl` (kind "reference"), or the oracle port
+    (kind "port") when oracle/_ref is not staged.  Returns (kind, run) with run(layer, q, k, v, mask) -> out."""
+    import tempfile
+    import numpy as np
+    from oracle import make_ref
+    scaling = wl.D ** -0.5
+    if make_ref.available():
+        KS = make_ref.load_reference_strategy()
+        with tempfile.TemporaryDirectory() as wd:           # the class reads ./results/head_mappings/<model>_layers_<..>.npy
+            os.makedirs(os.path.join(wd, "results", "head_mappings"))
+            np.save(os.path.join(wd, "results", "head_mappings",
+                                 f"bench_layers_{'_'.join(map(str, wl.anchors))}.npy"),
+                    np.asarray(wl.head_mapping(), dtype=np.int32))
+            cwd = os.getcwd()
+            os.chdir(wd)
+            try:
+                strat = KS(recompute_layers=list(wl.anchors), model_name="x/bench", k=wl.pct, tile_size=wl.tile,
+                           rolling_prefill=wl.rolling, block_size=block_size)
+            finally:
+                os.chdir(cwd)
+        groups = wl.H // wl.G
+        return "reference", lambda layer, q, k, v, mask: strat.attention_forward(_RefModule(layer, groups), q, k, v,
+                                                                                  mask, scaling)[0]
     from oracle.kascade_oracle import KascadeOracle
-    from kascade_b200.workloads import PrefillWorkload
+    orc = KascadeOracle(recompute_layers=wl.anchors, head_mapping=wl.head_mapping(), k=wl.pct, tile_size=wl.tile,
+                        rolling_prefill=wl.rolling, row_block=block_size)
+    return "port", lambda layer, q, k, v, mask: orc.attention_forward(layer, q, k, v, scaling)
+
+
+def cpu_prefill_sample(seq_len: int, target_len: int = 32768, n_anchor: int = 4, n_reuse: int = 27):
+    """Times one layer of each kind (layer 0, reuse, anchor > 0) of the reference's CPU strategy at `seq_len`
+    tokens, fp32, and extrapolates the stack (1 + n_anchor + n_reuse layers) at `target_len` tokens by the L^2
+    work ratio.  Returns (stack_ms, [t_layer0, t_reuse, t_anchor] in seconds, kind)."""
+    from bench_workloads import PrefillWorkload
     wl = PrefillWorkload(seq_len=seq_len, layers=3, anchors=(0, 2))
-    orc = KascadeOracle(recompute_layers=(0, 2), head_mapping=wl.head_mapping(), k=10, tile_size=32,
-                        rolling_prefill=True, row_block=512)
+    kind, run = _reference_strategy(wl)
+    fmin = torch.finfo(torch.float32).min
+    mask = torch.full((seq_len, seq_len), fmin).triu_(1)[None, None]
     times = []
-    for layer in range(3):
-        q, k, v = wl.layer_inputs(layer, "cpu")
-        q, k, v = (x.float().transpose(1, 2).contiguous() for x in (q, k, v))
-        t0 = time.perf_counter()
-        orc.attention_forward(layer, q, k, v, 128 ** -0.5)
-        times.append(time.perf_counter() - t0)
+    with torch.no_grad():
+        for layer in range(3):
+            q, k, v = wl.layer_inputs(layer, "cpu")
+            q, k, v = (x.float().transpose(1, 2).contiguous() for x in (q, k, v))
+            t0 = time.perf_counter()
+            run(layer, q, k, v, mask)
+            times.append(time.perf_counter() - t0)
     scale = (target_len / seq_len) ** 2
     stack_ms = (times[0] + n_anchor * times[2] + n_reuse * times[1]) * scale * 1e3
-    return stack_ms, times
+    return stack_ms, times, kind
+
+
+def prefill_config(wl, world=1, parallelism=None):
+    """The `config` object of the JSON line; the reference arm prints the same keys for the same workload."""
+    name = ("llama31_8b_prefill_attention_stack_32k" if wl.seq_len == 32768 and not wl.qk_norm else
+            f"qwen3_8b_prefill_attention_stack_{wl.seq_len}_qknorm" if wl.qk_norm else
+            f"llama31_8b_prefill_attention_stack_{wl.seq_len}")
+    return {"workload": name, "layers": wl.layers, "anchors": list(wl.anchors), "seq_len": wl.seq_len, "batch": wl.B,
+            "q_heads": wl.H, "kv_heads": wl.G, "head_dim": wl.D, "topk_pct": wl.pct, "tile": wl.tile,
+            "rolling": wl.rolling, "parallelism": parallelism or f"kv-head shard x{world}",
+            "cache_policy": f"inputs larger than L2 ({wl.seq_len * (wl.H + 2 * wl.G) * wl.D * 2 / 1e6:.0f} MB "
+                            f"per layer, {wl.layers} distinct layers)"}
 
 
 def run_reference(args, rank):
-    """--impl reference: the reference's CPU implementation of the path (the oracle port — the Python
-    reference itself cannot travel to the GPU box) on all host threads, same metric and unit."""
+    """--impl reference: the reference's CPU implementation of the path — its own PyTorch KascadeStrategy,
+    unmodified, from oracle/_ref — on all host threads, same metric, unit and config as the GPU arm.  A step is
+    a bounded sample: one layer of each kind at a sample length chosen so that the whole run stays within a few
+    minutes; `value` is the 32-layer stack at 32 768 tokens extrapolated from it by the L^2 work ratio."""
     if rank != 0:
         return
+    from bench_workloads import PrefillWorkload
     torch.set_num_threads(max(os.cpu_count() or 1, 1))     # a launcher may have pinned OMP_NUM_THREADS to 1
     cores = torch.get_num_threads()
-    L = 2048
+    wl = PrefillWorkload()
+    budget_s = 150.0
+    n_runs = max(args.steps, 1) + max(args.warmup, 0)
+    L = 1024
+    _, probe_times, kind = cpu_prefill_sample(L)
+    t_probe = sum(probe_times) * 1.25                       # + input generation and the mask
+    while L < 8192 and t_probe * 4.4 * n_runs <= budget_s:  # the work grows ~4x per doubling of L
+        L *= 2
+        t_probe *= 4.4
     for _ in range(args.warmup):
         cpu_prefill_sample(L)
     t0 = time.perf_counter()
-    vals = [cpu_prefill_sample(L)[0] for _ in range(args.steps)]
+    samples = [cpu_prefill_sample(L) for _ in range(max(args.steps, 1))]
     wall = (time.perf_counter() - t0) / max(args.steps, 1)
-    value = sum(vals) / len(vals)
-    sample = (f"oracle port, fp32, {cores} threads: 3 layers (anchor 0, reuse, anchor>0) at L={L}, stack of 32 layers "
-              f"at 32768 extrapolated by (32768/{L})^2 and 1/27/4 layer weights")
+    value = sum(s[0] for s in samples) / len(samples)
+    tl = [sum(s[1][i] for s in samples) / len(samples) for i in range(3)]
+    what = ("the reference's own KascadeStrategy (unmodified, oracle/_ref)" if kind == "reference"
+            else "oracle port (oracle/_ref not staged)")
+    sample = (f"{what}, fp32, {cores} threads, block_size 512: measured at L={L} layer 0 {tl[0]:.2f}s, reuse {tl[1]:.2f}s, "
+              f"anchor>0 {tl[2]:.2f}s per layer; value = 32-layer stack at 32768 tokens extrapolated by (32768/{L})^2 "
+              f"with 1/27/4 layer weights")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "ms", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall * 1e3, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "llama31_8b_prefill_attention_stack_32k", "layers": 32, "seq_len": 32768,
-                       "topk_pct": 10, "tile": 32, "rolling": True},
-            "cpu_baseline": {"value": value, "unit": "ms", "cores": cores, "kind": "port", "sample": sample},
+            "config": prefill_config(wl, max(args.gpus, 1)),
+            "measured": {"seq_len": L, "layer0_s": tl[0], "reuse_s": tl[1], "anchor_s": tl[2],
+                         "extrapolation": f"(32768/{L})^2, 1 layer-0 + 27 reuse + 4 anchor layers"},
+            "cpu_baseline": {"value": value, "unit": "ms", "cores": cores, "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def sharded_self_check(rank, world, dev, exchange, seq_len=2048):
+    """N > 1: every rank runs three layers (layer 0, a reuse layer, an anchor > 0) of a short prompt both through
+    the head-sharded strategy with the benchmark's exchange mode and through an unsharded strategy over all heads
+    on its own GPU, and compares the gathered [B, L, H, D] outputs of every layer bit for bit.  Returns "ok" or a
+    description of the first difference (the same string on all ranks)."""
+    import torch.distributed as dist
+    from bench_workloads import PrefillWorkload
+    from kascade_b200 import EfficientKascadeStrategy
+    wl = PrefillWorkload(seq_len=seq_len, layers=3, anchors=(0, 2))
+    gpr = wl.G // world
+    heads = list(range(rank * gpr, (rank + 1) * gpr))
+    kw = dict(k=wl.pct, tile_size=wl.tile, rolling_prefill=wl.rolling, head_mapping=wl.head_mapping(), register=False)
+    full = EfficientKascadeStrategy(list(wl.anchors), "x/check", **kw)
+    part = EfficientKascadeStrategy(list(wl.anchors), "x/check", shard=(rank, world), exchange=exchange, **kw)
+    worst, where = 0.0, None
+    for layer in range(wl.layers):
+        q, k, v = wl.layer_inputs(layer, dev)
+        ref, _ = full.attention_forward(_Module(layer), q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), None,
+                                        wl.D ** -0.5)
+        hg = wl.H // wl.G
+        qh = [g * hg + i for g in heads for i in range(hg)]
+        part.attention_forward(_Module(layer), q[:, :, qh].contiguous().transpose(1, 2),
+                               k[:, :, heads].contiguous().transpose(1, 2), v[:, :, heads].contiguous().transpose(1, 2),
+                               None, wl.D ** -0.5)
+        part.wait_gathers()
+        torch.cuda.synchronize()
+        got = part.gathered_out
+        if got.dim() == 5:                                            # NCCL layout [world, B, L, H/world, D]
+            got = torch.cat([got[r] for r in range(world)], dim=2)
+        diff = (got.float() - ref.float()).abs().max().item()
+        if diff > worst:
+            worst, where = diff, layer
+        dist.barrier()                                                # nobody overwrites a buffer a peer still compares
+    t = torch.tensor([worst], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    del full, part
+    torch.cuda.empty_cache()
+    return "ok" if float(t.item()) == 0.0 else f"gathered outputs differ from the unsharded run by up to {float(t.item()):.3e}"
 
 
 def bench_decode(args, dev, world, peaks, batch=None, ragged=False, rank=0):
@@ -167,7 +276,7 @@ def bench_decode(args, dev, world, peaks, batch=None, ragged=False, rank=0):
     32 768, 16-token pages behind a seeded random block table, 32 layers with anchors {0,2,8,13,14}."""
     import torch.distributed as dist
     from kascade_b200 import EfficientKascadeStrategy, _native as nat
-    from kascade_b200.workloads import DecodeWorkload
+    from bench_workloads import DecodeWorkload
     scaling = 128 ** -0.5
     if ragged:                                                    # 256 sequences, contexts uniform in [4096, 65536]
         dw = DecodeWorkload.ragged(rank=rank, world=world, distinct_caches=2)
@@ -320,8 +429,14 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-dense", action="store_true")
-    ap.add_argument("--no-peer-store", action="store_true",
-                    help="N > 1: all-gather the per-head outputs with NCCL instead of storing them into the peers from the kernel")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "peer_store", "nccl"],
+                    help="N > 1: how the per-head outputs reach the other GPUs: copy-engine pushes on side streams "
+                         "(push), stores from the kernel epilogue (peer_store), NCCL all-gather (nccl); auto = "
+                         "peer_store on 2 GPUs, push from 4 on")
+    ap.add_argument("--no-peer-store", action="store_true", help="same as --exchange nccl")
+    ap.add_argument("--wait-every-layer", action="store_true",
+                    help="N > 1: synchronise the GPUs after every layer (what a consumer of each layer's gathered "
+                         "outputs needs) instead of once per step")
     ap.add_argument("--decode-only", action="store_true", help="profiling aid: run only the decode configuration")
     ap.add_argument("--kv-write-only", action="store_true", help="profiling aid: run only the KV-cache write path")
     ap.add_argument("--decode-batch", type=int, default=None, help="profiling aid: decode batch (default 64)")
@@ -337,7 +452,7 @@ def main():
 
     import torch.distributed as dist
     from kascade_b200 import EfficientKascadeStrategy, _native as nat
-    from kascade_b200.workloads import DecodeWorkload, PrefillWorkload
+    from bench_workloads import DecodeWorkload, PrefillWorkload
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -371,7 +486,7 @@ def main():
 
     # ---------------- prefill stack (headline) -----------------------------------------------------
     if args.config == 4:
-        from kascade_b200.workloads import QWEN3_ANCHORS
+        from bench_workloads import QWEN3_ANCHORS
         wl = PrefillWorkload(seq_len=131072 if args.seq_len == 32768 else args.seq_len, layers=36,
                              anchors=QWEN3_ANCHORS, qk_norm=True)
         args.skip_decode = True
@@ -380,10 +495,13 @@ def main():
     assert wl.G % world == 0, "KV heads must divide over the ranks"
     gpr = wl.G // world
     my_heads = list(range(rank * gpr, (rank + 1) * gpr))
+    exchange = "nccl" if args.no_peer_store else args.exchange
+    if exchange == "auto":
+        exchange = "peer_store" if world == 2 else "push"
+    sharded_check = sharded_self_check(rank, world, dev, exchange) if world > 1 else None
     strat = EfficientKascadeStrategy(list(wl.anchors), "synthetic/llama31-8b-shape", k=wl.pct, tile_size=wl.tile,
                                      rolling_prefill=wl.rolling, head_mapping=wl.head_mapping(), register=False,
-                                     shard=(rank, world) if world > 1 else None,
-                                     peer_store=world > 1 and not args.no_peer_store)
+                                     shard=(rank, world) if world > 1 else None, exchange=exchange)
     inputs = [wl.layer_inputs(l, dev, my_heads if world > 1 else None) for l in range(wl.layers)]
     scaling = wl.D ** -0.5
     mods = [_Module(l) for l in range(wl.layers)]
@@ -394,6 +512,8 @@ def main():
         for l in range(wl.layers):
             q, k, v = inputs[l]
             out, _ = strat.attention_forward(mods[l], q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), None, scaling)
+            if world > 1 and args.wait_every_layer:
+                strat.wait_gathers()
         if world > 1:
             strat.wait_gathers()
         result["out"] = out
@@ -553,25 +673,23 @@ def main():
         L = 4096
         n_anchor = len([a for a in wl.anchors if a != 0])
         n_reuse = wl.layers - n_anchor - 1
-        stack_ms, times = cpu_prefill_sample(L, wl.seq_len, n_anchor, n_reuse)
-        cpu = {"value": stack_ms, "unit": "ms", "cores": torch.get_num_threads(), "kind": "port",
-               "sample": (f"oracle port fp32: anchor-0 {times[0]:.1f}s, reuse {times[1]:.1f}s, anchor>0 {times[2]:.1f}s at "
-                          f"L={L}; {wl.layers}-layer stack at {wl.seq_len} extrapolated by ({wl.seq_len}/{L})^2 with "
-                          f"1/{n_reuse}/{n_anchor} layer weights")}
+        stack_ms, times, kind = cpu_prefill_sample(L, wl.seq_len, n_anchor, n_reuse)
+        what = ("the reference's own KascadeStrategy (unmodified, oracle/_ref)" if kind == "reference"
+                else "oracle port (oracle/_ref not staged)")
+        cpu = {"value": stack_ms, "unit": "ms", "cores": torch.get_num_threads(), "kind": kind,
+               "sample": (f"{what}, fp32, block_size 512: layer 0 {times[0]:.1f}s, reuse {times[1]:.1f}s, anchor>0 "
+                          f"{times[2]:.1f}s measured at L={L}; {wl.layers}-layer stack at {wl.seq_len} extrapolated by "
+                          f"({wl.seq_len}/{L})^2 with 1/{n_reuse}/{n_anchor} layer weights")}
 
     if rank == 0:
         line = {"metric": METRIC, "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": {"workload": (f"qwen3_8b_prefill_attention_stack_{wl.seq_len}_qknorm" if args.config == 4 else
-                                        "llama31_8b_prefill_attention_stack_32k" if wl.seq_len == 32768
-                                        else f"llama31_8b_prefill_attention_stack_{wl.seq_len}"),
-                           "layers": wl.layers, "anchors": list(wl.anchors), "seq_len": wl.seq_len, "batch": wl.B,
-                           "q_heads": wl.H, "kv_heads": wl.G, "head_dim": wl.D, "topk_pct": wl.pct, "tile": wl.tile,
-                           "rolling": wl.rolling,
-                           "parallelism": f"kv-head shard x{world}" + ("" if world == 1 else (", outputs stored into the peers by the kernel epilogue (" + strat._peer.how + ")" if strat._peer_store and strat._peer is not None else ", outputs all-gathered by NCCL")),
-                           "cache_policy": f"inputs larger than L2 ({wl.seq_len * (wl.H + 2 * wl.G) * wl.D * 2 / 1e6:.0f} MB "
-                                           f"per layer, {wl.layers} distinct layers)"},
+                "config": prefill_config(wl, world),
+                "exchange": (None if world == 1 else strat.exchange_description()),
+                "gpu_sync": (None if world == 1 else "after every layer" if args.wait_every_layer else
+                             "once per step (the layers' outputs are not consumed in between)"),
+                "sharded_check": sharded_check,
                 "algorithmic_tflop_per_step": wl.flops_stack() / 1e12,
                 "achieved_tflops": wl.flops_stack() / (ms_step * 1e-3) / 1e12,
                 "gpu_launches": launches, "device_status": status, "clocks": clocks}

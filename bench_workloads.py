@@ -71,7 +71,7 @@ class PrefillWorkload:
         return 2 * self.flops_qk_causal()
 
     def sparse_keys_per_tile(self) -> List[int]:
-        from .strategy import topk_budget
+        from kascade_b200.strategy import topk_budget
         kk = topk_budget(self.pct, self.seq_len, self.tile)
         out = []
         for t in range(-(-self.seq_len // self.tile)):
@@ -154,12 +154,12 @@ class DecodeWorkload:
         return (torch.randn(self.batch, self.H, self.D, generator=gen, device=device) / self.D ** 0.5).half()
 
     def budget(self) -> int:
-        from .strategy import topk_budget
+        from kascade_b200.strategy import topk_budget
         return topk_budget(self.pct, self.context, 32)
 
     # ---- algorithmic bytes per layer kind ---------------------------------------------------------
     def bytes_reuse(self) -> float:
-        from .strategy import topk_budget
+        from kascade_b200.strategy import topk_budget
         keys = sum(topk_budget(self.pct, n, 32) for n in self.seq_lens())
         return self.G * keys * (2 * self.D * 2 + 4) + 2 * self.batch * self.H * self.D * 2
 

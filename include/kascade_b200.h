@@ -54,6 +54,11 @@ int kb200_abi_version(void);
  * reference (its kernels spin without a limit). */
 int kb200_read_status(int* host_out);
 
+/* Number of tensor-map descriptors the prefill entry points have encoded so far in this process.  The
+ * descriptors are kept per (pointer, strides, extents), so a loop over the same buffers stops encoding after
+ * its first pass; the counter lets a host check that.  No counterpart in the reference. */
+long long kb200_tensor_map_encodes(void);
+
 /* ---- Top-k selection (replaces the torch.topk call sites,
  *      strategies/EfficientKascadeStrategy.py:82,90,111) ---------------------------------------- */
 
@@ -128,8 +133,9 @@ int kb200_decode_sparse_paged(const void* q, int64_t q_stride_b, int64_t q_strid
  *    by every GPU that loads the library until the process exits).  With num_splits = 0 the library
  *    lowers its own choice until it fits; an explicit num_splits that does not fit is rejected with
  *    a message, nothing is launched.  num_splits = 1 needs no scratch and always fits.
- *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress) with that
- *    device current, and caches it; make that first call during set-up, before any stream capture.
+ *  - The first call on a device that uses more than one split looks up the array's device address
+ *    (cudaGetSymbolAddress) with that device current, and caches it; make that first call during set-up,
+ *    before any stream capture.
  *    The device that is current at the call must be the one that owns the pointers.
  *  - All calls on a device share the one array.  Nothing in it has to start at zero — every slot the
  *    merge step reads is written earlier in the same call — but two calls that overlap on the GPU
@@ -137,6 +143,9 @@ int kb200_decode_sparse_paged(const void* q, int64_t q_stride_b, int64_t q_strid
  *    with a workspace.
  * Arguments as kb200_decode_sparse_paged, without workspace / workspace_bytes. */
 #define KB200_NOALLOC_MAX_SLOTS 8192
+/* Splits kb200_decode_sparse_paged_noalloc uses for this problem and this num_splits argument
+ * (0 = the call would be rejected); with 1 split the call launches one kernel, otherwise two. */
+int kb200_decode_noalloc_splits(int batch, int num_q_heads, int num_kv_heads, int k_max, int num_splits);
 int kb200_decode_sparse_paged_noalloc(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                                       const kb200_kv_layout* kv, const int32_t* topk_idx,
                                       int64_t idx_stride_b, int64_t idx_stride_g,
@@ -237,6 +246,27 @@ int kb200_prefill_sparse_fanout(const kb200_act_layout* q, const kb200_act_layou
                                 const kb200_out_fanout* fan, float* lse2, int batch, int seq_len,
                                 int num_q_heads, int num_kv_heads, int idx_kv_heads, void* stream);
 
+/* Output exchange by the copy engines, for prompts whose KV heads are sharded over the GPUs of one node
+ * (alternative to kb200_out_fanout: from four GPUs on, the NVLink time of a reuse layer exceeds its compute
+ * time, and stores issued by the kernel hold it up).  The kernel writes its heads into this GPU's own
+ * [rows, pitch] buffer; kb200_peer_push then copies that slice (width_bytes at offset_bytes of every row) into
+ * the same place of every peer's buffer: one strided 2-D device-to-device copy per peer, each on the stream the
+ * plan names, ordered after everything queued on compute_stream so far (ready_event is recorded there) and
+ * followed by a record of done_event[i].  No SM is used; the next layer's kernels run meanwhile.  The caller
+ * owns streams and events (cudaStream_t / cudaEvent_t passed as void*), makes the compute stream wait for the
+ * done events before it overwrites the slice (kb200_stream_wait_events), and synchronises the GPUs before
+ * anyone reads a peer-written buffer.  The reference all-gathers nothing (single GPU). */
+typedef struct kb200_push_plan {
+  void* dst[KB200_MAX_FANOUT];        /* peers' buffers (mapped into this process), same shape as the source */
+  void* stream[KB200_MAX_FANOUT];     /* one copy stream per peer */
+  void* done_event[KB200_MAX_FANOUT]; /* recorded on stream[i] after the copy to peer i */
+  int32_t count;
+} kb200_push_plan;
+int kb200_peer_push(const kb200_push_plan* plan, const void* src_base, size_t offset_bytes, size_t pitch_bytes,
+                    size_t width_bytes, size_t rows, void* ready_event, void* compute_stream);
+/* Makes `stream` wait for `count` events (NULL entries are skipped).  Host-side helper of kb200_peer_push. */
+int kb200_stream_wait_events(void* stream, void* const* events, int count);
+
 /* Per-tile budgets of an anchor prefill layer, written on the device for kb200_topk_select:
  *   n_valid[b,g,t] = 32*t,
  *   k_row[b,g,t]   = rolling ? min(k_max, max(128, floor(pct * 32*t / 100))) : k_max
@@ -276,6 +306,15 @@ int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const kb200_act_la
  *   status [4] int32: 0 ok, non-zero = a bounded wait gave up.
  * No counterpart in the reference. */
 int kb200_selftest_umma(const void* a, const void* b, float* out, int32_t* status, void* stream);
+
+/* Exercises the give-up path of the bounded device-side waits without hanging anything: one CTA allocates
+ * tensor memory, then all its threads wait for at most limit_ns (0 < limit_ns <= 100 ms) on a barrier on
+ * which nobody arrives.  The wait runs out, the CTA frees its tensor memory, records `code` (1..255) in the
+ * device status word that kb200_read_status returns and clears, and returns.
+ *   result [3] int32: code the CTA ended with, threads whose wait returned "gave up", elapsed ns.
+ * While the status word is non-zero the tile prefill kernels return at entry; read it to clear it.
+ * No counterpart in the reference (its kernels spin without a limit). */
+int kb200_selftest_wait_timeout(int32_t* result, uint64_t limit_ns, int code, void* stream);
 
 #ifdef __cplusplus
 }

@@ -24,7 +24,7 @@ EXPORTS = [
     "kb200_decode_anchor_paged", "kb200_prefill_dense", "kb200_prefill_pool_scores",
     "kb200_prefill_sparse", "kb200_prefill_budgets", "kb200_selftest_umma", "kb200_read_status",
     "kb200_decode_sparse_paged_noalloc", "kb200_prefill_dense_fanout", "kb200_prefill_sparse_fanout",
-    "kb200_kv_write",
+    "kb200_kv_write", "kb200_peer_push", "kb200_stream_wait_events", "kb200_selftest_wait_timeout", "kb200_tensor_map_encodes", "kb200_decode_noalloc_splits",
 ]
 
 
@@ -62,6 +62,12 @@ def out_fanout(pointers, total_heads: int, head_offset: int) -> OutFanout:
         f.out[i] = int(ptr)
     f.count, f.total_heads, f.head_offset = len(pointers), int(total_heads), int(head_offset)
     return f
+
+
+class PushPlan(C.Structure):
+    """kb200_push_plan: peers' buffers with one copy stream and one completion event per peer."""
+    _fields_ = [("dst", C.c_void_p * MAX_FANOUT), ("stream", C.c_void_p * MAX_FANOUT),
+                ("done_event", C.c_void_p * MAX_FANOUT), ("count", C.c_int32)]
 
 
 _lib = None
@@ -111,6 +117,12 @@ def load() -> C.CDLL:
         lib.kb200_kv_write.argtypes = [AL, vp, AL, AL, vp, vp, C.POINTER(KvLayout), vp, vp, f32, vp, f32, i32, i32,
                                        i32, i32, vp]
         lib.kb200_selftest_umma.argtypes = [vp, vp, vp, vp, vp]
+        lib.kb200_peer_push.argtypes = [C.POINTER(PushPlan), vp, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, vp, vp]
+        lib.kb200_stream_wait_events.argtypes = [vp, C.POINTER(C.c_void_p), i32]
+        lib.kb200_selftest_wait_timeout.argtypes = [vp, C.c_uint64, i32, vp]
+        lib.kb200_tensor_map_encodes.restype = C.c_longlong
+        lib.kb200_tensor_map_encodes.argtypes = []
+        lib.kb200_decode_noalloc_splits.argtypes = [i32, i32, i32, i32, i32]
         _lib = lib
     return _lib
 
@@ -131,11 +143,45 @@ def init(device: Optional[int] = None) -> C.CDLL:
     return lib
 
 
-def read_status() -> int:
-    """Device status word (0 = every kernel ran to completion); synchronises the device."""
-    out = C.c_int(0)
-    _check(init().kb200_read_status(C.byref(out)), "kb200_read_status")
+def read_status(device=None) -> int:
+    """Status word of `device` (default: the current one); 0 = every kernel ran to completion.  Reading
+    clears it.  Synchronises the device."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    with torch.cuda.device(dev):
+        out = C.c_int(0)
+        _check(init(dev).kb200_read_status(C.byref(out)), "kb200_read_status")
     return out.value
+
+
+def check_status(device=None, where: str = ""):
+    """Raise if a kernel of this library gave up a bounded wait on `device` since the last check: its
+    outputs (and those of every later tile-prefill launch, which return at entry while the word is set) are
+    not valid.  Call it where the host synchronises anyway."""
+    st = read_status(device)
+    if st != 0:
+        raise KascadeNativeError(f"a kernel gave up a bounded device-side wait (code {st}){' ' + where if where else ''}; "
+                                 "outputs since the last status check are invalid")
+
+
+def _on_device_of(arg_index: int):
+    """Decorator: run the wrapped call with the GPU of its `arg_index`-th argument (a tensor) current.  The
+    library launches on the current device, on the current stream of that device, and keeps its per-device
+    state (kernel attributes, the built-in decode scratch) by it; without this a caller whose current device
+    differs from the tensors' would launch on the wrong GPU."""
+    def deco(fn):
+        import functools
+
+        @functools.wraps(fn)
+        def wrapped(*args, **kwargs):
+            t = args[arg_index]
+            if not t.is_cuda:
+                raise KascadeNativeError(f"{fn.__name__}: expected CUDA tensors, got one on {t.device}")
+            if t.device.index == torch.cuda.current_device():
+                return fn(*args, **kwargs)
+            with torch.cuda.device(t.device):
+                return fn(*args, **kwargs)
+        return wrapped
+    return deco
 
 
 def _stream() -> C.c_void_p:
@@ -146,12 +192,18 @@ def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
     return C.c_void_p(0 if t is None else t.data_ptr())
 
 
+def _want_opt(t: Optional[torch.Tensor], dtype, name: str):
+    if t is not None:
+        _want(t, dtype, name)
+
+
 def _want(t: torch.Tensor, dtype, name: str):
     if t.dtype != dtype or not t.is_cuda:
         raise KascadeNativeError(f"{name}: expected a CUDA {dtype} tensor, got {t.dtype} on {t.device}")
 
 
 # ------------------------------------------------------------------------------------------------
+@_on_device_of(0)
 def topk_select(scores: torch.Tensor, n_valid: Optional[torch.Tensor], k_row: Optional[torch.Tensor],
                 k_max: int, out_idx: torch.Tensor, out_count: Optional[torch.Tensor], n_cols: Optional[int] = None):
     """scores [..., row_stride] fp32 (last dim contiguous, rows equally spaced), out_idx [..., idx_stride]."""
@@ -166,6 +218,7 @@ def topk_select(scores: torch.Tensor, n_valid: Optional[torch.Tensor], k_row: Op
     _launched(1 if rows else 0)
 
 
+@_on_device_of(0)
 def prefill_budgets(n_valid, k_row, batch, groups, tiles, k_max, pct, rolling):
     lib = init(n_valid.device.index)
     _check(lib.kb200_prefill_budgets(_ptr(n_valid), _ptr(k_row), batch, groups, tiles, k_max, float(pct),
@@ -205,6 +258,7 @@ def decode_default_splits(batch: int, groups: int, max_keys: int) -> int:
     return load().kb200_decode_default_splits(batch, groups, max_keys)
 
 
+@_on_device_of(0)
 def decode_sparse_paged(q, kv: KvLayout, topk_idx, topk_count, k_max, head_map, scale, out, lse2=None,
                         workspace=None, num_splits=0):
     """q [B,H,D] fp16; topk_idx [B,G,kstride] int32; out [B,H,D] fp16 contiguous."""
@@ -212,6 +266,8 @@ def decode_sparse_paged(q, kv: KvLayout, topk_idx, topk_count, k_max, head_map, 
     _want(q, torch.float16, "q")
     _want(out, torch.float16, "out")
     _want(topk_idx, torch.int32, "topk_idx")
+    _want_opt(topk_count, torch.int32, "topk_count")
+    _want_opt(head_map, torch.int32, "head_map")
     B, H, D = q.shape
     G = topk_idx.shape[1]
     assert D == HEAD_DIM and q.stride(2) == 1 and out.is_contiguous() and topk_idx.stride(2) == 1
@@ -227,6 +283,7 @@ def decode_sparse_paged(q, kv: KvLayout, topk_idx, topk_count, k_max, head_map, 
 NOALLOC_MAX_SLOTS = 8192
 
 
+@_on_device_of(0)
 def decode_sparse_paged_noalloc(q, kv: KvLayout, topk_idx, topk_count, k_max, head_map, scale, out, lse2=None,
                                 num_splits=0):
     """Same result as decode_sparse_paged, for callers that cannot allocate or pass a workspace: the split
@@ -236,6 +293,8 @@ def decode_sparse_paged_noalloc(q, kv: KvLayout, topk_idx, topk_count, k_max, he
     _want(q, torch.float16, "q")
     _want(out, torch.float16, "out")
     _want(topk_idx, torch.int32, "topk_idx")
+    _want_opt(topk_count, torch.int32, "topk_count")
+    _want_opt(head_map, torch.int32, "head_map")
     B, H, D = q.shape
     G = topk_idx.shape[1]
     assert D == HEAD_DIM and q.stride(2) == 1 and out.is_contiguous() and topk_idx.stride(2) == 1
@@ -243,9 +302,10 @@ def decode_sparse_paged_noalloc(q, kv: KvLayout, topk_idx, topk_count, k_max, he
         _ptr(q), q.stride(0), q.stride(1), C.byref(kv), _ptr(topk_idx), topk_idx.stride(0), topk_idx.stride(1),
         _ptr(topk_count), k_max, _ptr(head_map), float(scale), _ptr(out), _ptr(lse2), B, H, G, num_splits,
         _stream()), "kb200_decode_sparse_paged_noalloc")
-    _launched(2 if num_splits != 1 else 1)
+    _launched(2 if lib.kb200_decode_noalloc_splits(B, H, G, k_max, num_splits) > 1 else 1)
 
 
+@_on_device_of(0)
 def decode_anchor_paged(q, kv: KvLayout, seq_lens, max_seq_len, scale, logits, pooled, out, lse2,
                         workspace=None, num_splits=0):
     """q [B,H,D]; logits [B,H,stride] fp32; pooled [B,G,stride] fp32; out [B,H,D] fp16 or None."""
@@ -272,6 +332,7 @@ def act_layout(x: torch.Tensor) -> ActLayout:
     return ActLayout(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2))
 
 
+@_on_device_of(0)
 def prefill_dense(q, k, v, scale, out, lse2, fanout: Optional[OutFanout] = None):
     """q [B,L,H,D], k/v [B,L,G,D] (views allowed); out [B,L,H,D] fp16 contiguous or None; lse2 [B,L,H] fp32 or None.
     With `fanout` (see out_fanout) the rows go into several [B,L,total_heads,D] buffers instead of `out`."""
@@ -293,6 +354,7 @@ def prefill_dense(q, k, v, scale, out, lse2, fanout: Optional[OutFanout] = None)
     _launched(1)
 
 
+@_on_device_of(0)
 def prefill_pool_scores(q, k, lse2, scale, pooled):
     """pooled [B,G,T,row_stride] fp32 contiguous."""
     lib = init(q.device.index)
@@ -307,6 +369,7 @@ def prefill_pool_scores(q, k, lse2, scale, pooled):
     _launched(1)
 
 
+@_on_device_of(0)
 def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=None, fanout: Optional[OutFanout] = None):
     """tile_idx [B,G,T,kstride] int32, tile_count [B,G,T] int32, out [B,L,H,D] fp16 contiguous.
     With `fanout` (see out_fanout) the rows go into several [B,L,total_heads,D] buffers instead of `out`."""
@@ -316,6 +379,7 @@ def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=Non
     ql, kl, vl = act_layout(q), act_layout(k), act_layout(v)
     _want(tile_idx, torch.int32, "tile_idx")
     _want(tile_count, torch.int32, "tile_count")
+    _want_opt(head_map, torch.int32, "head_map")
     assert tile_idx.is_contiguous() and tile_count.is_contiguous()
     if fanout is not None:
         _check(lib.kb200_prefill_sparse_fanout(C.byref(ql), C.byref(kl), C.byref(vl), _ptr(tile_idx),
@@ -332,6 +396,7 @@ def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=Non
     _launched(1)
 
 
+@_on_device_of(2)
 def kv_write(q_in, q_out, k_new, v_new, start_pos, n_new, kv: KvLayout, q_gain=None, k_gain=None, eps=1e-6,
              inv_freq=None, rope_scale=1.0):
     """q_in [B,T,H,D] (or None), k_new / v_new [B,T,G,D] fp16 views; start_pos [B] int32; n_new [B] int32 or None;
@@ -345,6 +410,9 @@ def kv_write(q_in, q_out, k_new, v_new, start_pos, n_new, kv: KvLayout, q_gain=N
         _want(q_out, torch.float16, "q_out")
         assert q_out.is_contiguous() and q_out.shape == q_in.shape
     _want(start_pos, torch.int32, "start_pos")
+    _want_opt(n_new, torch.int32, "n_new")
+    _want_opt(q_gain, torch.float16, "q_gain")
+    _want_opt(k_gain, torch.float16, "k_gain")
     if inv_freq is not None:
         _want(inv_freq, torch.float32, "inv_freq")
         assert inv_freq.is_contiguous() and inv_freq.numel() == HEAD_DIM // 2
@@ -354,9 +422,61 @@ def kv_write(q_in, q_out, k_new, v_new, start_pos, n_new, kv: KvLayout, q_gain=N
     _launched(1)
 
 
+@_on_device_of(0)
 def selftest_umma(a: torch.Tensor, b: torch.Tensor):
     lib = init(a.device.index)
     out = torch.zeros(4, 128, 128, dtype=torch.float32, device=a.device)
     status = torch.full((4,), -1, dtype=torch.int32, device=a.device)
     _check(lib.kb200_selftest_umma(_ptr(a), _ptr(b), _ptr(out), _ptr(status), _stream()), "kb200_selftest_umma")
     return out, status
+
+
+def selftest_wait_timeout(device, limit_ns: int = 1_000_000, code: int = 77) -> torch.Tensor:
+    """Runs the wait-that-runs-out selftest on `device`; returns [code, threads that gave up, elapsed ns].
+    The device status word then holds `code` until read_status() / check_status() clears it."""
+    result = torch.zeros(3, dtype=torch.int32, device=device)
+    with torch.cuda.device(result.device):
+        lib = init(result.device.index)
+        _check(lib.kb200_selftest_wait_timeout(_ptr(result), int(limit_ns), int(code), _stream()),
+               "kb200_selftest_wait_timeout")
+    _launched(1)
+    return result
+
+
+def tensor_map_encodes() -> int:
+    return int(load().kb200_tensor_map_encodes())
+
+
+def _cuda_event(ev: torch.cuda.Event) -> int:
+    """cudaEvent_t of a torch event (torch creates it lazily, at the first record)."""
+    if not ev.cuda_event:
+        ev.record()
+    return int(ev.cuda_event)
+
+
+def push_plan(dst_pointers, streams, done_events) -> PushPlan:
+    """One entry per peer: device address of its buffer, a torch stream for the copy, a torch event."""
+    if not (len(dst_pointers) == len(streams) == len(done_events)) or len(dst_pointers) > MAX_FANOUT:
+        raise KascadeNativeError("push_plan: one stream and one event per peer, at most %d peers" % MAX_FANOUT)
+    plan = PushPlan()
+    for i, (ptr, st, ev) in enumerate(zip(dst_pointers, streams, done_events)):
+        plan.dst[i], plan.stream[i], plan.done_event[i] = int(ptr), int(st.cuda_stream), _cuda_event(ev)
+    plan.count = len(dst_pointers)
+    return plan
+
+
+def peer_push(plan: PushPlan, src: torch.Tensor, offset_bytes: int, pitch_bytes: int, width_bytes: int, rows: int,
+              ready_event: torch.cuda.Event):
+    """Copy the row slice [offset, offset + width) of every `pitch`-byte row of `src` into the peers' buffers with
+    the copy engines, after everything queued on the current stream (see kb200_peer_push)."""
+    with torch.cuda.device(src.device):
+        _check(load().kb200_peer_push(C.byref(plan), _ptr(src), offset_bytes, pitch_bytes, width_bytes, rows,
+                                      C.c_void_p(_cuda_event(ready_event)), _stream()), "kb200_peer_push")
+
+
+def stream_wait_events(events):
+    """Make the current stream wait for the given torch events (those already recorded)."""
+    handles = [int(e.cuda_event) for e in events if e.cuda_event]
+    if handles:
+        arr = (C.c_void_p * len(handles))(*handles)
+        _check(load().kb200_stream_wait_events(_stream(), arr, len(handles)), "kb200_stream_wait_events")

@@ -27,7 +27,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
 ]
-# extra compiler flags, e.g. KB200_NVCC_EXTRA=-DKB200_TRACE for the kernels' timeline tracing
+# extra compiler flags (A/B builds of a kernel variant)
 NVCC_FLAGS += shlex.split(os.environ.get("KB200_NVCC_EXTRA", ""))
 
 

@@ -12,6 +12,14 @@ namespace kb200 {
 // thread-local error text returned by kb200_last_error()
 void set_error(const char* fmt, ...);
 bool initialised(int* device_out);
+int check_on_current_device(const void* ptr, const char* what);
+
+#define KB_ENTRY(first_ptr, what)                                                                 \
+  do {                                                                                            \
+    KB_REQUIRE(kb200::initialised(nullptr),                                                       \
+               "kb200_init has not been called for the device that is current in this thread");  \
+    if (kb200::check_on_current_device(first_ptr, what) != 0) return -1;                          \
+  } while (0)
 
 #define KB_REQUIRE(cond, ...)        \
   do {                               \

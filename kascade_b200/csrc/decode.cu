@@ -450,7 +450,22 @@ static int static_partials(float** out) {
   return 0;
 }
 
+// Splits the no-allocation entry point uses: an explicit request as given if it fits the built-in scratch
+// (a single split always fits, it needs none), the library's own choice lowered until it fits; 0 = rejected.
+static int noalloc_splits(int batch, int H, int G, int k_max, int num_splits) {
+  int splits = num_splits > 0 ? num_splits : default_splits(batch, G, k_max);
+  if (num_splits == 0)
+    while (splits > 1 && (long long)batch * H * splits > KB200_NOALLOC_MAX_SLOTS) --splits;
+  if (splits > 1 && (long long)batch * H * splits > KB200_NOALLOC_MAX_SLOTS) return 0;
+  return splits;
+}
+
 }  // namespace kb200
+
+extern "C" int kb200_decode_noalloc_splits(int batch, int num_q_heads, int num_kv_heads, int k_max, int num_splits) {
+  if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_splits < 0) return 0;
+  return kb200::noalloc_splits(batch, num_q_heads, num_kv_heads, k_max, num_splits);
+}
 
 extern "C" size_t kb200_decode_workspace_bytes(int batch, int num_q_heads, int num_splits) {
   if (batch <= 0 || num_q_heads <= 0 || num_splits <= 0) return 0;
@@ -470,7 +485,7 @@ extern "C" int kb200_decode_sparse_paged(const void* q, int64_t q_stride_b, int6
                                          int batch, int num_q_heads, int num_kv_heads,
                                          int num_splits, void* stream) {
   using namespace kb200;
-  KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
+  KB_ENTRY(q, "decode_sparse: q");
   KB_REQUIRE(q && topk_idx && out, "decode_sparse: null pointer");
   KB_REQUIRE(batch >= 0 && k_max >= 0, "decode_sparse: negative size");
   KB_REQUIRE(num_kv_heads > 0 && num_q_heads == num_kv_heads * kHg,
@@ -519,7 +534,7 @@ extern "C" int kb200_decode_anchor_paged(const void* q, int64_t q_stride_b, int6
                                          int batch, int num_q_heads, int num_kv_heads,
                                          int num_splits, void* stream) {
   using namespace kb200;
-  KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
+  KB_ENTRY(q, "decode_anchor: q");
   KB_REQUIRE(q && seq_lens && logits && pooled && lse2_out, "decode_anchor: null pointer");
   KB_REQUIRE(batch >= 0 && max_seq_len >= 0, "decode_anchor: negative size");
   KB_REQUIRE(num_kv_heads > 0 && num_q_heads == num_kv_heads * kHg,
@@ -589,7 +604,7 @@ extern "C" int kb200_decode_sparse_paged_noalloc(const void* q, int64_t q_stride
                                                  float* lse2_out, int batch, int num_q_heads,
                                                  int num_kv_heads, int num_splits, void* stream) {
   using namespace kb200;
-  KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
+  KB_ENTRY(q, "decode_noalloc: q");
   KB_REQUIRE(q && topk_idx && out, "decode_noalloc: null pointer");
   KB_REQUIRE(batch >= 0 && k_max >= 0, "decode_noalloc: negative size");
   KB_REQUIRE(num_kv_heads > 0 && num_q_heads == num_kv_heads * kHg,
@@ -601,21 +616,20 @@ extern "C" int kb200_decode_sparse_paged_noalloc(const void* q, int64_t q_stride
   if (batch == 0) return 0;
   DecodeParams p{};
   if (fill_kv(p, kv, true) != 0) return -1;
-  int splits = num_splits > 0 ? num_splits : default_splits(batch, num_kv_heads, k_max);
-  if (num_splits == 0) {                       // the library's own choice must fit: fall back to fewer splits
-    while (splits > 1 && (long long)batch * num_q_heads * splits > KB200_NOALLOC_MAX_SLOTS) --splits;
-  }
-  const long long slots = (long long)batch * num_q_heads * splits;
-  KB_REQUIRE(splits == 1 || (long long)batch * num_q_heads * splits <= KB200_NOALLOC_MAX_SLOTS,
+  const int splits = noalloc_splits(batch, num_q_heads, num_kv_heads, k_max, num_splits);
+  const long long slots = (long long)batch * num_q_heads * (splits > 0 ? splits : num_splits);
+  KB_REQUIRE(splits > 0,
              "decode_noalloc: batch %d x %d heads x %d splits = %lld partial slots exceed the built-in scratch of %d "
              "slots; use fewer splits or kb200_decode_sparse_paged with a caller-owned workspace",
-             batch, num_q_heads, splits, slots, KB200_NOALLOC_MAX_SLOTS);
-  float* scratch = nullptr;
-  if (static_partials(&scratch) != 0) return -1;
-  const size_t bhs = (size_t)batch * num_q_heads * splits;
-  p.ws_m = scratch;
-  p.ws_l = scratch + bhs;
-  p.ws_o = scratch + 2 * bhs;
+             batch, num_q_heads, num_splits, slots, KB200_NOALLOC_MAX_SLOTS);
+  if (splits > 1) {                            // a single split writes the output directly: no scratch, no look-up
+    float* scratch = nullptr;
+    if (static_partials(&scratch) != 0) return -1;
+    const size_t bhs = (size_t)batch * num_q_heads * splits;
+    p.ws_m = scratch;
+    p.ws_l = scratch + bhs;
+    p.ws_o = scratch + 2 * bhs;
+  }
   p.q = static_cast<const __half*>(q);
   p.q_stride_b = q_stride_b;
   p.q_stride_h = q_stride_h;

@@ -127,7 +127,7 @@ extern "C" int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const k
                               float norm_eps, const float* inv_freq, float rope_scale, int batch, int max_new,
                               int num_q_heads, int num_kv_heads, void* stream) {
   using namespace kb200;
-  KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
+  KB_ENTRY(k_new ? k_new->ptr : nullptr, "kv_write: k_new");
   KB_REQUIRE(k_new && k_new->ptr && v_new && v_new->ptr && start_pos && kv && kv->k && kv->v,
              "kv_write: null pointer");
   KB_REQUIRE(batch >= 0 && max_new >= 0 && num_kv_heads > 0 && num_q_heads >= 0, "kv_write: bad sizes");

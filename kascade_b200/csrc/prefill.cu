@@ -38,6 +38,8 @@
 #include <stdlib.h>
 
 #include <algorithm>
+#include <atomic>
+#include <mutex>
 
 #include "common.cuh"
 #include "umma.cuh"
@@ -190,25 +192,6 @@ struct PfCfg {
   static constexpr int kMmaWarp = kGather ? 12 : (kHasV ? 9 : 13);
 };
 
-// Optional timeline tracing (compile with -DKB200_TRACE): up to six roles of CTA 0 record
-// (tag, clock64) pairs, read back by kb200_debug_trace.  Compiled out by default.
-#ifdef KB200_TRACE
-__device__ long long g_trace[6][2048][2];
-__device__ int g_trace_n[6];
-#define KB_TR_DECL int trn = 0
-#define KB_TR(role, tag)                                                     \
-  do {                                                                       \
-    if (blockIdx.x == 0 && trn < 2048) {                                     \
-      g_trace[role][trn][0] = (tag);                                         \
-      g_trace[role][trn][1] = clock64();                                     \
-      g_trace_n[role] = ++trn;                                               \
-    }                                                                        \
-  } while (0)
-#else
-#define KB_TR_DECL
-#define KB_TR(role, tag)
-#endif
-
 template <int MODE>
 __global__ void __launch_bounds__(PfCfg<MODE>::kThreads, 1)
 tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_constant__ CUtensorMap tm_q,
@@ -223,8 +206,12 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
 
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // an earlier CTA or kernel gave up a bounded wait: do not queue up more waits behind it
-  if (*reinterpret_cast<volatile int*>(&g_status_word) != 0) return;
+  // an earlier CTA or kernel gave up a bounded wait: do not queue up more waits behind it.  One thread
+  // reads the word and the whole CTA takes the same decision.
+  __shared__ int s_abort;
+  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(&g_status_word);
+  __syncthreads();
+  if (s_abort != 0) return;
   const uint32_t pad = (1024u - (smem_addr(smem_raw) & 1023u)) & 1023u;
   if (pad > (uint32_t)kPadAllowance) {                   // never seen; refuse rather than overrun
     if (tid == 0) atomicCAS(&g_status_word, 0, 90);
@@ -302,7 +289,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     const int n_st = is_v ? kNV : kNK;
     int st = 0, ph = 1, qn = 0;                          // ring position, parity of its "empty" phase; Q tiles loaded
     bool ok = true;
-    KB_TR_DECL;
     uint32_t soff[4];                                    // swizzled offset of (row 2 q + (lane >> 4), chunk lane & 15)
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) soff[q4] = tile_off(2 * q4 + (lane >> 4), lane & 15, 128);
@@ -347,10 +333,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         const int key0 = max(0, min(a0, p.L - 1)), key1 = max(0, min(a1, p.L - 1));
         a0 = b0; a1 = b1;
         b0 = load_key(j + 2, 0); b1 = load_key(j + 2, 1);
-        if (lane == 0 && part == 0) KB_TR(4 + (is_v ? 1 : 0), 20);
         ok = mbar_wait(&bar_empty[st], ph, &give_up, is_v ? 12 : 11);
         if (!ok) break;
-        if (lane == 0 && part == 0) KB_TR(4 + (is_v ? 1 : 0), 21);
         // Per copy: one shuffle (the row's key), one multiply-add (its address), one cp.async; the
         // swizzled destination of row (2 i + sub) repeats every four i, 1024 bytes further on.
         const uint32_t dst = ring_s + st * kStageBytes + r_begin * 128;
@@ -367,7 +351,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
           }
         }
         cp_arrive_noinc(&bar_full[st]);
-        if (lane == 0 && part == 0) KB_TR(4 + (is_v ? 1 : 0), 22);
         if (++st == n_st) { st = 0; ph ^= 1; }
       }
     }
@@ -514,7 +497,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   // Products of different warps are not ordered; every dependency between them goes through a
   // barrier (S consumed -> next Q.K^T into that buffer; P written -> P.V; P.V done -> P rewritten).
   auto mma_qk_v = [&]() {
-    KB_TR_DECL;
     constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
     constexpr uint32_t kStage16 = kStageBytes >> 4;      // descriptor address units are 16 bytes
     const uint32_t q_lo = desc_lo(q_s, 16), k_lo0 = desc_lo(k_s, 16);
@@ -545,7 +527,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         if (!ok) break;
         if (GATHER) fence_proxy_async_smem();            // cp.async bytes -> visible to the tensor core
         tc_fence_after();
-        if (lane == 0) KB_TR(2, 10);
         const uint32_t k_lo = k_lo0 + k_st * kStage16;
         const uint32_t d = t_s0 + w * 128;
         if (el) {
@@ -560,14 +541,12 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
           if (j + 1 == it.nb) mma_commit(&sh.bar_qempty);  // the tile's last Q.K^T is queued: Q may be replaced
         }
         __syncwarp();
-        if (lane == 0) KB_TR(2, 11);
         ++iss;
         if (++k_st == kNK) { k_st = 0; k_ph ^= 1; }
       }
     }
   };
   auto mma_pv_v = [&]() {
-    KB_TR_DECL;
     constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
     constexpr uint32_t kStage16 = kStageBytes >> 4;
     const uint32_t t_acc = tmem + 384, t_p = tmem + 256;
@@ -594,7 +573,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         // P(j) is in tensor memory, and O is in the scale P(j) was computed in
         ok = mbar_wait(&bar_pready[w], cons & 1, &give_up, 24);
         if (!ok) break;
-        if (lane == 0) KB_TR(3, 13);
         if (GATHER) fence_proxy_async_smem();
         tc_fence_after();
         const uint32_t v_lo = v_lo0 + v_st * kStage16;
@@ -607,7 +585,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
           mma_commit(&bar_odone[w]);
         }
         __syncwarp();
-        if (lane == 0) KB_TR(3, 14);
         ++cons;
         if (++v_st == kNV) { v_st = 0; v_ph ^= 1; }
       }
@@ -630,7 +607,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   // block j waits for P.V(j-1) and rescales its O row before it releases P(j).  Each thread keeps
   // its part of the row sum in the reference of its own last block; the parts meet in the epilogue.
   auto softmax_role_v = [&]() {
-    KB_TR_DECL;
     const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane, q_local = row >> 2;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
@@ -656,11 +632,9 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         if (!ok) break;
       }
       for (int j = wg, jj = 0; j < it.nb; j += 2, ++jj) {
-        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 0);
         ok = mbar_wait(&bar_sfull[wg], (done_mine + jj) & 1, &give_up, 31);
         if (!ok) break;
         tc_fence_after();
-        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 1);
         // the whole S row (128 fp32) comes into registers with one round trip to tensor memory
         uint32_t sr[4][32];
 #pragma unroll
@@ -668,7 +642,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&sh.bar_sfree[wg]);                   // Q.K^T(j+2) may overwrite the buffer
-        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 2);
         const int c0 = j * 128 - off;                     // key position (inside the tile) of column 0
         if ((c0 + 127) > 0) {                             // only the last block(s) of a tile
 #pragma unroll
@@ -689,7 +662,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
           }
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale2;
-        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 3);
         // ---- the row's reference for this block --------------------------------------------------
         // index (in the other stream's count) of block j-1: the other stream owns j-1, j-3, ...
         const int prev_idx = done_other + ((j - 1) >> 1);
@@ -704,7 +676,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         const float ref = (mx > ref_prev + kRescaleLog2) ? mx : ref_prev;
         *ref_mine = ref;
         mbar_arrive(&sh.bar_lse[wg]);
-        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 4);
         // P.V of this stream's previous block has read the P buffer
         if (done_mine + jj > 0) {
           ok = mbar_wait(&bar_odone[wg], (done_mine + jj - 1) & 1, &give_up, 38);
@@ -730,7 +701,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         const float beta = (m_l == -INFINITY) ? 0.f : ex2(m_l - ref);
         l_run = l_run * beta + ((s0 + s1) + (s2 + s3));
         m_l = ref;
-        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 5);
         if (j > 0 && __any_sync(0xFFFFFFFFu, ref != ref_prev)) {
           // O is in the scale of ref(j-1): once P.V(j-1) has landed, bring this row to ref(j).
           // (P.V(j-3) is known complete: this thread waited for P.V(j-2) above, and they complete in order.)
@@ -749,7 +719,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
           }
         }
         tmem_wait_st();
-        if (lane == 0 && (warp & 3) == 0) KB_TR(wg, 6);
         tc_fence_before();
         mbar_arrive(&bar_pready[wg]);
       }
@@ -1061,6 +1030,48 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   if (tid == 0 && give_up != 0) atomicCAS(&g_status_word, 0, give_up);
 }
 
+// The give-up path of the bounded waits, exercised on purpose and harmlessly: one CTA allocates tensor
+// memory like the prefill kernels, then every thread waits (with a limit of `limit_ns`) on a barrier on
+// which nobody ever arrives.  The wait must run out, the first thread to notice records `code`, the others
+// see the flag and leave too, the CTA frees its tensor memory, publishes the code in the device status
+// word (the one kb200_read_status returns and clears) and returns.  result[0] = the code the CTA ended
+// with, result[1] = number of threads whose wait returned false, result[2] = elapsed nanoseconds.
+__global__ void __launch_bounds__(128, 1)
+selftest_wait_timeout_kernel(int32_t* __restrict__ result, unsigned long long limit_ns, int code) {
+  using namespace umma;
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base_sh;
+  __shared__ int give_up;
+  __shared__ int n_false;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    give_up = 0;
+    n_false = 0;
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_sh, 32);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint64_t t0 = global_ns();
+  const bool ok = mbar_wait_limit(&bar, 0, &give_up, code, limit_ns);   // nobody arrives: must return false
+  if (!ok) atomicAdd(&n_false, 1);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0) tmem_dealloc(tmem_base_sh, 32);
+  if (tid == 0) {
+    if (give_up != 0) atomicCAS(&g_status_word, 0, give_up);
+    result[0] = give_up;
+    result[1] = n_false;
+    result[2] = (int32_t)min((unsigned long long)(global_ns() - t0), 0x7FFFFFFFull);
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -1084,6 +1095,26 @@ int init_prefill() {
 
 // 4-D tiled map over fp16 activations: dimensions (d, head, token, batch), 128-byte swizzle, boxes of
 // 64 x box_heads x box_tokens x 1 elements.  Host-only work (the descriptor is passed by value).
+// Encoded descriptors are kept in a small table keyed by (pointer, strides, extents, box): a serving
+// loop presents the same few layouts again and again (one per layer buffer), so steady-state calls
+// encode nothing.  A descriptor holds no device state, so an entry never goes stale: the same key
+// always encodes to the same bytes.
+struct MapKey {
+  const void* base;
+  int64_t sb, st, sh;
+  int heads, tokens, batch, box_heads, box_tokens;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && sb == o.sb && st == o.st && sh == o.sh && heads == o.heads && tokens == o.tokens &&
+           batch == o.batch && box_heads == o.box_heads && box_tokens == o.box_tokens;
+  }
+};
+constexpr int kMapCacheSize = 128;
+static MapKey g_map_keys[kMapCacheSize];
+static CUtensorMap g_map_vals[kMapCacheSize];
+static int g_map_used = 0, g_map_next = 0;
+static std::mutex g_map_mutex;
+static std::atomic<long long> g_map_encodes{0};
+
 static int make_act_map(CUtensorMap* map, const __half* base, int64_t sb, int64_t st, int64_t sh, int heads,
                         int tokens, int batch, int box_heads, int box_tokens, const char* what) {
   KB_REQUIRE(g_encode_tiled, "kb200_init has not been called");
@@ -1091,6 +1122,15 @@ static int make_act_map(CUtensorMap* map, const __half* base, int64_t sb, int64_
   const int64_t min_stride = 8;
   if (heads == 1 && sh < min_stride) sh = kD;
   if (batch == 1 && sb < min_stride) sb = (int64_t)tokens * (st > 0 ? st : kD);
+  const MapKey key{base, sb, st, sh, heads, tokens, batch, box_heads, box_tokens};
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    for (int i = 0; i < g_map_used; ++i)
+      if (g_map_keys[i] == key) {
+        *map = g_map_vals[i];
+        return 0;
+      }
+  }
   const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)heads, (cuuint64_t)tokens, (cuuint64_t)batch};
   const cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)st * 2, (cuuint64_t)sb * 2};
   const cuuint32_t box[4] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_tokens, 1};
@@ -1101,6 +1141,11 @@ static int make_act_map(CUtensorMap* map, const __half* base, int64_t sb, int64_
   KB_REQUIRE(r == CUDA_SUCCESS,
              "prefill: cuTensorMapEncodeTiled rejected the layout of %s (error %d; strides b/t/h = %lld/%lld/%lld)", what,
              (int)r, (long long)sb, (long long)st, (long long)sh);
+  g_map_encodes.fetch_add(1);
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  const int slot = g_map_used < kMapCacheSize ? g_map_used++ : (g_map_next++ % kMapCacheSize);
+  g_map_keys[slot] = key;
+  g_map_vals[slot] = *map;
   return 0;
 }
 
@@ -1164,8 +1209,8 @@ static unsigned persistent_grid(const PrefillParams& p) {
   return (unsigned)(items < sms ? items : sms);
 }
 
-static int check_shape(int batch, int seq_len, int H, int G) {
-  KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
+static int check_shape(const kb200_act_layout* q, int batch, int seq_len, int H, int G) {
+  KB_ENTRY(q ? q->ptr : nullptr, "prefill: q");
   KB_REQUIRE(batch >= 0 && seq_len >= 0, "prefill: negative size");
   KB_REQUIRE(G > 0 && H == G * kHg,
              "prefill: %d query heads / %d KV heads; exactly %d query heads per KV head are supported", H, G, kHg);
@@ -1175,15 +1220,8 @@ static int check_shape(int batch, int seq_len, int H, int G) {
 
 }  // namespace kb200
 
-#ifdef KB200_TRACE
-extern "C" int kb200_debug_trace(long long* buf, int* cnt) {
-  cudaMemcpyFromSymbol(buf, kb200::g_trace, sizeof(long long) * 6 * 2048 * 2);
-  cudaMemcpyFromSymbol(cnt, kb200::g_trace_n, sizeof(int) * 6);
-  int z[6] = {0, 0, 0, 0, 0, 0};
-  cudaMemcpyToSymbol(kb200::g_trace_n, z, sizeof(z));
-  return 0;
-}
-#endif
+extern "C" long long kb200_tensor_map_encodes(void) { return kb200::g_map_encodes.load(); }
+
 extern "C" int kb200_read_status(int* host_out) {
   using namespace kb200;
   KB_REQUIRE(host_out, "read_status: null pointer");
@@ -1193,11 +1231,22 @@ extern "C" int kb200_read_status(int* host_out) {
   return 0;
 }
 
+extern "C" int kb200_selftest_wait_timeout(int32_t* result, uint64_t limit_ns, int code, void* stream) {
+  using namespace kb200;
+  KB_ENTRY(result, "selftest_wait_timeout: result");
+  KB_REQUIRE(result, "selftest_wait_timeout: null pointer");
+  KB_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ull, "selftest_wait_timeout: limit must lie in (0, 100 ms]");
+  KB_REQUIRE(code > 0 && code < 256, "selftest_wait_timeout: code must lie in [1, 255]");
+  selftest_wait_timeout_kernel<<<1, 128, 0, (cudaStream_t)stream>>>(result, (unsigned long long)limit_ns, code);
+  KB_CHECK_LAUNCH("selftest_wait_timeout_kernel");
+  return 0;
+}
+
 namespace kb200 {
 static int prefill_dense_impl(const kb200_act_layout* q, const kb200_act_layout* k, const kb200_act_layout* v,
                               float softmax_scale, void* out, const kb200_out_fanout* fan, float* lse2, int batch,
                               int seq_len, int num_q_heads, int num_kv_heads, void* stream) {
-  if (check_shape(batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
+  if (check_shape(q, batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
   if (fan) out = fan->count >= 1 ? fan->out[0] : nullptr;
   KB_REQUIRE(out || lse2, "prefill_dense: nothing to compute (out and lse2 are both null)");
   if (batch == 0 || seq_len == 0) return 0;
@@ -1247,7 +1296,7 @@ extern "C" int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_
                                          int64_t row_stride, int batch, int seq_len, int num_q_heads,
                                          int num_kv_heads, void* stream) {
   using namespace kb200;
-  if (check_shape(batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
+  if (check_shape(q, batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
   KB_REQUIRE(lse2 && pooled, "prefill_pool_scores: null pointer");
   KB_REQUIRE(row_stride >= seq_len, "prefill_pool_scores: row_stride (%lld) smaller than seq_len (%d)",
              (long long)row_stride, seq_len);
@@ -1276,7 +1325,7 @@ static int prefill_sparse_impl(const kb200_act_layout* q, const kb200_act_layout
                                const int32_t* head_map, float softmax_scale, void* out, const kb200_out_fanout* fan,
                                float* lse2, int batch, int seq_len, int num_q_heads, int num_kv_heads,
                                int idx_kv_heads, void* stream) {
-  if (check_shape(batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
+  if (check_shape(q, batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
   if (fan) out = fan->count >= 1 ? fan->out[0] : nullptr;
   KB_REQUIRE(tile_idx && tile_count && out, "prefill_sparse: null pointer");
   KB_REQUIRE(idx_stride >= 0, "prefill_sparse: negative idx_stride");

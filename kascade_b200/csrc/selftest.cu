@@ -112,7 +112,7 @@ int init_selftest() {
 
 extern "C" int kb200_selftest_umma(const void* a, const void* b, float* out, int32_t* status, void* stream) {
   using namespace kb200;
-  KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
+  KB_ENTRY(a, "selftest_umma: a");
   KB_REQUIRE(a && b && out && status, "selftest_umma: null pointer");
   KB_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(b) & 15) == 0,
              "selftest_umma: inputs must be 16-byte aligned");

@@ -181,7 +181,7 @@ extern "C" int kb200_topk_select(const float* scores, int64_t row_stride, int n_
                                  int32_t* out_idx, int64_t idx_stride, int32_t* out_count,
                                  int64_t rows, void* stream) {
   using namespace kb200;
-  KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
+  KB_ENTRY(scores, "topk_select: scores");
   KB_REQUIRE(scores && out_idx, "topk_select: null pointer");
   KB_REQUIRE(rows >= 0 && n_cols >= 0 && k_max >= 0, "topk_select: negative size");
   KB_REQUIRE(n_cols <= row_stride, "topk_select: n_cols (%d) exceeds row_stride (%lld)", n_cols,
@@ -201,7 +201,7 @@ extern "C" int kb200_topk_select(const float* scores, int64_t row_stride, int n_
 extern "C" int kb200_prefill_budgets(int32_t* n_valid, int32_t* k_row, int batch, int num_kv_heads,
                                      int num_tiles, int k_max, float pct, int rolling, void* stream) {
   using namespace kb200;
-  KB_REQUIRE(initialised(nullptr), "kb200_init has not been called");
+  KB_ENTRY(n_valid, "prefill_budgets: n_valid");
   KB_REQUIRE(n_valid && k_row, "prefill_budgets: null pointer");
   int total = batch * num_kv_heads * num_tiles;
   if (total <= 0) return 0;

@@ -57,18 +57,22 @@ __device__ __forceinline__ uint64_t global_ns() {
 }
 // Waits for the phase with the given parity to complete.  Returns false (after setting *flag to
 // `code`) once kWaitLimitNs have passed; callers then drain and leave instead of spinning for ever.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* flag, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* flag, int code,
+                                                uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_ns();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 0) {
       if (*flag != 0) return false;                     // somebody else already gave up
-      if (global_ns() - t0 > kWaitLimitNs) break;
+      if (global_ns() - t0 > limit_ns) break;
     }
   }
   *flag = code;
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* flag, int code) {
+  return mbar_wait_limit(bar, parity, flag, code, kWaitLimitNs);
 }
 
 // ---- TMA (bulk tensor copies, no multicast) --------------------------------------------------------

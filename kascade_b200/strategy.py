@@ -94,13 +94,25 @@ class EfficientKascadeStrategy(Strategy):
     compute only its slice of the KV heads of every prefill layer (batch 1): the caller passes the
     local heads' q/k/v, anchor index rows are all-gathered over torch.distributed, and the per-head
     outputs of every layer are all-gathered into ``self.gathered_out`` ([world, B, L, H/world, D]).
-    With ``peer_store=True`` there is no output all-gather: the prefill kernels store their rows
-    straight into every rank's [B, L, H, D] buffer over NVLink (``gathered_out`` then has that shape,
-    two buffers are used in turn, and it is complete after ``wait_gathers()``)."""
+    ``exchange`` picks how the sharded outputs travel:
+
+    * ``"nccl"`` (default): an asynchronous ``all_gather_into_tensor`` per layer;
+    * ``"peer_store"`` (or ``peer_store=True``): no collective, the prefill kernels store their rows straight
+      into every rank's [B, L, H, D] buffer over NVLink (best on two GPUs, where a layer's compute time
+      exceeds its link time);
+    * ``"push"``: the kernel writes this rank's heads into its own [B, L, H, D] buffer and the copy engines
+      push that slice into the peers' buffers on side streams while the next layers' kernels run (best
+      from four GPUs on, where a reuse layer's link time exceeds its compute time).
+
+    In the last two modes ``gathered_out`` is a [B, L, H, D] buffer of a small ring (``copies``), complete
+    once ``wait_gathers()`` has returned on every rank.  The buffer of layer n is written again by layer
+    n + copies (and by the peers' kernels or copies of that layer): a consumer that reads every layer's
+    ``gathered_out`` must call ``wait_gathers()`` after every layer, on all ranks, before it reads."""
 
     def __init__(self, recompute_layers: List[int], model_name: str, k=1, tile_size=1, rolling_prefill=False,
                  block_size=12288, *, head_mapping: Optional[Sequence[Sequence[int]]] = None,
-                 register: bool = True, shard: Optional[tuple] = None, peer_store: bool = False):
+                 register: bool = True, shard: Optional[tuple] = None, peer_store: bool = False,
+                 exchange: Optional[str] = None, copies: Optional[int] = None):
         if recompute_layers is None:
             raise ValueError("recompute_layers cannot be None for EfficientKascadeStrategy")
         if not (0 <= k <= 100):
@@ -118,9 +130,18 @@ class EfficientKascadeStrategy(Strategy):
             else self.get_head_mapping(model_name)
         self._register = register
         self._shard = tuple(shard) if shard is not None else None
-        self._peer_store = bool(peer_store) and self._shard is not None and self._shard[1] > 1
+        if exchange is None:
+            exchange = "peer_store" if peer_store else "nccl"
+        if exchange not in ("nccl", "peer_store", "push"):
+            raise ValueError(f"exchange must be 'nccl', 'peer_store' or 'push', got {exchange!r}")
+        sharded = self._shard is not None and self._shard[1] > 1
+        self._exchange = exchange if sharded else "nccl"
+        self._peer_store = self._exchange in ("peer_store", "push")   # outputs live in peer-mapped [B,L,H,D] buffers
+        self._copies = int(copies) if copies else (4 if self._exchange == "push" else 2)
         self._peer = None                       # kascade_b200.peer.PeerBuffers, allocated at the first prefill
         self._peer_copy = 0
+        self._push = None                       # push mode: streams, events and plans
+        self._checked_device = None
         self.gathered_out: Optional[torch.Tensor] = None
         self._pending = []
         # cross-layer state written by anchor layers (strategies/KascadeStrategy.py:95,133)
@@ -155,6 +176,22 @@ class EfficientKascadeStrategy(Strategy):
 
         ALL_MASK_ATTENTION_FUNCTIONS.register(self.name, ALL_MASK_ATTENTION_FUNCTIONS["sdpa"])
         ALL_ATTENTION_FUNCTIONS.register(self.name, _fwd)
+
+    def check_status(self, device=None):
+        """Raise ``KascadeNativeError`` if a kernel gave up a bounded device-side wait since the last check
+        (its outputs are then invalid).  Synchronises the device.  Called by this class at the first layer of
+        every prompt, in ``wait_gathers()`` and wherever it has to synchronise anyway; a host that wants to
+        know right after a forward calls it itself."""
+        nat.check_status(device, "in an efficient_kascade prefill")
+
+    def exchange_description(self) -> str:
+        if self._shard is None or self._shard[1] == 1:
+            return "single GPU"
+        how = f" ({self._peer.how})" if self._peer is not None else ""
+        return {"nccl": "outputs all-gathered by NCCL",
+                "peer_store": "outputs stored into the peers by the kernel epilogue" + how,
+                "push": f"outputs pushed to the peers by the copy engines on side streams, {self._copies} buffers" + how,
+                }[self._exchange]
 
     def is_anchor(self, layer_idx: int) -> bool:
         return layer_idx == 0 or layer_idx in self.recompute_layers
@@ -213,6 +250,10 @@ class EfficientKascadeStrategy(Strategy):
             return out.unsqueeze(1), None
         if Lq != Lk:
             raise NotImplementedError("prefill expects the whole prompt (Lq == Lk); chunked prefill is not supported")
+        if layer == 0:
+            # a tile-prefill kernel that gave up a bounded wait leaves a status word behind, and every later
+            # one returns at entry while it is set: find out before the next prompt is queued behind it
+            self.check_status(query.device)
         q, k, v = self._token_major(query), self._token_major(key), self._token_major(value)
         if Lk <= 128:
             out = torch.empty(B, Lq, H, D, dtype=torch.float16, device=query.device)
@@ -235,6 +276,7 @@ class EfficientKascadeStrategy(Strategy):
             hidden = ~last if last.dtype == torch.bool else last != 0
             lead = torch.cumprod(hidden.to(torch.int32), dim=-1).sum(-1)          # length of the hidden prefix
             pads = [int(x) for x in lead.tolist()]
+            self.check_status(attention_mask.device)                              # the host has just synchronised
             self._pad_ref, self._pad_version = weakref.ref(attention_mask), attention_mask._version
             self._pads = pads if any(pads) else None
         return self._pads
@@ -303,15 +345,22 @@ class EfficientKascadeStrategy(Strategy):
         return self._publish(out)
 
     def _publish(self, out: torch.Tensor) -> torch.Tensor:
-        """Head-sharded runs: start the all-gather of this layer's per-head outputs (asynchronous, on
-        the communicator's stream) and return the local slice."""
+        """Head-sharded runs: start the exchange of this layer's per-head outputs (asynchronous) and return
+        the local slice."""
         if self._shard is None:
             return out
         if self._peer_store:
-            # the kernel has written this rank's heads into every rank's buffer; hand back the local slice
             full = self.gathered_out
-            h = full.shape[2] // self._shard[1]
-            return full[:, :, self._shard[0] * h:(self._shard[0] + 1) * h]
+            rank, world = self._shard
+            h = full.shape[2] // world
+            if self._exchange == "push":
+                # the kernel has written this rank's heads into its own buffer; the copy engines carry the
+                # slice to the peers while the next layers run
+                B, L, H, D = full.shape
+                c = self._peer_copy
+                nat.peer_push(self._push["plans"][c], full, rank * h * D * 2, H * D * 2, h * D * 2, B * L,
+                              self._push["ready"][c])
+            return full[:, :, rank * h:(rank + 1) * h]
         import torch.distributed as dist
         world = self._shard[1]
         self._pending = [w for w in self._pending if not w[0].is_completed()]
@@ -321,36 +370,54 @@ class EfficientKascadeStrategy(Strategy):
         self.gathered_out = buf
         return out
 
-    def wait_gathers(self):
-        """Block the current stream until every rank's outputs started so far have arrived."""
+    def wait_gathers(self, check_status: bool = False):
+        """Block the current stream until every rank's outputs started so far have arrived.  With
+        ``check_status`` the device status word is read too (that synchronises the host)."""
         if self._peer_store:
             if self._peer is not None:
                 import torch.distributed as dist
-                # stream-ordered after this rank's kernels; completes once every rank has got here
+                if self._push is not None:                 # this rank's own copies first
+                    nat.stream_wait_events([e for evs in self._push["done"] for e in evs])
+                # stream-ordered after this rank's kernels and copies; completes once every rank has got here
                 dist.all_reduce(self._scratch("peer_sync", (1,), torch.int32, self._peer.tensors[0].device))
-            return
-        for work, _, _ in self._pending:
-            work.wait()
-        self._pending = []
+        else:
+            for work, _, _ in self._pending:
+                work.wait()
+            self._pending = []
+        if check_status:
+            self.check_status()
 
     def _next_fanout(self, B: int, L: int, H: int, D: int, dev):
-        """Peer-store mode: the output buffers of this layer (two sets used in turn) as a kb200_out_fanout."""
+        """Peer-mapped output buffers: the [B, L, H_total, D] buffer of this layer (a ring of `copies`) as a
+        kb200_out_fanout — every rank's buffer in peer-store mode, this rank's own buffer in push mode."""
         rank, world = self._shard
         shape = (B, L, H * world, D)
         if self._peer is None or tuple(self._peer.tensors[0].shape) != shape:
             from .peer import alloc_peer_buffers
             try:
-                self._peer = alloc_peer_buffers(shape, torch.float16, dev, copies=2)
+                self._peer = alloc_peer_buffers(shape, torch.float16, dev, copies=self._copies)
             except RuntimeError as e:
                 # no peer mapping in this job (every rank gets here together): keep the sharded prefill
                 # running with the NCCL all-gather of the outputs
                 import warnings
-                warnings.warn(f"peer_store disabled, outputs are all-gathered with NCCL instead: {e}")
-                self._peer_store = False
+                warnings.warn(f"exchange '{self._exchange}' disabled, outputs are all-gathered with NCCL instead: {e}")
+                self._peer_store, self._exchange = False, "nccl"
                 return None
-            self._peer_fans = [nat.out_fanout(self._peer.fanout_pointers(c, rank), H * world, rank * H)
-                               for c in range(2)]
-        self._peer_copy ^= 1
+            n = self._copies
+            if self._exchange == "push":
+                self._peer_fans = [nat.out_fanout([self._peer.pointers[c][rank]], H * world, rank * H) for c in range(n)]
+                streams = [torch.cuda.Stream(device=dev) for _ in range(world - 1)]
+                done = [[torch.cuda.Event() for _ in range(world - 1)] for _ in range(n)]
+                ready = [torch.cuda.Event() for _ in range(n)]
+                plans = [nat.push_plan(self._peer.fanout_pointers(c, rank)[1:], streams, done[c]) for c in range(n)]
+                self._push = {"streams": streams, "done": done, "ready": ready, "plans": plans}
+            else:
+                self._peer_fans = [nat.out_fanout(self._peer.fanout_pointers(c, rank), H * world, rank * H)
+                                   for c in range(n)]
+        self._peer_copy = (self._peer_copy + 1) % self._copies
+        if self._push is not None:
+            # the copies that still read this buffer (layer n - copies) must have finished
+            nat.stream_wait_events(self._push["done"][self._peer_copy])
         self.gathered_out = self._peer.tensors[self._peer_copy]
         return self._peer_fans[self._peer_copy]
 
@@ -362,7 +429,9 @@ class EfficientKascadeStrategy(Strategy):
         kk = torch.clamp(torch.floor((self.k / 100) * lens), min=128.0)
         kk = torch.minimum(kk, lens) - self.tile_size
         kk = torch.where(lens <= 128, lens, kk).to(torch.int32)
-        kmax = max_len if max_len <= 128 else topk_budget(self.k, max_len, self.tile_size)
+        # rows are as long as the largest per-sequence budget: the reference formula at max_len, and the
+        # "at most 128 keys: attend to everything" rule for the short sequences of a mixed batch
+        kmax = max_len if max_len <= 128 else max(topk_budget(self.k, max_len, self.tile_size), 128)
         return kk, max(kmax, 1)
 
     def _decode(self, layer: int, q, kv, seq_lens, max_len: int, scaling, G: int, dense_only=False) -> torch.Tensor:

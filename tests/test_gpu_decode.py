@@ -202,3 +202,47 @@ def test_decode_step_replays_from_a_cuda_graph():
         assert torch.equal(outs[l], eager2[l]), f"layer {l}: graph replay did not pick up the new cache content"
     from kascade_b200 import _native as nat
     assert nat.read_status() == 0
+
+
+def test_mixed_batch_short_sequences_attend_to_everything():
+    """A ragged paged batch that mixes contexts of at most 128 keys with longer ones: the short sequences
+    attend to all their keys (strategies/EfficientKascadeStrategy.py:137-140 runs dense attention for them),
+    also when the budget of the longest sequence (10 % of 1000 -> 96 keys) is smaller than their length.
+    Every sequence must come out as when it is decoded alone."""
+    from kascade_b200 import EfficientKascadeStrategy
+    g = torch.Generator().manual_seed(42)
+    G, H, D, page = 2, 8, 128, 16
+    lens = [100, 128, 1000, 129]
+    B, Lmax = len(lens), max(lens)
+    hm = [[0, 1], [1, 0]]
+    scale = D ** -0.5
+    k = (torch.randn(B, G, Lmax, D, generator=g) / D ** 0.5).half().cuda()
+    v = torch.randn(B, G, Lmax, D, generator=g).half().cuda()
+    kc, vc, bt = paged_from_contiguous(k, v, page_size=page, seed=3)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    qs = [(torch.randn(B, H, D, generator=g) / D ** 0.5).half().cuda() for _ in range(2)]
+
+    def run(batch_rows):
+        strat = EfficientKascadeStrategy([0], "x/y", k=10, tile_size=32, head_mapping=hm, register=False)
+        sl = seq_lens[batch_rows].contiguous()
+        outs = [strat.paged_decode_forward(layer, qs[layer][batch_rows].contiguous(), kc, vc, bt[batch_rows].contiguous(),
+                                           sl, scale, int(sl.max().item())).clone() for layer in (0, 1)]
+        return outs, strat._dec_count.clone()
+
+    whole, counts = run(list(range(B)))
+    torch.cuda.synchronize()
+    assert counts[:, 0].tolist() == [100, 128, 96, 96], counts.tolist()
+    for b in range(B):
+        alone, _ = run([b])
+        for layer in (0, 1):
+            # (not bit-wise: the split count, hence the summation order, depends on the batch)
+            assert_close(whole[layer][b], alone[layer][0], atol=1e-3, rtol=5e-3,
+                         what=f"sequence {b} (len {lens[b]}), layer {layer}: in the batch vs alone")
+    # the short sequences equal dense attention over all their keys
+    for b in (0, 1):
+        kb, vb = k[b, :, :lens[b]].float(), v[b, :, :lens[b]].float()
+        qb = qs[1][b].float().view(G, 4, D)
+        # reuse layer 1 maps KV head g to the rows of anchor head hm[1][g] but reads its OWN keys: all of them here
+        p = torch.softmax(torch.einsum("ghd,gld->ghl", qb, kb) * scale, -1)
+        ref = torch.einsum("ghl,gld->ghd", p, vb).reshape(H, D)
+        assert_close(whole[1][b], ref, what=f"short sequence {b} against dense attention")

@@ -82,7 +82,7 @@ def test_shard_helpers():
 
 
 def test_workload_accounting():
-    from kascade_b200.workloads import DecodeWorkload, PrefillWorkload
+    from bench_workloads import DecodeWorkload, PrefillWorkload
     wl = PrefillWorkload()
     assert abs(wl.flops_dense() / 1e12 - 8.796) < 0.01
     assert abs(wl.flops_sparse() / 1e12 - 0.897) < 0.01
@@ -96,7 +96,7 @@ def test_ragged_decode_workload_accounting():
     """The long-reasoning decode configuration: 256 seeded contexts in [4096, 65536], batch-sharded round-robin;
     algorithmic bytes are sums over the sequences (budgets follow the reference's formula per sequence)."""
     from kascade_b200.strategy import topk_budget
-    from kascade_b200.workloads import DecodeWorkload
+    from bench_workloads import DecodeWorkload
     whole = DecodeWorkload.ragged()
     assert whole.batch == 256 and min(whole.contexts) >= 4096 and max(whole.contexts) <= 65536
     assert whole.context == max(whole.contexts)
@@ -111,7 +111,7 @@ def test_ragged_decode_workload_accounting():
 
 
 def test_long_prompt_workload_is_normalised():
-    from kascade_b200.workloads import PrefillWorkload, QWEN3_ANCHORS
+    from bench_workloads import PrefillWorkload, QWEN3_ANCHORS
     wl = PrefillWorkload(seq_len=256, layers=36, anchors=QWEN3_ANCHORS, qk_norm=True)
     q, k, v = wl.layer_inputs(3, "cpu")
     rms_q = q.float().pow(2).mean(-1).sqrt()
