@@ -122,6 +122,7 @@ struct PfShared {
   uint64_t bar_sfull[3], bar_pready[3], bar_odone[3], bar_x, bar_ofree, bar_lse[3], bar_sfree[2], bar_turn[2];
   uint32_t tmem;
   int give_up;
+  int abort;                                           // copy of the device status word taken at CTA start
   union {
     float xchg[2][2][128];                             // softmax modes: [m (with V: row reference) | l][warpgroup][row]
     float lse[2][2][128];                              // pool mode: lse2 of the tile's rows [warpgroup][tile parity]
@@ -206,12 +207,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
 
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // an earlier CTA or kernel gave up a bounded wait: do not queue up more waits behind it.  One thread
-  // reads the word and the whole CTA takes the same decision.
-  __shared__ int s_abort;
-  if (tid == 0) s_abort = *reinterpret_cast<volatile int*>(&g_status_word);
-  __syncthreads();
-  if (s_abort != 0) return;
   const uint32_t pad = (1024u - (smem_addr(smem_raw) & 1023u)) & 1023u;
   if (pad > (uint32_t)kPadAllowance) {                   // never seen; refuse rather than overrun
     if (tid == 0) atomicCAS(&g_status_word, 0, 90);
@@ -220,6 +215,11 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   uint8_t* smem = smem_raw + pad;
   constexpr int kTiles = 1 + kNK + (HAS_V ? kNV : 0);
   PfShared& sh = *reinterpret_cast<PfShared*>(smem + kTiles * kStageBytes);
+  // an earlier CTA or kernel gave up a bounded wait: do not queue up more waits behind it.  One thread
+  // reads the word and the whole CTA takes the same decision.
+  if (tid == 0) sh.abort = *reinterpret_cast<volatile int*>(&g_status_word);
+  __syncthreads();
+  if (sh.abort != 0) return;
   // modes without V: [3 streams][2][128] floats behind PfShared (partial row statistics / staged lse values)
   float* const xchg3 = reinterpret_cast<float*>(smem + kTiles * kStageBytes + 2560);
   uint64_t* bar_kfull = sh.bar_kfull;
