@@ -71,9 +71,7 @@ extern "C" int kb200_init(int device) {
   KB_CUDA(cudaGetDevice(&prev));
   KB_CUDA(cudaSetDevice(device));
   int rc = 0;
-  if (kb200::init_decode() != 0 || kb200::init_prefill() != 0 || kb200::init_selftest() != 0 ||
-      kb200::init_topk() != 0)
-    rc = -1;
+  if (kb200::init_decode() != 0 || kb200::init_prefill() != 0 || kb200::init_selftest() != 0) rc = -1;
   if (prev != device) cudaSetDevice(prev);
   if (rc != 0) return -1;
   kb200::g_sm_count[device] = prop.multiProcessorCount;

@@ -60,6 +60,5 @@ int sm_count();
 int init_decode();
 int init_prefill();
 int init_selftest();
-int init_topk();
 
 }  // namespace kb200

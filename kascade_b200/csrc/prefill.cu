@@ -110,6 +110,38 @@ __device__ __forceinline__ float ex2_fma(float x) {
   q = fmaf(q, f, 1.0f);
   return __uint_as_float(__float_as_uint(q) + (__float_as_uint(t) << 23));
 }
+// Two fp32 operations per instruction (sm_100: fma / add on register pairs) and the three-input maximum:
+// the softmax warps are bound by the number of instructions they issue, not by a single pipe, so every
+// per-element instruction that two elements can share is worth taking.  Results are those of the scalar
+// forms, bit for bit.
+__device__ __forceinline__ uint64_t pair_u(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pair_f(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpair_f(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -187,7 +219,7 @@ struct PfCfg {
   static constexpr int kIssuers = kIsPool ? 2 : 1;
   static constexpr int kThreads = (kGather || !kHasV) ? 512 : 384;
   static constexpr int kNK = kHasV ? 3 : kNKNoV;
-  static constexpr int kProducerArrivals = kGather ? 128 : 1;   // Q tile: all gather threads
+  static constexpr int kProducerArrivals = 1;                   // Q tile: one thread announces the TMA bytes
   static constexpr int kRingArrivals = kGather ? 96 : 1;        // K / V stage: three gather warps each
   static constexpr int kProducerWarp0 = kHasV ? 8 : 12;
   static constexpr int kMmaWarp = kGather ? 12 : (kHasV ? 9 : 13);
@@ -287,57 +319,69 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     uint64_t* bar_empty = is_v ? bar_vempty : bar_kempty;
     const uint32_t ring_s = is_v ? v_s : k_s;
     const int n_st = is_v ? kNV : kNK;
-    int st = 0, ph = 1, qn = 0;                          // ring position, parity of its "empty" phase; Q tiles loaded
+    int st = 0, ph = 1;                                  // ring position, parity of its "empty" phase
     bool ok = true;
     uint32_t soff[4];                                    // swizzled offset of (row 2 q + (lane >> 4), chunk lane & 15)
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) soff[q4] = tile_off(2 * q4 + (lane >> 4), lane & 15, 128);
-    for (int k = 0; k < n_rounds && ok; ++k) {
-      const int item = item_of(k);
-      if (item >= n_items) continue;
-      const TileItem it = decode_item<MODE>(p, item);
-      if (it.nb == 0) continue;
-      if (warp < 12) {
-        // warps 8-11 also load the Q tile; its buffer is free once the last Q.K^T of the previous
-        // tile has completed
-        const int ptid = tid - 8 * 32;
-        ok = mbar_wait(&sh.bar_qempty, (qn & 1) ^ 1, &give_up, 13);
-        if (!ok) break;
-        const __half* qb = p.q + (int64_t)it.b * p.q_sb;
-#pragma unroll 4
-        for (int i = 0; i < 16; ++i) {
-          const int id = i * 128 + ptid, row = id >> 4, c = id & 15;
-          const int tok = it.tile_start + (row >> 2), head = it.g * kHg + (row & 3);
-          const bool in = tok < p.L;                     // rows past the prompt are zero-filled
-          cp16_zfill(q_s + tile_off(row, c, 128),
-                     qb + (int64_t)(in ? tok : 0) * p.q_st + (int64_t)head * p.q_sh + c * 8, in ? 16u : 0u);
+    const int sub = lane >> 4;
+    const int tok_bytes = (int)((is_v ? p.v_st : p.k_st) * 2);   // host side checks that this fits
+    // What the gather needs to know of a tile.  The next tile's record is fetched (two dependent global
+    // loads: head map, row count) while the current tile is being gathered, and the index loads run two
+    // key blocks ahead ACROSS the tile boundary, so the warps do not stall at the start of a tile.
+    struct GatherTile {
+      const char* base;                                  // this lane's 16-byte chunk of key 0 of the (sequence, KV head)
+      const int32_t* idx;
+      int count, total, tile_start, nb;
+    };
+    auto fetch = [&](int k) -> GatherTile {
+      GatherTile g;
+      g.base = nullptr; g.idx = nullptr; g.count = 0; g.total = 0; g.tile_start = 0; g.nb = 0;
+      if (k < n_rounds) {
+        const int item = item_of(k);
+        if (item < n_items) {
+          const TileItem it = decode_item<MODE>(p, item);
+          g.base = reinterpret_cast<const char*>(
+              (is_v ? p.v + (int64_t)it.b * p.v_sb + (int64_t)it.g * p.v_sh
+                    : p.k + (int64_t)it.b * p.k_sb + (int64_t)it.g * p.k_sh) + (lane & 15) * 8);
+          g.idx = it.idx_row; g.count = it.count; g.total = it.total; g.tile_start = it.tile_start; g.nb = it.nb;
         }
-        cp_arrive_noinc(&sh.bar_q);
-        ++qn;
       }
-      // this lane copies 16-byte chunk c of the rows r_begin + 2 i + sub
-      const int c = lane & 15, sub = lane >> 4;
-      const char* base = reinterpret_cast<const char*>(
-          (is_v ? p.v + (int64_t)it.b * p.v_sb + (int64_t)it.g * p.v_sh
-                : p.k + (int64_t)it.b * p.k_sb + (int64_t)it.g * p.k_sh) + c * 8);
-      const int tok_bytes = (int)((is_v ? p.v_st : p.k_st) * 2);   // host side checks that this fits
-      // key positions of rows (r_begin + lane) and (r_begin + 32 + lane) of block j; the index loads
-      // run two blocks ahead of their use
-      auto load_key = [&](int j, int r) -> int {
-        const int s = j * 128 + r_begin + r * 32 + lane;
-        if (j >= it.nb || s >= it.total || (r == 1 && (!has_tail || lane >= 16))) return 0;
-        return s < it.count ? __ldg(it.idx_row + s) : it.tile_start + (s - it.count);
-      };
-      int a0 = load_key(0, 0), a1 = load_key(0, 1), b0 = load_key(1, 0), b1 = load_key(1, 1);
-      for (int j = 0; j < it.nb; ++j) {
+      return g;
+    };
+    // key position of row (r_begin + 32 r + lane) of key block j of tile g
+    auto key_of = [&](const GatherTile& g, int j, int r) -> int {
+      const int s = j * 128 + r_begin + r * 32 + lane;
+      if (s >= g.total || (r == 1 && (!has_tail || lane >= 16))) return 0;
+      return s < g.count ? __ldg(g.idx + s) : g.tile_start + (s - g.count);
+    };
+    GatherTile cur = fetch(0);
+    int a0 = 0, a1 = 0, b0 = 0, b1 = 0;                  // keys of the next block and of the one after it
+    bool a_ok = false, b_ok = false;
+    for (int k = 0; k < n_rounds && ok; ++k) {
+      const GatherTile nxt = fetch(k + 1);
+      // The next tile's index row comes from HBM (every row is read once): pull it into L2 now, a whole
+      // tile ahead, so that the index loads two blocks ahead of the copies find it there.  One warp per
+      // ring does it; a lane touches every 32nd 128-byte line.
+      if (part == 0 && nxt.idx != nullptr) {
+        const char* row_bytes = reinterpret_cast<const char*>(nxt.idx);
+        for (int off = lane * 128; off < nxt.count * 4; off += 32 * 128)
+          asm volatile("prefetch.global.L2 [%0];\n" ::"l"(row_bytes + off));
+      }
+      for (int j = 0; j < cur.nb; ++j) {
+        if (!a_ok) { a0 = key_of(cur, j, 0); a1 = key_of(cur, j, 1); }
         const int key0 = max(0, min(a0, p.L - 1)), key1 = max(0, min(a1, p.L - 1));
-        a0 = b0; a1 = b1;
-        b0 = load_key(j + 2, 0); b1 = load_key(j + 2, 1);
+        a0 = b0; a1 = b1; a_ok = b_ok;
+        const int j2 = j + 2;
+        if (j2 < cur.nb) { b0 = key_of(cur, j2, 0); b1 = key_of(cur, j2, 1); b_ok = true; }
+        else if (j2 - cur.nb < nxt.nb) { b0 = key_of(nxt, j2 - cur.nb, 0); b1 = key_of(nxt, j2 - cur.nb, 1); b_ok = true; }
+        else b_ok = false;
         ok = mbar_wait(&bar_empty[st], ph, &give_up, is_v ? 12 : 11);
         if (!ok) break;
         // Per copy: one shuffle (the row's key), one multiply-add (its address), one cp.async; the
         // swizzled destination of row (2 i + sub) repeats every four i, 1024 bytes further on.
         const uint32_t dst = ring_s + st * kStageBytes + r_begin * 128;
+        const char* base = cur.base;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int key = __shfl_sync(0xFFFFFFFFu, key0, i * 2 + sub);
@@ -353,6 +397,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         cp_arrive_noinc(&bar_full[st]);
         if (++st == n_st) { st = 0; ph ^= 1; }
       }
+      cur = nxt;
     }
     cp_wait_all();                                       // nothing of this CTA is in flight at teardown
   };
@@ -507,11 +552,36 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     // descriptors and ring positions are then warp-uniform values, which is what lets the tensor
     // core be fed at its own rate (a single diverged lane computing them per instruction cannot).
     const bool el = elect_one();
+    if (GATHER && el) tma_prefetch_desc(&tm_q);
     for (int k = 0; k < n_rounds && ok; ++k) {
       const int item = item_of(k);
       if (item >= n_items) continue;
       const TileItem it = decode_item<MODE>(p, item);
       if (it.nb == 0) continue;
+      if (GATHER) {
+        // Sparse mode: this warp also fetches the Q tile (two TMA boxes), as soon as the previous tile's
+        // last Q.K^T has completed; the next tile's Q is pulled into L2 meanwhile, so that its copy
+        // starts from there.
+        ok = mbar_wait(&sh.bar_qempty, (qn & 1) ^ 1, &give_up, 13);
+        if (!ok) break;
+        if (el) {
+          mbar_arrive_expect_tx(&sh.bar_q, kStageBytes);
+          tma_load_4d(q_s, &tm_q, 0, it.g * kHg, it.tile_start, it.b, &sh.bar_q);
+          tma_load_4d(q_s + kStageBytes / 2, &tm_q, 64, it.g * kHg, it.tile_start, it.b, &sh.bar_q);
+          if (k + 1 < n_rounds) {
+            const int nitem = item_of(k + 1);
+            if (nitem < n_items) {
+              const int per = p.group * p.T;
+              const int hi = nitem / per, lo = nitem - hi * per;
+              const int r = lo / p.group, bg = hi * p.group + (lo - r * p.group);
+              const int nb_ = bg / p.G, ng = bg - nb_ * p.G, nt = p.T - 1 - r;
+              tma_prefetch_4d(&tm_q, 0, ng * kHg, nt * kTile, nb_);
+              tma_prefetch_4d(&tm_q, 64, ng * kHg, nt * kTile, nb_);
+            }
+          }
+        }
+        __syncwarp();
+      }
       ok = mbar_wait(&sh.bar_q, qn & 1, &give_up, 21);
       if (!ok) break;
       ++qn;
@@ -617,10 +687,20 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     const float* ref_other = &sh.xchg[0][wg ^ 1][row];
     int done_mine = 0, done_other = 0, tiles_done = 0;        // blocks finished per stream, tiles finished
     bool ok = true;
+    // sparse mode: the record of a tile (two dependent global loads) is fetched one tile ahead
+    TileItem it_next;
+    if (GATHER) it_next = decode_item<MODE>(p, min(item_of(0), n_items - 1));
     for (int k = 0; k < n_rounds && ok; ++k) {
       const int item = item_of(k);
-      if (item >= n_items) continue;
-      const TileItem it = decode_item<MODE>(p, item);
+      TileItem it;
+      if (GATHER) {
+        it = it_next;
+        if (k + 1 < n_rounds) it_next = decode_item<MODE>(p, min(item_of(k + 1), n_items - 1));
+        if (item >= n_items) continue;
+      } else {
+        if (item >= n_items) continue;
+        it = decode_item<MODE>(p, item);
+      }
       if (it.nb == 0) continue;
       const int tok = it.tile_start + q_local;
       const int off = GATHER ? it.count : it.tile_start;   // slot - off = key position inside the tile
@@ -651,14 +731,27 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
               if ((c0 + part * 32 + i) > q_local) sr[part][i] = 0xFF800000u;     // -inf
         }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        if (GATHER) {
 #pragma unroll
-        for (int part = 0; part < 4; ++part) {
+          for (int part = 0; part < 4; ++part) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(sr[part][i]));
-            mx1 = fmaxf(mx1, __uint_as_float(sr[part][i + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(sr[part][i + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(sr[part][i + 3]));
+            for (int i = 0; i < 32; i += 8) {
+              mx0 = max3(mx0, __uint_as_float(sr[part][i]), __uint_as_float(sr[part][i + 1]));
+              mx1 = max3(mx1, __uint_as_float(sr[part][i + 2]), __uint_as_float(sr[part][i + 3]));
+              mx2 = max3(mx2, __uint_as_float(sr[part][i + 4]), __uint_as_float(sr[part][i + 5]));
+              mx3 = max3(mx3, __uint_as_float(sr[part][i + 6]), __uint_as_float(sr[part][i + 7]));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int part = 0; part < 4; ++part) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              mx0 = fmaxf(mx0, __uint_as_float(sr[part][i]));
+              mx1 = fmaxf(mx1, __uint_as_float(sr[part][i + 1]));
+              mx2 = fmaxf(mx2, __uint_as_float(sr[part][i + 2]));
+              mx3 = fmaxf(mx3, __uint_as_float(sr[part][i + 3]));
+            }
           }
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale2;
@@ -682,20 +775,46 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
           if (!ok) break;
         }
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        if (GATHER) {
+          // two fp32 operations per instruction: in the sparse mode the softmax warps share their issue
+          // slots with six gather warps and every instruction saved shows (-4 %); in the dense mode, which
+          // runs on the power cap, the same code was 2-3 % slower than the scalar form
+          uint64_t s01 = 0ull, s23 = 0ull;                  // four partial row sums, two per register pair
+          const uint64_t scale_2 = pair_f(p.scale2, p.scale2), nref_2 = pair_f(-ref, -ref);
 #pragma unroll
-        for (int part = 0; part < 4; ++part) {             // 32 keys -> 16 packed P columns
-          uint32_t pr[16];
+          for (int part = 0; part < 4; ++part) {           // 32 keys -> 16 packed P columns
+            uint32_t pr[16];
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            float a0 = ex2(fmaf(__uint_as_float(sr[part][2 * i]), p.scale2, -ref));
-            float a1 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 1]), p.scale2, -ref));
-            float a2 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 2]), p.scale2, -ref));
-            float a3 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 3]), p.scale2, -ref));
-            s0 += a0; s1 += a1; s2 += a2; s3 += a3;
-            pr[i] = pack2(a0, a1);
-            pr[i + 1] = pack2(a2, a3);
+            for (int i = 0; i < 16; i += 2) {
+              float a0, a1, a2, a3;
+              unpair_f(fma2(pair_u(sr[part][2 * i], sr[part][2 * i + 1]), scale_2, nref_2), a0, a1);
+              unpair_f(fma2(pair_u(sr[part][2 * i + 2], sr[part][2 * i + 3]), scale_2, nref_2), a2, a3);
+              a0 = ex2(a0); a1 = ex2(a1); a2 = ex2(a2); a3 = ex2(a3);
+              s01 = add2(s01, pair_f(a0, a1));
+              s23 = add2(s23, pair_f(a2, a3));
+              pr[i] = pack2(a0, a1);
+              pr[i + 1] = pack2(a2, a3);
+            }
+            tmem_st16(tp + part * 16, pr);                 // P columns [part*16, +16) = keys [part*32, +32)
           }
-          tmem_st16(tp + part * 16, pr);                   // P columns [part*16, +16) = keys [part*32, +32)
+          unpair_f(s01, s0, s1);
+          unpair_f(s23, s2, s3);
+        } else {
+#pragma unroll
+          for (int part = 0; part < 4; ++part) {           // 32 keys -> 16 packed P columns
+            uint32_t pr[16];
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              float a0 = ex2(fmaf(__uint_as_float(sr[part][2 * i]), p.scale2, -ref));
+              float a1 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 1]), p.scale2, -ref));
+              float a2 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 2]), p.scale2, -ref));
+              float a3 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 3]), p.scale2, -ref));
+              s0 += a0; s1 += a1; s2 += a2; s3 += a3;
+              pr[i] = pack2(a0, a1);
+              pr[i + 1] = pack2(a2, a3);
+            }
+            tmem_st16(tp + part * 16, pr);                 // P columns [part*16, +16) = keys [part*32, +32)
+          }
         }
         // this thread's part of the row sum moves to the block's reference
         const float beta = (m_l == -INFINITY) ? 0.f : ex2(m_l - ref);
@@ -744,10 +863,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       tc_fence_after();
       const float inv = 1.0f / l_tot;
       // this warpgroup stores output columns [wg*64, +64) of its rows
-      // With KV heads sharded over GPUs the rows go straight into every GPU's [B, L, H_out, D] buffer
-      // (plain peer stores over NVLink: the all-gather of the outputs is this epilogue).  A thread
-      // holds 128 bytes of ITS row; eight neighbouring lanes transpose their eight 16-byte chunks so
-      // that every store instruction writes 128 contiguous bytes per row instead of 16.
       uint4 w[8];
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
@@ -762,23 +877,32 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
           w[part * 4 + e].w = pack2(__uint_as_float(oa[e * 8 + 6]) * inv, __uint_as_float(oa[e * 8 + 7]) * inv);
         }
       }
-#pragma unroll
-      for (int bit = 1; bit < 8; bit <<= 1) {
-        const bool up = (lane & bit) != 0;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          if (c & bit) continue;
-          const uint4 send = up ? w[c] : w[c | bit];
-          uint4 recv;
-          recv.x = __shfl_xor_sync(0xFFFFFFFFu, send.x, bit);
-          recv.y = __shfl_xor_sync(0xFFFFFFFFu, send.y, bit);
-          recv.z = __shfl_xor_sync(0xFFFFFFFFu, send.z, bit);
-          recv.w = __shfl_xor_sync(0xFFFFFFFFu, send.w, bit);
-          if (up) w[c] = recv; else w[c | bit] = recv;
-        }
-      }
-      // now w[j] is chunk (lane & 7) of row (row & ~7) + j
+      // O and the exchange buffer have been read: the next tile's first P.V may overwrite the accumulator
+      // while this tile's rows are still on their way out
+      tc_fence_before();
+      mbar_arrive(&sh.bar_ofree);
       {
+        // A thread holds 128 bytes of ITS row; eight neighbouring lanes transpose their eight 16-byte
+        // chunks so that every store instruction writes 128 contiguous bytes per row instead of 16 (storing
+        // the rows directly, 32 different lines per instruction, made the dense pass 5 % slower).  With KV
+        // heads sharded over GPUs and n_fan > 1 the rows also go straight into the peers' [B, L, H_out, D]
+        // buffers (plain peer stores over NVLink: the all-gather of the outputs is then this epilogue).
+#pragma unroll
+        for (int bit = 1; bit < 8; bit <<= 1) {
+          const bool up = (lane & bit) != 0;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            if (c & bit) continue;
+            const uint4 send = up ? w[c] : w[c | bit];
+            uint4 recv;
+            recv.x = __shfl_xor_sync(0xFFFFFFFFu, send.x, bit);
+            recv.y = __shfl_xor_sync(0xFFFFFFFFu, send.y, bit);
+            recv.z = __shfl_xor_sync(0xFFFFFFFFu, send.z, bit);
+            recv.w = __shfl_xor_sync(0xFFFFFFFFu, send.w, bit);
+            if (up) w[c] = recv; else w[c | bit] = recv;
+          }
+        }
+        // now w[j] is chunk (lane & 7) of row (row & ~7) + j
         const int row0 = row & ~7, chunk = lane & 7;
         int64_t offs[8];
 #pragma unroll
@@ -797,9 +921,6 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       }
       if (wg == 0 && p.lse2 && tok < p.L)
         p.lse2[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)] = m_tot + log2f(l_tot);
-      // O and the exchange buffer have been read
-      tc_fence_before();
-      mbar_arrive(&sh.bar_ofree);
       ++tiles_done;
     }
   };
@@ -1349,9 +1470,10 @@ static int prefill_sparse_impl(const kb200_act_layout* q, const kb200_act_layout
   p.lse2 = lse2;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
   p.group = pick_group(batch, num_kv_heads, seq_len, true);
-  CUtensorMap none{};                                    // the gather path uses no tensor maps
+  CUtensorMap tq, none{};                                // Q tiles by TMA; the K / V rows are gathered without maps
+  if (make_act_map(&tq, p.q, p.q_sb, p.q_st, p.q_sh, num_q_heads, seq_len, batch, kHg, kTile, "q") != 0) return -1;
   dim3 grid(persistent_grid(p));
-  tile_prefill_kernel<kSparse><<<grid, PfCfg<kSparse>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, none, none, none);
+  tile_prefill_kernel<kSparse><<<grid, PfCfg<kSparse>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, tq, none, none);
   KB_CHECK_LAUNCH("tile_prefill_kernel<sparse>");
   return 0;
 }

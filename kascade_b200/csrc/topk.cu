@@ -1,21 +1,10 @@
 // Exact per-row Top-k by radix select (one CTA per row).
 //
 // Replaces the torch.topk call sites of the reference's efficient path
-// (strategies/EfficientKascadeStrategy.py:82,90,111).
-//
-// topk_row_kernel (rows of up to kRowCap candidates, the prefill and decode shapes up to 32 768 keys): the
-// row is read from global memory ONCE into shared memory as order-preserving 32-bit keys, with its
-// minimum and maximum taken on the way.  The k-th largest key is then found by range refinement: a
-// 2048-bin histogram over the keys still in range [lo, hi], binned by (key - lo) >> shift with the
-// shift chosen from the range, so that the first pass already spreads the row over all bins whatever
-// its exponent (post-softmax scores of a row share their leading bits; fixed digit positions would put
-// them all into a handful of bins and serialise the shared-memory atomics).  The bin that holds the
-// k-th key becomes the new range; at most three passes end with a single key value.  A last pass over
-// the shared-memory copy compacts the selected positions in ascending index order, taking ties at the
-// threshold from the lowest index upwards.  HBM traffic: the valid part of the score matrix, once.
-//
-// topk_select_kernel (longer rows): the same selection with the row re-read from global memory (L2)
-// in every pass: three fixed 11/11/10-bit histogram passes and the compaction pass.
+// (strategies/EfficientKascadeStrategy.py:82,90,111).  The row is read from global memory (L2 after
+// the first pass): three 11/11/10-bit histogram passes find the k-th largest key exactly, a fourth pass
+// compacts the selected positions in ascending index order, taking ties at the threshold from the
+// lowest index upwards.
 #include "common.cuh"
 
 namespace kb200 {
@@ -169,171 +158,6 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
   }
 }
 
-// ---- rows that fit shared memory ------------------------------------------------------------------
-constexpr int kRowThreads = 1024;
-constexpr int kRowCap = 32768;                            // candidates per row held in shared memory (128 KB)
-constexpr int kRowSmem = kRowCap * 4 + kTopkBins * 4;
-
-__global__ void __launch_bounds__(kRowThreads, 1)
-topk_row_kernel(const float* __restrict__ scores, int64_t row_stride, int n_cols,
-                const int32_t* __restrict__ n_valid, const int32_t* __restrict__ k_row, int k_max,
-                int32_t* __restrict__ out_idx, int64_t idx_stride, int32_t* __restrict__ out_count, int64_t rows) {
-  extern __shared__ __align__(16) uint32_t row_keys[];     // [kRowCap] keys, then [kTopkBins] histogram
-  uint32_t* hist = row_keys + kRowCap;
-  __shared__ uint32_t warp_a[kRowThreads / 32], warp_b[kRowThreads / 32];
-  __shared__ uint32_t sh_bin, sh_remaining;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-
-  // longest rows first (rows are ordered by ascending tile within a head: walk them backwards)
-  for (int64_t rr = blockIdx.x; rr < rows; rr += gridDim.x) {
-    const int64_t row = rows - 1 - rr;
-    int n = n_valid ? n_valid[row] : n_cols;
-    n = max(0, min(n, n_cols));
-    int k = k_row ? min(k_row[row], k_max) : k_max;
-    k = max(0, min(k, n));
-    int32_t* out = out_idx + row * idx_stride;
-    if (tid == 0 && out_count) out_count[row] = k;
-    if (k == 0) continue;
-    if (k == n) {                                          // every candidate is selected
-      for (int i = tid; i < n; i += kRowThreads) out[i] = i;
-      continue;
-    }
-    // ---- one read of the row: keys to shared memory, minimum and maximum on the way ----------------
-    const float4* row4 = reinterpret_cast<const float4*>(scores + row * row_stride);
-    const int n4 = (n + 3) >> 2;
-    uint32_t kmin = 0xFFFFFFFFu, kmax = 0u;
-    for (int i4 = tid; i4 < n4; i4 += kRowThreads) {
-      const float4 x = __ldg(row4 + i4);
-      uint4 u = make_uint4(float_key(x.x), float_key(x.y), float_key(x.z), float_key(x.w));
-      const int base = i4 * 4;
-      // entries past n (the row's last, partial group of four) never compete: smallest key
-      if (base + 1 >= n) u.y = 0u;
-      if (base + 2 >= n) u.z = 0u;
-      if (base + 3 >= n) u.w = 0u;
-      reinterpret_cast<uint4*>(row_keys)[i4] = u;
-      kmax = max(max(kmax, u.x), max(max(u.y, u.z), u.w));
-      kmin = min(kmin, u.x);
-      if (base + 1 < n) kmin = min(kmin, u.y);
-      if (base + 2 < n) kmin = min(kmin, u.z);
-      if (base + 3 < n) kmin = min(kmin, u.w);
-    }
-    kmin = __reduce_min_sync(0xFFFFFFFFu, kmin);
-    kmax = __reduce_max_sync(0xFFFFFFFFu, kmax);
-    if (lane == 0) { warp_a[warp] = kmin; warp_b[warp] = kmax; }
-    __syncthreads();
-    {
-      uint32_t a = warp_a[lane], b = warp_b[lane];         // 32 warps: one value per lane
-      kmin = __reduce_min_sync(0xFFFFFFFFu, a);
-      kmax = __reduce_max_sync(0xFFFFFFFFu, b);
-    }
-    __syncthreads();                                       // warp_a / warp_b are reused below
-
-    // ---- range refinement: [lo, hi] always contains the k-th largest key ---------------------------
-    // `remaining` = rank of the wanted key among the keys <= hi, counted from the top
-    uint32_t lo = kmin, hi = kmax, remaining = (uint32_t)k;
-    const int iters = (n4 + kRowThreads - 1) / kRowThreads;
-#pragma unroll 1
-    for (int pass = 0; pass < 4 && lo != hi; ++pass) {
-      const uint32_t range = hi - lo;                      // >= 1
-      const int bits = 32 - __clz(range);
-      const int shift = bits > 11 ? bits - 11 : 0;         // (range >> shift) < 2048
-      for (int i = tid; i < kTopkBins; i += kRowThreads) hist[i] = 0;
-      __syncthreads();
-      for (int it = 0; it < iters; ++it) {
-        const int i4 = it * kRowThreads + tid;
-        if (i4 < n4) {
-          const uint4 u = reinterpret_cast<const uint4*>(row_keys)[i4];
-          const uint32_t us[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (us[e] >= lo && us[e] <= hi && i4 * 4 + e < n) atomicAdd(&hist[(us[e] - lo) >> shift], 1u);
-        }
-      }
-      __syncthreads();
-      // bin d with count(> d) < remaining <= count(>= d): suffix sums over 2 bins per thread
-      {
-        const uint32_t c0 = hist[tid * 2], c1 = hist[tid * 2 + 1], ssum = c0 + c1;
-        uint32_t suf = ssum;                               // sum over lanes >= lane of this warp
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-          const uint32_t v = __shfl_down_sync(0xFFFFFFFFu, suf, off);
-          if (lane + off < 32) suf += v;
-        }
-        if (lane == 0) warp_a[warp] = suf;
-        __syncthreads();
-        uint32_t higher = 0;
-#pragma unroll
-        for (int w = 0; w < kRowThreads / 32; ++w) higher += w > warp ? warp_a[w] : 0u;
-        const uint32_t above = higher + suf - ssum;        // keys in bins of higher threads
-        if (above < remaining && remaining <= above + ssum) {
-          if (remaining <= above + c1) { sh_bin = (uint32_t)(tid * 2 + 1); sh_remaining = remaining - above; }
-          else { sh_bin = (uint32_t)(tid * 2); sh_remaining = remaining - above - c1; }
-        }
-      }
-      __syncthreads();
-      const uint32_t d = sh_bin;
-      remaining = sh_remaining;
-      const uint32_t new_lo = lo + (d << shift);
-      const uint64_t top = (uint64_t)new_lo + ((1ull << shift) - 1ull);
-      hi = top < (uint64_t)hi ? (uint32_t)top : hi;
-      lo = new_lo;
-      __syncthreads();                                     // sh_bin / warp_a are rewritten by the next pass
-    }
-    // lo == hi = key of the k-th largest score; `remaining` keys equal to it are still wanted
-    const uint32_t tau = lo, need_eq = remaining;
-    uint32_t gt_total = 0, eq_total = 0;
-    for (int it = 0; it < iters; ++it) {
-      const int i4 = it * kRowThreads + tid;
-      const bool in = i4 < n4;
-      uint4 u = make_uint4(0u, 0u, 0u, 0u);
-      if (in) u = reinterpret_cast<const uint4*>(row_keys)[i4];
-      const uint32_t us[4] = {u.x, u.y, u.z, u.w};
-      uint32_t gt[4], eq[4], packed = 0;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const bool ok = in && (i4 * 4 + e < n);
-        gt[e] = ok && (us[e] > tau);
-        eq[e] = ok && (us[e] == tau);
-        packed += gt[e] + (eq[e] << 16);
-      }
-      // block-wide exclusive scan of (eq << 16 | gt) in index order (at most 4096 per step: no carry)
-      uint32_t incl = packed;
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, off);
-        if (lane >= off) incl += v;
-      }
-      if (lane == 31) warp_b[warp] = incl;
-      __syncthreads();
-      uint32_t base = 0, total = 0;
-#pragma unroll
-      for (int w = 0; w < kRowThreads / 32; ++w) {
-        const uint32_t v = warp_b[w];
-        if (w < warp) base += v;
-        total += v;
-      }
-      const uint32_t excl = base + incl - packed;
-      uint32_t gt_before = gt_total + (excl & 0xFFFFu);
-      uint32_t eq_before = eq_total + (excl >> 16);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const bool sel = gt[e] || (eq[e] && eq_before < need_eq);
-        if (sel) out[gt_before + min(eq_before, need_eq)] = i4 * 4 + e;
-        gt_before += gt[e];
-        eq_before += eq[e];
-      }
-      gt_total += total & 0xFFFFu;
-      eq_total += total >> 16;
-      __syncthreads();
-    }
-  }
-}
-
-int init_topk() {
-  KB_CUDA(cudaFuncSetAttribute(topk_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRowSmem));
-  return 0;
-}
-
 __global__ void prefill_budgets_kernel(int32_t* n_valid, int32_t* k_row, int num_tiles, int total,
                                        int k_max, float pct, int rolling) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -367,13 +191,6 @@ extern "C" int kb200_topk_select(const float* scores, int64_t row_stride, int n_
   KB_REQUIRE(idx_stride >= (int64_t)k_max, "topk_select: idx_stride (%lld) smaller than k_max (%d)",
              (long long)idx_stride, k_max);
   if (rows == 0) return 0;
-  if (n_cols <= kRowCap) {                               // the row fits shared memory: one read of the scores
-    const int64_t grid = rows < (int64_t)sm_count() ? rows : (int64_t)sm_count();
-    topk_row_kernel<<<(unsigned)grid, kRowThreads, kRowSmem, (cudaStream_t)stream>>>(
-        scores, row_stride, n_cols, n_valid, k_row, k_max, out_idx, idx_stride, out_count, rows);
-    KB_CHECK_LAUNCH("topk_row_kernel");
-    return 0;
-  }
   int64_t grid = rows < (int64_t)sm_count() * 64 ? rows : (int64_t)sm_count() * 64;
   topk_select_kernel<<<(unsigned)grid, kTopkThreads, 0, (cudaStream_t)stream>>>(
       scores, row_stride, n_cols, n_valid, k_row, k_max, out_idx, idx_stride, out_count, rows);
