@@ -373,6 +373,77 @@ def bench_decode(args, dev, world, peaks, batch=None, ragged=False, rank=0):
     return decode
 
 
+def bench_decoder_generate(args, dev, world, rank):
+    """The long-reasoning decode as a whole decoder: a random-init Llama-3.1-8B-architecture stack (32 layers, hidden
+    4096, SwiGLU 14336, 32 / 8 heads, RoPE theta 500000, fp16, weights N(0, 0.02)) generates `--gen-tokens` tokens for
+    256 sequences with contexts uniform in [4096, 65536] (batch-sharded over the ranks, weights replicated, no
+    collective).  Per layer the step calls kb200_kv_write (RoPE + paged append) and the Kascade paged decode; the
+    dense layers are torch GEMMs.  One step is captured into a CUDA graph and replayed.  The KV caches of 256 such
+    sequences for 32 layers (1.2 TB) do not fit one GPU, so `distinct_layer_caches` caches are cycled over the
+    layers (the bytes every layer reads are those of a real run; what it appends lands in a shared cache)."""
+    import torch.distributed as dist
+    from bench_decoder import DecoderConfig, KascadeLlamaDecoder
+    from bench_workloads import DecodeWorkload
+    gen = int(args.gen_tokens)
+    cfg = DecoderConfig()
+    dw = DecodeWorkload.ragged(rank=rank, world=world, distinct_caches=2, reserve=gen)
+    model = KascadeLlamaDecoder(cfg, dev, dw.head_mapping())
+    caches = [dw.make_cache(i, dev) for i in range(dw.distinct_caches)]
+    block_table = caches[0][2]                                    # one page table: the caches share their page layout
+    caches = [(kc, vc) for kc, vc, _ in caches]
+    lens0 = torch.tensor(dw.seq_lens(), dtype=torch.int32, device=dev)
+    seq_lens = lens0.clone()
+    max_len = dw.context + gen
+    tokens = torch.randint(0, cfg.vocab, (dw.batch,), device=dev, generator=torch.Generator(device=dev).manual_seed(11))
+    model._qkv_cache = [None] * cfg.layers
+
+    def step():
+        nxt = model.step(tokens, lambda l: caches[l % len(caches)], block_table, seq_lens, max_len)
+        tokens.copy_(nxt)
+        seq_lens.add_(1)
+
+    for _ in range(3):                                            # warm-up: every scratch buffer of a step exists afterwards
+        step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    seq_lens.copy_(lens0)
+    for _ in range(2):
+        graph.replay()
+    seq_lens.copy_(lens0)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t_ms = torch.tensor([_time_cuda(lambda i: graph.replay(), gen) * gen], device=dev)
+    if world > 1:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(t_ms.item())
+    # the library's part of a step alone: the same kernels on the q / k / v of the last step
+    seq_lens.copy_(lens0)
+    agraph = torch.cuda.CUDAGraph()
+    model.step(tokens, lambda l: caches[l % len(caches)], block_table, seq_lens, max_len, attention_only=True)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(agraph):
+        model.step(tokens, lambda l: caches[l % len(caches)], block_table, seq_lens, max_len, attention_only=True)
+    agraph.replay()
+    t_att = torch.tensor([_time_cuda(lambda i: agraph.replay(), 16)], device=dev)
+    if world > 1:
+        dist.all_reduce(t_att, op=dist.ReduceOp.MAX)
+    batch_total = 256
+    res = {"tokens_per_s": batch_total * gen / (total_ms * 1e-3), "generated_tokens_per_sequence": gen,
+           "ms_per_token_step": total_ms / gen, "attention_us_per_step": float(t_att.item()) * 1e3,
+           "attention_share": float(t_att.item()) / (total_ms / gen), "batch_total": batch_total, "batch_per_gpu": dw.batch,
+           "contexts": f"uniform {min(dw.contexts)}..{max(dw.contexts)} on this rank, seed 0", "cuda_graph": True,
+           "model": "random-init Llama-3.1-8B architecture: 32 layers, hidden 4096, SwiGLU 14336, 32/8 heads, RoPE theta "
+                    "500000, vocab 128256 (tied), fp16, weights N(0, 0.02)",
+           "per_layer": "torch GEMMs (qkv, o, gate/up, down) + kb200_kv_write (RoPE, paged append) + Kascade paged decode",
+           "distinct_layer_caches": dw.distinct_caches, "parallelism": f"batch shard x{world}, weights replicated, no collective"}
+    del caches, model
+    torch.cuda.empty_cache()
+    return res
+
+
 # ------------------------------------------------------------------------------------------------
 def bench_kv_write(dev, peaks, seq_len=32768, H=32, G=8, D=128, page=16):
     """KV-cache write path (RoPE of Q and K, paged append of K and V) for one layer of a prefill at seq_len
@@ -429,14 +500,17 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-dense", action="store_true")
-    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "peer_store", "nccl"],
+    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "peer_store", "multicast", "nccl", "local"],
                     help="N > 1: how the per-head outputs reach the other GPUs: copy-engine pushes on side streams "
-                         "(push), stores from the kernel epilogue (peer_store), NCCL all-gather (nccl); auto = "
-                         "peer_store on 2 GPUs, push from 4 on")
+                         "(push), stores from the kernel epilogue to every peer (peer_store) or once to an NVLink multicast "
+                         "address (multicast), NCCL all-gather (nccl); auto = peer_store on 2 GPUs, multicast from 4 on; local = measurement aid: like push with the copies left "
+                         "out (every rank keeps only its own heads), which gives the step time without any output exchange")
     ap.add_argument("--no-peer-store", action="store_true", help="same as --exchange nccl")
     ap.add_argument("--wait-every-layer", action="store_true",
                     help="N > 1: synchronise the GPUs after every layer (what a consumer of each layer's gathered "
                          "outputs needs) instead of once per step")
+    ap.add_argument("--skip-decoder", action="store_true", help="--config 5: attention only, without the decoder around it")
+    ap.add_argument("--gen-tokens", type=int, default=128, help="--config 5: tokens generated per sequence")
     ap.add_argument("--decode-only", action="store_true", help="profiling aid: run only the decode configuration")
     ap.add_argument("--kv-write-only", action="store_true", help="profiling aid: run only the KV-cache write path")
     ap.add_argument("--decode-batch", type=int, default=None, help="profiling aid: decode batch (default 64)")
@@ -470,16 +544,23 @@ def main():
         return
     if args.config == 5:
         decode = bench_decode(args, dev, world, peaks, ragged=True, rank=rank)
+        decoder = None if args.skip_decoder else bench_decoder_generate(args, dev, world, rank)
         if rank == 0:
-            print(json.dumps({"metric": "decode attention us/step, 256 sequences with contexts 4096..65536, 10% top-k",
-                              "value": decode["us_per_step"], "unit": "us", "n_gpus": world, "steps": args.steps,
-                              "warmup": args.warmup, "ms_per_step": decode["us_per_step"] / 1e3,
-                              "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
-                              "data": "synthetic",
-                              "config": {"workload": "llama31_8b_decode_attention_ragged_b256", "parallelism":
-                                         f"batch shard x{world}", "cache_policy": "caches larger than L2"},
-                              "gpu_launches": decode["gpu_launches"], "device_status": nat.read_status(),
-                              "decode": decode}), flush=True)
+            line = {"metric": "long-reasoning decode: tokens/s of a Llama-3.1-8B-architecture decoder and attention us/step, "
+                              "256 sequences with contexts 4096..65536, 10% top-k",
+                    "value": decode["us_per_step"], "unit": "us", "n_gpus": world, "steps": args.steps,
+                    "warmup": args.warmup, "ms_per_step": decode["us_per_step"] / 1e3,
+                    "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+                    "data": "synthetic",
+                    "config": {"workload": "llama31_8b_decode_attention_ragged_b256", "parallelism":
+                               f"batch shard x{world}", "cache_policy": "caches larger than L2"},
+                    "gpu_launches": decode["gpu_launches"], "device_status": nat.read_status(),
+                    "decode": decode}
+            if decoder:
+                line["decoder"] = decoder
+                line["tokens_per_s"] = decoder["tokens_per_s"]
+                line["attention_us_per_step"] = decoder["attention_us_per_step"]
+            print(json.dumps(line), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -497,8 +578,13 @@ def main():
     my_heads = list(range(rank * gpr, (rank + 1) * gpr))
     exchange = "nccl" if args.no_peer_store else args.exchange
     if exchange == "auto":
-        exchange = "peer_store" if world == 2 else "push"
+        exchange = "peer_store" if world == 2 else "multicast"
+    local_only = exchange == "local"
+    if local_only:
+        exchange = "push"
     sharded_check = sharded_self_check(rank, world, dev, exchange) if world > 1 else None
+    if local_only:
+        nat.peer_push = lambda *a, **k: None                       # the copies are left out on purpose (see --exchange)
     strat = EfficientKascadeStrategy(list(wl.anchors), "synthetic/llama31-8b-shape", k=wl.pct, tile_size=wl.tile,
                                      rolling_prefill=wl.rolling, head_mapping=wl.head_mapping(), register=False,
                                      shard=(rank, world) if world > 1 else None, exchange=exchange)
@@ -686,7 +772,8 @@ def main():
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": prefill_config(wl, world),
-                "exchange": (None if world == 1 else strat.exchange_description()),
+                "exchange": (None if world == 1 else "NONE (measurement aid): outputs stay on their rank" if local_only
+                             else strat.exchange_description()),
                 "gpu_sync": (None if world == 1 else "after every layer" if args.wait_every_layer else
                              "once per step (the layers' outputs are not consumed in between)"),
                 "sharded_check": sharded_check,

@@ -107,6 +107,7 @@ class DecodeWorkload:
     page: int = 16
     distinct_caches: int = 4          # layer caches held in HBM and cycled over the 32 layers
     contexts: Sequence[int] = None    # per-sequence contexts (ragged batch); None: every sequence at `context`
+    reserve: int = 0                  # tokens of page room behind every sequence (for tokens generated later)
 
     def seq_lens(self) -> List[int]:
         return [self.context] * self.batch if self.contexts is None else [int(c) for c in self.contexts]
@@ -125,8 +126,8 @@ class DecodeWorkload:
     def make_cache(self, idx: int, device):
         """(k_cache, v_cache [pages, 16, G, D] fp16, block_table [B, pages_per_seq] int32)."""
         gen = torch.Generator(device=device).manual_seed(1000 + idx)
-        pps = -(-self.context // self.page)
-        per_seq = [-(-n // self.page) for n in self.seq_lens()]
+        pps = -(-(self.context + self.reserve) // self.page)
+        per_seq = [-(-(n + self.reserve) // self.page) for n in self.seq_lens()]
         n_pages = sum(per_seq)
         shape = (n_pages, self.page, self.G, self.D)
         k = torch.empty(shape, dtype=torch.float16, device=device)

@@ -219,6 +219,43 @@ int kb200_prefill_sparse(const kb200_act_layout* q, const kb200_act_layout* k,
                          void* out, float* lse2, int batch, int seq_len, int num_q_heads,
                          int num_kv_heads, int idx_kv_heads, void* stream);
 
+/* ---- ragged batches in one launch ---------------------------------------------------------------
+ * A batch whose prompts differ in length (left- or right-padded by the tokenizer, or simply of different
+ * lengths inside equally sized slots) runs through the same persistent kernels in ONE launch per kernel:
+ * sequence b occupies rows seq_start[b] .. seq_start[b] + seq_len[b] - 1 of its slot of max_len rows
+ * (element (b, seq_start[b] + token, head, d) of every activation, row seq_start[b] + token of `out`); tiles
+ * beyond a sequence's end are skipped, key positions and index rows are relative to the sequence's first
+ * token.  The reference has no varlen prefill (README.md:135 lists it as future work; its only length
+ * argument is cache_seqlens of kernels/flash_decoding/reuse_kascade_gqa_decode_with_kvcache.py:160-171).
+ *   seq_start [B] int32 device, or NULL (every sequence starts at row 0: right padding)
+ *   seq_len   [B] int32 device, 0 <= seq_len[b], seq_start[b] + seq_len[b] <= max_len
+ * lse2 [B, max_len, H] and pooled [B, G, ceil(max_len/32), row_stride] are indexed by the token / tile number
+ * inside the sequence. */
+typedef struct kb200_ragged {
+  const int32_t* seq_start;
+  const int32_t* seq_len;
+} kb200_ragged;
+int kb200_prefill_dense_ragged(const kb200_act_layout* q, const kb200_act_layout* k,
+                               const kb200_act_layout* v, float softmax_scale, void* out, float* lse2,
+                               const kb200_ragged* ragged, int batch, int max_len, int num_q_heads,
+                               int num_kv_heads, void* stream);
+int kb200_prefill_pool_scores_ragged(const kb200_act_layout* q, const kb200_act_layout* k,
+                                     const float* lse2, float softmax_scale, float* pooled,
+                                     int64_t row_stride, const kb200_ragged* ragged, int batch, int max_len,
+                                     int num_q_heads, int num_kv_heads, void* stream);
+int kb200_prefill_sparse_ragged(const kb200_act_layout* q, const kb200_act_layout* k,
+                                const kb200_act_layout* v, const int32_t* tile_idx, int64_t idx_stride,
+                                const int32_t* tile_count, const int32_t* head_map, float softmax_scale,
+                                void* out, float* lse2, const kb200_ragged* ragged, int batch, int max_len,
+                                int num_q_heads, int num_kv_heads, int idx_kv_heads, void* stream);
+/* Budgets of a ragged batch for kb200_topk_select, per sequence by the reference's formulas
+ * (strategies/KascadeStrategy.py:127-139) for a prompt of seq_len[b] tokens:
+ *   k_b = min(max(128, int(pct/100 * seq_len[b])), seq_len[b]) - 32,
+ *   n_valid[b,g,t] = 32*t, k_row[b,g,t] = min(k_cap, rolling ? min(k_b, max(128, floor(pct*32*t/100))) : k_b)
+ * for tiles inside the sequence, 0 / 0 for tiles beyond its end.  k_cap = row length of the index tensor. */
+int kb200_prefill_budgets_ragged(int32_t* n_valid, int32_t* k_row, const int32_t* seq_len, int batch,
+                                 int num_kv_heads, int num_tiles, int k_cap, float pct, int rolling, void* stream);
+
 /* Output fan-out for prompts whose KV heads are sharded over GPUs: the rows a call computes (its
  * num_q_heads heads) are stored by the kernel's epilogue into `count` buffers, each
  * [B, L, total_heads, D] fp16 contiguous, at heads [head_offset, head_offset + num_q_heads).  out[0] is
@@ -232,6 +269,10 @@ typedef struct kb200_out_fanout {
   int32_t count;
   int32_t total_heads;
   int32_t head_offset;
+  int32_t multicast;   /* 0: plain addresses.  1: count must be 1 and out[0] is the address of an NVLink multicast
+                          object (NVLS: one mapping that stands for the same buffer on every GPU of the group); the
+                          epilogue then stores every row ONCE with multimem.st and the NVSwitch delivers it to all
+                          GPUs, this one included: the egress of a rank is its own slice, not (GPUs - 1) copies of it. */
 } kb200_out_fanout;
 
 /* kb200_prefill_dense / kb200_prefill_sparse with the output rows fanned out (see kb200_out_fanout);

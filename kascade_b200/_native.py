@@ -24,7 +24,8 @@ EXPORTS = [
     "kb200_decode_anchor_paged", "kb200_prefill_dense", "kb200_prefill_pool_scores",
     "kb200_prefill_sparse", "kb200_prefill_budgets", "kb200_selftest_umma", "kb200_read_status",
     "kb200_decode_sparse_paged_noalloc", "kb200_prefill_dense_fanout", "kb200_prefill_sparse_fanout",
-    "kb200_kv_write", "kb200_peer_push", "kb200_stream_wait_events", "kb200_selftest_wait_timeout", "kb200_tensor_map_encodes", "kb200_decode_noalloc_splits",
+    "kb200_kv_write", "kb200_prefill_dense_ragged", "kb200_prefill_pool_scores_ragged", "kb200_prefill_sparse_ragged",
+    "kb200_prefill_budgets_ragged", "kb200_peer_push", "kb200_stream_wait_events", "kb200_selftest_wait_timeout", "kb200_tensor_map_encodes", "kb200_decode_noalloc_splits",
 ]
 
 
@@ -50,18 +51,33 @@ MAX_FANOUT = 8
 class OutFanout(C.Structure):
     """kb200_out_fanout: the output rows of a call go into `count` buffers [B, L, total_heads, D]."""
     _fields_ = [("out", C.c_void_p * MAX_FANOUT), ("count", C.c_int32), ("total_heads", C.c_int32),
-                ("head_offset", C.c_int32)]
+                ("head_offset", C.c_int32), ("multicast", C.c_int32)]
 
 
-def out_fanout(pointers, total_heads: int, head_offset: int) -> OutFanout:
-    """pointers: device addresses (ints) of the [B, L, total_heads, D] fp16 buffers, own buffer first."""
+def out_fanout(pointers, total_heads: int, head_offset: int, multicast: bool = False) -> OutFanout:
+    """pointers: device addresses (ints) of the [B, L, total_heads, D] fp16 buffers, own buffer first; with
+    `multicast` a single NVLink multicast address that stands for the buffer on every GPU."""
     if not 1 <= len(pointers) <= MAX_FANOUT:
         raise KascadeNativeError(f"fan-out of {len(pointers)} outputs (1..{MAX_FANOUT} supported)")
     f = OutFanout()
     for i, ptr in enumerate(pointers):
         f.out[i] = int(ptr)
     f.count, f.total_heads, f.head_offset = len(pointers), int(total_heads), int(head_offset)
+    f.multicast = 1 if multicast else 0
+    if multicast and len(pointers) != 1:
+        raise KascadeNativeError("a multicast fan-out takes exactly one address")
     return f
+
+
+class Ragged(C.Structure):
+    """kb200_ragged: per-sequence first row and length inside equally sized batch slots."""
+    _fields_ = [("seq_start", C.c_void_p), ("seq_len", C.c_void_p)]
+
+
+def ragged(seq_start: Optional[torch.Tensor], seq_len: torch.Tensor) -> Ragged:
+    _want(seq_len, torch.int32, "seq_len")
+    _want_opt(seq_start, torch.int32, "seq_start")
+    return Ragged(0 if seq_start is None else seq_start.data_ptr(), seq_len.data_ptr())
 
 
 class PushPlan(C.Structure):
@@ -114,6 +130,12 @@ def load() -> C.CDLL:
         lib.kb200_prefill_sparse_fanout.argtypes = [AL, AL, AL, vp, i64, vp, vp, f32, FO, vp, i32, i32, i32,
                                                     i32, i32, vp]
         lib.kb200_prefill_budgets.argtypes = [vp, vp, i32, i32, i32, i32, f32, i32, vp]
+        RG = C.POINTER(Ragged)
+        lib.kb200_prefill_dense_ragged.argtypes = [AL, AL, AL, f32, vp, vp, RG, i32, i32, i32, i32, vp]
+        lib.kb200_prefill_pool_scores_ragged.argtypes = [AL, AL, vp, f32, vp, i64, RG, i32, i32, i32, i32, vp]
+        lib.kb200_prefill_sparse_ragged.argtypes = [AL, AL, AL, vp, i64, vp, vp, f32, vp, vp, RG, i32, i32, i32,
+                                                    i32, i32, vp]
+        lib.kb200_prefill_budgets_ragged.argtypes = [vp, vp, vp, i32, i32, i32, i32, f32, i32, vp]
         lib.kb200_kv_write.argtypes = [AL, vp, AL, AL, vp, vp, C.POINTER(KvLayout), vp, vp, f32, vp, f32, i32, i32,
                                        i32, i32, vp]
         lib.kb200_selftest_umma.argtypes = [vp, vp, vp, vp, vp]
@@ -226,6 +248,15 @@ def prefill_budgets(n_valid, k_row, batch, groups, tiles, k_max, pct, rolling):
     _launched(1)
 
 
+@_on_device_of(0)
+def prefill_budgets_ragged(n_valid, k_row, seq_len, batch, groups, tiles, k_cap, pct, rolling):
+    lib = init(n_valid.device.index)
+    _want(seq_len, torch.int32, "seq_len")
+    _check(lib.kb200_prefill_budgets_ragged(_ptr(n_valid), _ptr(k_row), _ptr(seq_len), batch, groups, tiles, k_cap,
+                                            float(pct), int(bool(rolling)), _stream()), "kb200_prefill_budgets_ragged")
+    _launched(1)
+
+
 def kv_layout_paged(k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], block_table: torch.Tensor) -> KvLayout:
     """vLLM-style cache [num_pages, page_size, G, D] and block table [B, max_pages] int32."""
     _want(k_cache, torch.float16, "k_cache")
@@ -333,14 +364,23 @@ def act_layout(x: torch.Tensor) -> ActLayout:
 
 
 @_on_device_of(0)
-def prefill_dense(q, k, v, scale, out, lse2, fanout: Optional[OutFanout] = None):
+def prefill_dense(q, k, v, scale, out, lse2, fanout: Optional[OutFanout] = None, ragged: Optional[Ragged] = None):
     """q [B,L,H,D], k/v [B,L,G,D] (views allowed); out [B,L,H,D] fp16 contiguous or None; lse2 [B,L,H] fp32 or None.
-    With `fanout` (see out_fanout) the rows go into several [B,L,total_heads,D] buffers instead of `out`."""
+    With `fanout` (see out_fanout) the rows go into several [B,L,total_heads,D] buffers instead of `out`; with
+    `ragged` (see ragged()) every sequence has its own first row and length inside its slot of L rows."""
     lib = init(q.device.index)
     B, L, H, _ = q.shape
     G = k.shape[2]
     ql, kl = act_layout(q), act_layout(k)
     vl = act_layout(v) if v is not None else ActLayout(0, 0, 0, 0)
+    if ragged is not None:
+        if out is not None:
+            _want(out, torch.float16, "out")
+            assert out.is_contiguous()
+        _check(lib.kb200_prefill_dense_ragged(C.byref(ql), C.byref(kl), C.byref(vl), float(scale), _ptr(out), _ptr(lse2),
+                                              C.byref(ragged), B, L, H, G, _stream()), "kb200_prefill_dense_ragged")
+        _launched(1)
+        return
     if fanout is not None:
         _check(lib.kb200_prefill_dense_fanout(C.byref(ql), C.byref(kl), C.byref(vl), float(scale), C.byref(fanout),
                                               _ptr(lse2), B, L, H, G, _stream()), "kb200_prefill_dense_fanout")
@@ -355,7 +395,7 @@ def prefill_dense(q, k, v, scale, out, lse2, fanout: Optional[OutFanout] = None)
 
 
 @_on_device_of(0)
-def prefill_pool_scores(q, k, lse2, scale, pooled):
+def prefill_pool_scores(q, k, lse2, scale, pooled, ragged: Optional[Ragged] = None):
     """pooled [B,G,T,row_stride] fp32 contiguous."""
     lib = init(q.device.index)
     B, L, H, _ = q.shape
@@ -364,13 +404,20 @@ def prefill_pool_scores(q, k, lse2, scale, pooled):
     _want(pooled, torch.float32, "pooled")
     _want(lse2, torch.float32, "lse2")
     assert pooled.is_contiguous() and lse2.is_contiguous()
+    if ragged is not None:
+        _check(lib.kb200_prefill_pool_scores_ragged(C.byref(ql), C.byref(kl), _ptr(lse2), float(scale), _ptr(pooled),
+                                                    pooled.shape[-1], C.byref(ragged), B, L, H, G, _stream()),
+               "kb200_prefill_pool_scores_ragged")
+        _launched(1)
+        return
     _check(lib.kb200_prefill_pool_scores(C.byref(ql), C.byref(kl), _ptr(lse2), float(scale), _ptr(pooled),
                                          pooled.shape[-1], B, L, H, G, _stream()), "kb200_prefill_pool_scores")
     _launched(1)
 
 
 @_on_device_of(0)
-def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=None, fanout: Optional[OutFanout] = None):
+def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=None, fanout: Optional[OutFanout] = None,
+                   ragged: Optional[Ragged] = None):
     """tile_idx [B,G,T,kstride] int32, tile_count [B,G,T] int32, out [B,L,H,D] fp16 contiguous.
     With `fanout` (see out_fanout) the rows go into several [B,L,total_heads,D] buffers instead of `out`."""
     lib = init(q.device.index)
@@ -390,6 +437,13 @@ def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=Non
         return
     _want(out, torch.float16, "out")
     assert out.is_contiguous()
+    if ragged is not None:
+        _check(lib.kb200_prefill_sparse_ragged(C.byref(ql), C.byref(kl), C.byref(vl), _ptr(tile_idx), tile_idx.shape[-1],
+                                               _ptr(tile_count), _ptr(head_map), float(scale), _ptr(out), _ptr(lse2),
+                                               C.byref(ragged), B, L, H, G, tile_idx.shape[1], _stream()),
+               "kb200_prefill_sparse_ragged")
+        _launched(1)
+        return
     _check(lib.kb200_prefill_sparse(C.byref(ql), C.byref(kl), C.byref(vl), _ptr(tile_idx), tile_idx.shape[-1],
                                     _ptr(tile_count), _ptr(head_map), float(scale), _ptr(out), _ptr(lse2), B, L, H,
                                     G, tile_idx.shape[1], _stream()), "kb200_prefill_sparse")

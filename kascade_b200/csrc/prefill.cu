@@ -67,10 +67,15 @@ struct PrefillParams {
   __half* out;                    // == out_fan[0] unless the output goes to several GPUs
   __half* out_fan[KB200_MAX_FANOUT];   // outputs [B, L, H_out, D]: this GPU's own buffer and its peers'
   int n_fan, H_out, h_off;        // number of outputs, heads of an output row, first head written by this call
+  int mc;                         // out_fan[0] is a multicast address: rows are stored with multimem.st
   float* lse2;
   const float* lse2_in;
   float* pooled; int64_t pooled_stride;
-  int B, L, H, G, T;
+  int B, L, H, G, T;                  // L: tokens of a batch slot (the longest sequence), T: its tiles
+  // Ragged batches (NULL: every sequence has L tokens starting at row 0 of its slot): sequence b occupies
+  // rows seq_start[b] .. seq_start[b] + seq_len[b] - 1 of slot b; tiles beyond a sequence's end are skipped.
+  const int32_t* seq_start;
+  const int32_t* seq_len;
   int G_idx;                      // KV heads in the index tensors (>= G when heads are sharded)
   int group;                      // (sequence, KV head) pairs whose tiles are walked together, divides B * G
 };
@@ -142,6 +147,13 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
+// 16 bytes to an NVLink multicast address (the mapping of a multicast object): delivered to every GPU bound to it
+__device__ __forceinline__ void multimem_st16(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(mc_addr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -169,6 +181,7 @@ constexpr int kSmemNoV = kStageBytes * (1 + kNKNoV) + kPadAllowance + 2560 + kXc
 // One work item = one query tile of one KV head of one sequence.
 struct TileItem {
   int b, g, t, tile_start, rows_valid, count, total, nb;
+  int L, row0;                          // tokens of this sequence, its first row inside the batch slot
   const int32_t* idx_row;
 };
 
@@ -187,10 +200,15 @@ __device__ __forceinline__ TileItem decode_item(const PrefillParams& p, int item
   it.b = bg / p.G;
   it.g = bg - it.b * p.G;
   it.tile_start = it.t * kTile;
-  it.rows_valid = min(kTile, p.L - it.tile_start);
+  it.L = p.seq_len ? min(max(p.seq_len[it.b], 0), p.L) : p.L;
+  it.row0 = p.seq_start ? p.seq_start[it.b] : 0;
+  it.rows_valid = min(kTile, it.L - it.tile_start);
   it.count = 0;
   it.idx_row = nullptr;
-  if (MODE == kSparse) {
+  if (it.rows_valid <= 0) {                             // a tile beyond the end of a short sequence
+    it.rows_valid = 0;
+    it.total = 0;
+  } else if (MODE == kSparse) {
     const int src_g = p.head_map ? p.head_map[it.g] : it.g;
     const int64_t row = ((int64_t)it.b * p.G_idx + src_g) * p.T + it.t;
     const int c = p.tile_count[row];
@@ -332,19 +350,20 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     struct GatherTile {
       const char* base;                                  // this lane's 16-byte chunk of key 0 of the (sequence, KV head)
       const int32_t* idx;
-      int count, total, tile_start, nb;
+      int count, total, tile_start, nb, L;
     };
     auto fetch = [&](int k) -> GatherTile {
       GatherTile g;
-      g.base = nullptr; g.idx = nullptr; g.count = 0; g.total = 0; g.tile_start = 0; g.nb = 0;
+      g.base = nullptr; g.idx = nullptr; g.count = 0; g.total = 0; g.tile_start = 0; g.nb = 0; g.L = 1;
       if (k < n_rounds) {
         const int item = item_of(k);
         if (item < n_items) {
           const TileItem it = decode_item<MODE>(p, item);
           g.base = reinterpret_cast<const char*>(
-              (is_v ? p.v + (int64_t)it.b * p.v_sb + (int64_t)it.g * p.v_sh
-                    : p.k + (int64_t)it.b * p.k_sb + (int64_t)it.g * p.k_sh) + (lane & 15) * 8);
+              (is_v ? p.v + (int64_t)it.b * p.v_sb + (int64_t)it.row0 * p.v_st + (int64_t)it.g * p.v_sh
+                    : p.k + (int64_t)it.b * p.k_sb + (int64_t)it.row0 * p.k_st + (int64_t)it.g * p.k_sh) + (lane & 15) * 8);
           g.idx = it.idx_row; g.count = it.count; g.total = it.total; g.tile_start = it.tile_start; g.nb = it.nb;
+          g.L = it.L;
         }
       }
       return g;
@@ -370,7 +389,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       }
       for (int j = 0; j < cur.nb; ++j) {
         if (!a_ok) { a0 = key_of(cur, j, 0); a1 = key_of(cur, j, 1); }
-        const int key0 = max(0, min(a0, p.L - 1)), key1 = max(0, min(a1, p.L - 1));
+        const int key0 = max(0, min(a0, cur.L - 1)), key1 = max(0, min(a1, cur.L - 1));
         a0 = b0; a1 = b1; a_ok = b_ok;
         const int j2 = j + 2;
         if (j2 < cur.nb) { b0 = key_of(cur, j2, 0); b1 = key_of(cur, j2, 1); b_ok = true; }
@@ -419,8 +438,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       ok = mbar_wait(&sh.bar_qempty, (qn & 1) ^ 1, &give_up, 13);
       if (!ok) break;
       mbar_arrive_expect_tx(&sh.bar_q, kStageBytes);
-      tma_load_4d(q_s, &tm_q, 0, it.g * kHg, it.tile_start, it.b, &sh.bar_q);
-      tma_load_4d(q_s + kStageBytes / 2, &tm_q, 64, it.g * kHg, it.tile_start, it.b, &sh.bar_q);
+      tma_load_4d(q_s, &tm_q, 0, it.g * kHg, it.row0 + it.tile_start, it.b, &sh.bar_q);
+      tma_load_4d(q_s + kStageBytes / 2, &tm_q, 64, it.g * kHg, it.row0 + it.tile_start, it.b, &sh.bar_q);
       ++qn;
       for (int j = 0; j < it.nb; ++j) {
         ok = mbar_wait(&bar_kempty[st], ph, &give_up, 11);
@@ -428,8 +447,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         const uint32_t dst = k_s + st * kStageBytes;
         uint64_t* bar = &bar_kfull[st];
         mbar_arrive_expect_tx(bar, kStageBytes);
-        tma_load_4d(dst, &tm_k, 0, it.g, j * 128, it.b, bar);
-        tma_load_4d(dst + kStageBytes / 2, &tm_k, 64, it.g, j * 128, it.b, bar);
+        tma_load_4d(dst, &tm_k, 0, it.g, it.row0 + j * 128, it.b, bar);
+        tma_load_4d(dst + kStageBytes / 2, &tm_k, 64, it.g, it.row0 + j * 128, it.b, bar);
         if (++st == kNK) { st = 0; ph ^= 1; }
       }
     }
@@ -448,8 +467,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         const uint32_t dst = v_s + st * kStageBytes;
         uint64_t* bar = &bar_vfull[st];
         mbar_arrive_expect_tx(bar, kStageBytes);
-        tma_load_4d(dst, &tm_v, 0, it.g, j * 128, it.b, bar);
-        tma_load_4d(dst + kStageBytes / 2, &tm_v, 64, it.g, j * 128, it.b, bar);
+        tma_load_4d(dst, &tm_v, 0, it.g, it.row0 + j * 128, it.b, bar);
+        tma_load_4d(dst + kStageBytes / 2, &tm_v, 64, it.g, it.row0 + j * 128, it.b, bar);
         if (++st == kNV) { st = 0; ph ^= 1; }
       }
     }
@@ -566,17 +585,16 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         if (!ok) break;
         if (el) {
           mbar_arrive_expect_tx(&sh.bar_q, kStageBytes);
-          tma_load_4d(q_s, &tm_q, 0, it.g * kHg, it.tile_start, it.b, &sh.bar_q);
-          tma_load_4d(q_s + kStageBytes / 2, &tm_q, 64, it.g * kHg, it.tile_start, it.b, &sh.bar_q);
+          tma_load_4d(q_s, &tm_q, 0, it.g * kHg, it.row0 + it.tile_start, it.b, &sh.bar_q);
+          tma_load_4d(q_s + kStageBytes / 2, &tm_q, 64, it.g * kHg, it.row0 + it.tile_start, it.b, &sh.bar_q);
           if (k + 1 < n_rounds) {
             const int nitem = item_of(k + 1);
             if (nitem < n_items) {
-              const int per = p.group * p.T;
-              const int hi = nitem / per, lo = nitem - hi * per;
-              const int r = lo / p.group, bg = hi * p.group + (lo - r * p.group);
-              const int nb_ = bg / p.G, ng = bg - nb_ * p.G, nt = p.T - 1 - r;
-              tma_prefetch_4d(&tm_q, 0, ng * kHg, nt * kTile, nb_);
-              tma_prefetch_4d(&tm_q, 64, ng * kHg, nt * kTile, nb_);
+              const TileItem nx = decode_item<MODE>(p, nitem);
+              if (nx.nb > 0) {
+                tma_prefetch_4d(&tm_q, 0, nx.g * kHg, nx.row0 + nx.tile_start, nx.b);
+                tma_prefetch_4d(&tm_q, 64, nx.g * kHg, nx.row0 + nx.tile_start, nx.b);
+              }
             }
           }
         }
@@ -908,18 +926,26 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int rj = row0 + j, tj = it.tile_start + (rj >> 2);
-          offs[j] = tj < p.L ? (((int64_t)it.b * p.L + tj) * p.H_out + p.h_off + it.g * kHg + (rj & 3)) * kD + wg * 64 + chunk * 8
+          offs[j] = tj < it.L ? (((int64_t)it.b * p.L + it.row0 + tj) * p.H_out + p.h_off + it.g * kHg + (rj & 3)) * kD + wg * 64 + chunk * 8
                              : -1;
         }
-#pragma unroll 1
-        for (int f = 0; f < p.n_fan; ++f) {
-          __half* base = p.out_fan[f];
+        if (p.mc) {
+          // one store per row chunk to the multicast address: the switch replicates it to every GPU
+          __half* base = p.out_fan[0];
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            if (offs[j] >= 0) *reinterpret_cast<uint4*>(base + offs[j]) = w[j];
+            if (offs[j] >= 0) multimem_st16(base + offs[j], w[j]);
+        } else {
+#pragma unroll 1
+          for (int f = 0; f < p.n_fan; ++f) {
+            __half* base = p.out_fan[f];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (offs[j] >= 0) *reinterpret_cast<uint4*>(base + offs[j]) = w[j];
+          }
         }
       }
-      if (wg == 0 && p.lse2 && tok < p.L)
+      if (wg == 0 && p.lse2 && tok < it.L)
         p.lse2[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (row & 3)] = m_tot + log2f(l_tot);
       ++tiles_done;
     }
@@ -1013,7 +1039,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       mbar_arrive(&sh.bar_x);
       ok = mbar_wait(&sh.bar_x, tiles_done & 1, &give_up, 35);
       if (!ok) break;
-      if (wg == 0 && p.lse2 && tok < p.L) {
+      if (wg == 0 && p.lse2 && tok < it.L) {
         float m_tot = -INFINITY;
 #pragma unroll
         for (int s2 = 0; s2 < NS; ++s2) m_tot = fmaxf(m_tot, xm[s2 * 128 + row]);
@@ -1055,7 +1081,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       {
         const int tok = it.tile_start + (key_lane >> 2);
         lse_s[key_lane] =
-            tok < p.L ? p.lse2_in[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (key_lane & 3)] : INFINITY;
+            tok < it.L ? p.lse2_in[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (key_lane & 3)] : INFINITY;
         mbar_arrive(&sh.bar_lse[wg]);
         ok = mbar_wait(&sh.bar_lse[wg], tiles_seen & 1, &give_up, 43);
         if (!ok) break;
@@ -1293,6 +1319,7 @@ static int set_outputs(PrefillParams* p, void* out, const kb200_out_fanout* fan,
     p->n_fan = 1;
     p->H_out = num_q_heads;
     p->h_off = 0;
+    p->mc = 0;
     return 0;
   }
   KB_REQUIRE(fan->count >= 1 && fan->count <= KB200_MAX_FANOUT, "%s: fan-out of %d outputs (1..%d supported)", what,
@@ -1306,6 +1333,9 @@ static int set_outputs(PrefillParams* p, void* out, const kb200_out_fanout* fan,
                "%s: fan-out output %d is null or not 16-byte aligned", what, i);
     p->out_fan[i] = static_cast<__half*>(fan->out[i]);
   }
+  KB_REQUIRE(fan->multicast == 0 || (fan->multicast == 1 && fan->count == 1),
+             "%s: a multicast fan-out takes exactly one (multicast) address", what);
+  p->mc = fan->multicast;
   p->out = p->out_fan[0];
   p->n_fan = fan->count;
   p->H_out = fan->total_heads;
@@ -1364,9 +1394,20 @@ extern "C" int kb200_selftest_wait_timeout(int32_t* result, uint64_t limit_ns, i
 }
 
 namespace kb200 {
+static int set_ragged(PrefillParams* p, const kb200_ragged* rg, const char* what) {
+  p->seq_start = nullptr;
+  p->seq_len = nullptr;
+  if (!rg) return 0;
+  KB_REQUIRE(rg->seq_len, "%s: a ragged batch needs seq_len", what);
+  p->seq_start = rg->seq_start;
+  p->seq_len = rg->seq_len;
+  return 0;
+}
+
 static int prefill_dense_impl(const kb200_act_layout* q, const kb200_act_layout* k, const kb200_act_layout* v,
                               float softmax_scale, void* out, const kb200_out_fanout* fan, float* lse2, int batch,
-                              int seq_len, int num_q_heads, int num_kv_heads, void* stream) {
+                              int seq_len, int num_q_heads, int num_kv_heads, void* stream,
+                              const kb200_ragged* rg = nullptr) {
   if (check_shape(q, batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
   if (fan) out = fan->count >= 1 ? fan->out[0] : nullptr;
   KB_REQUIRE(out || lse2, "prefill_dense: nothing to compute (out and lse2 are both null)");
@@ -1379,6 +1420,7 @@ static int prefill_dense_impl(const kb200_act_layout* q, const kb200_act_layout*
   p.scale2 = softmax_scale * kLog2e;
   p.lse2 = lse2;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
+  if (set_ragged(&p, rg, "prefill_dense") != 0) return -1;
   p.group = pick_group(batch, num_kv_heads, seq_len, out != nullptr);
   CUtensorMap tq, tk, tv;
   if (make_act_map(&tq, p.q, p.q_sb, p.q_st, p.q_sh, num_q_heads, seq_len, batch, kHg, kTile, "q") != 0) return -1;
@@ -1412,11 +1454,10 @@ extern "C" int kb200_prefill_dense_fanout(const kb200_act_layout* q, const kb200
                             stream);
 }
 
-extern "C" int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_act_layout* k,
-                                         const float* lse2, float softmax_scale, float* pooled,
-                                         int64_t row_stride, int batch, int seq_len, int num_q_heads,
-                                         int num_kv_heads, void* stream) {
-  using namespace kb200;
+namespace kb200 {
+static int prefill_pool_impl(const kb200_act_layout* q, const kb200_act_layout* k, const float* lse2,
+                             float softmax_scale, float* pooled, int64_t row_stride, int batch, int seq_len,
+                             int num_q_heads, int num_kv_heads, void* stream, const kb200_ragged* rg) {
   if (check_shape(q, batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
   KB_REQUIRE(lse2 && pooled, "prefill_pool_scores: null pointer");
   KB_REQUIRE(row_stride >= seq_len, "prefill_pool_scores: row_stride (%lld) smaller than seq_len (%d)",
@@ -1430,6 +1471,7 @@ extern "C" int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_
   p.pooled = pooled;
   p.pooled_stride = row_stride;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
+  if (set_ragged(&p, rg, "prefill_pool_scores") != 0) return -1;
   p.group = pick_group(batch, num_kv_heads, seq_len, false);
   CUtensorMap tq, tk;
   if (make_act_map(&tq, p.q, p.q_sb, p.q_st, p.q_sh, num_q_heads, seq_len, batch, kHg, kTile, "q") != 0) return -1;
@@ -1439,13 +1481,42 @@ extern "C" int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_
   KB_CHECK_LAUNCH("tile_prefill_kernel<pool>");
   return 0;
 }
+}  // namespace kb200
+
+extern "C" int kb200_prefill_pool_scores(const kb200_act_layout* q, const kb200_act_layout* k,
+                                         const float* lse2, float softmax_scale, float* pooled,
+                                         int64_t row_stride, int batch, int seq_len, int num_q_heads,
+                                         int num_kv_heads, void* stream) {
+  return kb200::prefill_pool_impl(q, k, lse2, softmax_scale, pooled, row_stride, batch, seq_len, num_q_heads,
+                                  num_kv_heads, stream, nullptr);
+}
+
+extern "C" int kb200_prefill_pool_scores_ragged(const kb200_act_layout* q, const kb200_act_layout* k,
+                                                const float* lse2, float softmax_scale, float* pooled,
+                                                int64_t row_stride, const kb200_ragged* ragged, int batch, int max_len,
+                                                int num_q_heads, int num_kv_heads, void* stream) {
+  using namespace kb200;
+  KB_REQUIRE(ragged, "prefill_pool_scores_ragged: ragged is null");
+  return prefill_pool_impl(q, k, lse2, softmax_scale, pooled, row_stride, batch, max_len, num_q_heads, num_kv_heads,
+                           stream, ragged);
+}
+
+extern "C" int kb200_prefill_dense_ragged(const kb200_act_layout* q, const kb200_act_layout* k,
+                                          const kb200_act_layout* v, float softmax_scale, void* out, float* lse2,
+                                          const kb200_ragged* ragged, int batch, int max_len, int num_q_heads,
+                                          int num_kv_heads, void* stream) {
+  using namespace kb200;
+  KB_REQUIRE(ragged, "prefill_dense_ragged: ragged is null");
+  return prefill_dense_impl(q, k, v, softmax_scale, out, nullptr, lse2, batch, max_len, num_q_heads, num_kv_heads,
+                            stream, ragged);
+}
 
 namespace kb200 {
 static int prefill_sparse_impl(const kb200_act_layout* q, const kb200_act_layout* k, const kb200_act_layout* v,
                                const int32_t* tile_idx, int64_t idx_stride, const int32_t* tile_count,
                                const int32_t* head_map, float softmax_scale, void* out, const kb200_out_fanout* fan,
                                float* lse2, int batch, int seq_len, int num_q_heads, int num_kv_heads,
-                               int idx_kv_heads, void* stream) {
+                               int idx_kv_heads, void* stream, const kb200_ragged* rg = nullptr) {
   if (check_shape(q, batch, seq_len, num_q_heads, num_kv_heads) != 0) return -1;
   if (fan) out = fan->count >= 1 ? fan->out[0] : nullptr;
   KB_REQUIRE(tile_idx && tile_count && out, "prefill_sparse: null pointer");
@@ -1469,6 +1540,7 @@ static int prefill_sparse_impl(const kb200_act_layout* q, const kb200_act_layout
   if (set_outputs(&p, out, fan, num_q_heads, "prefill_sparse") != 0) return -1;
   p.lse2 = lse2;
   p.B = batch; p.L = seq_len; p.H = num_q_heads; p.G = num_kv_heads; p.T = ceil_div(seq_len, kTile);
+  if (set_ragged(&p, rg, "prefill_sparse") != 0) return -1;
   p.group = pick_group(batch, num_kv_heads, seq_len, true);
   CUtensorMap tq, none{};                                // Q tiles by TMA; the K / V rows are gathered without maps
   if (make_act_map(&tq, p.q, p.q_sb, p.q_st, p.q_sh, num_q_heads, seq_len, batch, kHg, kTile, "q") != 0) return -1;
@@ -1497,4 +1569,15 @@ extern "C" int kb200_prefill_sparse_fanout(const kb200_act_layout* q, const kb20
   KB_REQUIRE(fan, "prefill_sparse_fanout: fan is null");
   return prefill_sparse_impl(q, k, v, tile_idx, idx_stride, tile_count, head_map, softmax_scale, nullptr, fan, lse2,
                              batch, seq_len, num_q_heads, num_kv_heads, idx_kv_heads, stream);
+}
+
+extern "C" int kb200_prefill_sparse_ragged(const kb200_act_layout* q, const kb200_act_layout* k,
+                                           const kb200_act_layout* v, const int32_t* tile_idx, int64_t idx_stride,
+                                           const int32_t* tile_count, const int32_t* head_map, float softmax_scale,
+                                           void* out, float* lse2, const kb200_ragged* ragged, int batch, int max_len,
+                                           int num_q_heads, int num_kv_heads, int idx_kv_heads, void* stream) {
+  using namespace kb200;
+  KB_REQUIRE(ragged, "prefill_sparse_ragged: ragged is null");
+  return prefill_sparse_impl(q, k, v, tile_idx, idx_stride, tile_count, head_map, softmax_scale, out, nullptr, lse2,
+                             batch, max_len, num_q_heads, num_kv_heads, idx_kv_heads, stream, ragged);
 }

@@ -174,7 +174,41 @@ __global__ void prefill_budgets_kernel(int32_t* n_valid, int32_t* k_row, int num
   k_row[i] = k;
 }
 
+// per-sequence budgets of a ragged batch: the reference's formulas for a prompt of seq_len[b] tokens
+// (strategies/KascadeStrategy.py:127-139); tiles beyond a sequence's end get no candidates
+__global__ void prefill_budgets_ragged_kernel(int32_t* n_valid, int32_t* k_row, const int32_t* seq_len, int groups,
+                                              int num_tiles, int total, int k_cap, float pct, int rolling) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int t = i % num_tiles, b = i / (num_tiles * groups);
+  const int L = max(seq_len[b], 0), start = t * kTile;
+  int kk = min(max(128, (int)((double)pct / 100.0 * (double)L)), L) - kTile;
+  kk = max(kk, 0);
+  int k = kk;
+  if (rolling && L > 128) {
+    int r = (int)floor((double)pct * (double)start / 100.0);
+    k = min(kk, max(128, r));
+  }
+  const bool live = start < L;
+  n_valid[i] = live ? start : 0;
+  k_row[i] = live ? min(k, k_cap) : 0;
+}
+
 }  // namespace kb200
+
+extern "C" int kb200_prefill_budgets_ragged(int32_t* n_valid, int32_t* k_row, const int32_t* seq_len, int batch,
+                                            int num_kv_heads, int num_tiles, int k_cap, float pct, int rolling,
+                                            void* stream) {
+  using namespace kb200;
+  KB_ENTRY(n_valid, "prefill_budgets_ragged: n_valid");
+  KB_REQUIRE(n_valid && k_row && seq_len, "prefill_budgets_ragged: null pointer");
+  int total = batch * num_kv_heads * num_tiles;
+  if (total <= 0) return 0;
+  prefill_budgets_ragged_kernel<<<ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
+      n_valid, k_row, seq_len, num_kv_heads, num_tiles, total, k_cap, pct, rolling);
+  KB_CHECK_LAUNCH("prefill_budgets_ragged_kernel");
+  return 0;
+}
 
 extern "C" int kb200_topk_select(const float* scores, int64_t row_stride, int n_cols,
                                  const int32_t* n_valid, const int32_t* k_row, int k_max,

@@ -15,11 +15,12 @@ import torch.distributed as dist
 
 
 class PeerBuffers:
-    def __init__(self, tensors: List[torch.Tensor], pointers: List[List[int]], how: str, keep=None):
+    def __init__(self, tensors: List[torch.Tensor], pointers: List[List[int]], how: str, keep=None, multicast=None):
         self.tensors = tensors            # this rank's buffers, one per copy
         self.pointers = pointers          # [copy][rank] -> device address valid in this process
         self.how = how                    # "symmetric_memory" or "cuda_ipc"
         self._keep = keep                 # handles / mapped tensors that must stay alive
+        self.multicast = multicast        # [copy] -> NVLink multicast address of the buffer (0 / None: not available)
 
     def fanout_pointers(self, copy: int, rank: int) -> List[int]:
         """Own buffer first, then the peers starting with rank + 1 (ranks stagger their targets)."""
@@ -29,14 +30,15 @@ class PeerBuffers:
 
 def _via_symmetric_memory(shape, dtype, device, copies, group) -> PeerBuffers:
     import torch.distributed._symmetric_memory as symm
-    tensors, pointers, keep = [], [], []
+    tensors, pointers, keep, mc = [], [], [], []
     for _ in range(copies):
         t = symm.empty(*shape, dtype=dtype, device=device)
         hdl = symm.rendezvous(t, group=group)
         tensors.append(t)
         pointers.append([int(p) for p in hdl.buffer_ptrs])
+        mc.append(int(getattr(hdl, "multicast_ptr", 0) or 0))
         keep.append(hdl)
-    return PeerBuffers(tensors, pointers, "symmetric_memory", keep)
+    return PeerBuffers(tensors, pointers, "symmetric_memory", keep, mc)
 
 
 def _via_cuda_ipc(shape, dtype, device, copies, group) -> PeerBuffers:

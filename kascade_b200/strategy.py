@@ -102,7 +102,10 @@ class EfficientKascadeStrategy(Strategy):
       exceeds its link time);
     * ``"push"``: the kernel writes this rank's heads into its own [B, L, H, D] buffer and the copy engines
       push that slice into the peers' buffers on side streams while the next layers' kernels run (best
-      from four GPUs on, where a reuse layer's link time exceeds its compute time).
+      from four GPUs on, where a reuse layer's link time exceeds its compute time);
+    * ``"multicast"``: the kernel stores every row once to an NVLink multicast address (NVLS) and the NVSwitch
+      delivers it to all ranks: a rank's egress is its own slice instead of (ranks - 1) copies of it.  Needs
+      symmetric memory with a multicast mapping; falls back to ``"peer_store"`` where there is none.
 
     In the last two modes ``gathered_out`` is a [B, L, H, D] buffer of a small ring (``copies``), complete
     once ``wait_gathers()`` has returned on every rank.  The buffer of layer n is written again by layer
@@ -132,11 +135,11 @@ class EfficientKascadeStrategy(Strategy):
         self._shard = tuple(shard) if shard is not None else None
         if exchange is None:
             exchange = "peer_store" if peer_store else "nccl"
-        if exchange not in ("nccl", "peer_store", "push"):
-            raise ValueError(f"exchange must be 'nccl', 'peer_store' or 'push', got {exchange!r}")
+        if exchange not in ("nccl", "peer_store", "push", "multicast"):
+            raise ValueError(f"exchange must be 'nccl', 'peer_store', 'push' or 'multicast', got {exchange!r}")
         sharded = self._shard is not None and self._shard[1] > 1
         self._exchange = exchange if sharded else "nccl"
-        self._peer_store = self._exchange in ("peer_store", "push")   # outputs live in peer-mapped [B,L,H,D] buffers
+        self._peer_store = self._exchange in ("peer_store", "push", "multicast")   # outputs live in peer-mapped [B,L,H,D] buffers
         self._copies = int(copies) if copies else (4 if self._exchange == "push" else 2)
         self._peer = None                       # kascade_b200.peer.PeerBuffers, allocated at the first prefill
         self._peer_copy = 0
@@ -191,6 +194,7 @@ class EfficientKascadeStrategy(Strategy):
         return {"nccl": "outputs all-gathered by NCCL",
                 "peer_store": "outputs stored into the peers by the kernel epilogue" + how,
                 "push": f"outputs pushed to the peers by the copy engines on side streams, {self._copies} buffers" + how,
+                "multicast": "outputs stored once to an NVLink multicast address by the kernel epilogue (NVLS)" + how,
                 }[self._exchange]
 
     def is_anchor(self, layer_idx: int) -> bool:
@@ -238,9 +242,17 @@ class EfficientKascadeStrategy(Strategy):
         B, H, Lq, D = query.shape
         G, Lk = key.shape[1], key.shape[2]
         layer = int(module.layer_idx)
-        pads = self._left_padding(attention_mask, B, Lk) if self._shard is None else None
-        if pads is not None:
-            return self._forward_left_padded(pads, module, query, key, value, scaling), None
+        pad = self._padding(attention_mask, B, Lk) if self._shard is None else None
+        if pad is not None:
+            if Lq == 1:
+                return self._decode_padded(pad, module, query, key, value, scaling), None
+            if Lq != Lk:
+                raise NotImplementedError("prefill expects the whole prompt (Lq == Lk); chunked prefill is not supported")
+            starts, lens = pad
+            dev = query.device
+            rg = (torch.tensor(starts, dtype=torch.int32, device=dev), torch.tensor(lens, dtype=torch.int32, device=dev), lens)
+            q, k, v = self._token_major(query), self._token_major(key), self._token_major(value)
+            return self._prefill(layer, q, k, v, scaling, ragged=rg), None
         if Lq == 1:
             kv = nat.kv_layout_contiguous(*self._cache_views(key, value))
             seq_lens = self._scratch("seq_lens_full", (B,), torch.int32, query.device)
@@ -261,11 +273,12 @@ class EfficientKascadeStrategy(Strategy):
             return out, None
         return self._prefill(layer, q, k, v, scaling), None
 
-    # -- left-padded batches ----------------------------------------------------------------------
-    def _left_padding(self, attention_mask, B: int, Lk: int):
-        """Per-sequence number of leading key positions that the mask hides from the last query row, or
-        None if there is no such padding.  HF hands the same mask tensor to every layer of a forward, so
-        the (synchronising) look at it happens once per forward."""
+    # -- padded batches ---------------------------------------------------------------------------
+    def _padding(self, attention_mask, B: int, Lk: int):
+        """(first row, length) of every sequence if the batch is padded, read from the key columns that the mask
+        lets the LAST query row see (left padding hides a prefix, right padding a suffix), or None for a batch
+        without padding.  HF hands the same mask tensor to every layer of a forward, so the (synchronising) look at
+        it happens once per forward."""
         if attention_mask is None or attention_mask.dim() != 4 or attention_mask.shape[0] != B \
                 or attention_mask.shape[-1] != Lk:
             return None
@@ -273,33 +286,33 @@ class EfficientKascadeStrategy(Strategy):
         if ref is None or ref() is not attention_mask or self._pad_version != attention_mask._version:
             import weakref
             last = attention_mask[:, 0, -1, :]                                    # [B, Lk]
-            hidden = ~last if last.dtype == torch.bool else last != 0
-            lead = torch.cumprod(hidden.to(torch.int32), dim=-1).sum(-1)          # length of the hidden prefix
-            pads = [int(x) for x in lead.tolist()]
+            seen = last if last.dtype == torch.bool else last == 0
+            n_seen = seen.sum(-1)
+            first = torch.where(n_seen > 0, seen.to(torch.int32).argmax(-1), torch.zeros_like(n_seen))
+            both = torch.stack([first, n_seen]).tolist()
             self.check_status(attention_mask.device)                              # the host has just synchronised
+            starts, lens = [int(x) for x in both[0]], [int(x) for x in both[1]]
             self._pad_ref, self._pad_version = weakref.ref(attention_mask), attention_mask._version
-            self._pads = pads if any(pads) else None
+            self._pads = None if all(n == Lk for n in lens) else (starts, lens)
         return self._pads
 
-    def _forward_left_padded(self, pads, module, query, key, value, scaling) -> torch.Tensor:
+    def _decode_padded(self, pad, module, query, key, value, scaling) -> torch.Tensor:
+        """One decode step of a padded batch: every sequence runs on its own unpadded cache views with its own
+        index rows (a padded cache has no single layout the decode kernels could walk)."""
+        starts, lens = pad
         B, H, Lq, D = query.shape
-        Lk = key.shape[2]
         if getattr(self, "_children", None) is None or len(self._children) != B:
             self._children = [EfficientKascadeStrategy(self.recompute_layers, "", k=self.k, tile_size=self.tile_size,
                                                        rolling_prefill=self.rolling_prefill,
                                                        head_mapping=self._head_mapping, register=False)
                               for _ in range(B)]
         out = torch.zeros(B, Lq, H, D, dtype=torch.float16, device=query.device)
-        for b, (pad, child) in enumerate(zip(pads, self._children)):
-            if pad >= Lk:
+        for b, (s0, n, child) in enumerate(zip(starts, lens, self._children)):
+            if n == 0:
                 continue                                                           # nothing to attend to
-            kb, vb = key[b:b + 1, :, pad:], value[b:b + 1, :, pad:]
-            if Lq == 1:
-                ob, _ = child.attention_forward(module, query[b:b + 1], kb, vb, None, scaling)
-                out[b:b + 1] = ob
-            else:                                                                  # prefill: queries pad.. are the prompt
-                ob, _ = child.attention_forward(module, query[b:b + 1, :, pad:], kb, vb, None, scaling)
-                out[b:b + 1, pad:] = ob
+            ob, _ = child.attention_forward(module, query[b:b + 1], key[b:b + 1, :, s0:s0 + n], value[b:b + 1, :, s0:s0 + n],
+                                            None, scaling)
+            out[b:b + 1] = ob
         return out
 
     @staticmethod
@@ -309,26 +322,39 @@ class EfficientKascadeStrategy(Strategy):
         return key, value
 
     # -- prefill -----------------------------------------------------------------------------------
-    def _prefill(self, layer: int, q, k, v, scaling) -> torch.Tensor:
+    def _prefill(self, layer: int, q, k, v, scaling, ragged=None) -> torch.Tensor:
+        """q [B,L,H,D], k / v [B,L,G,D] token-major views.  `ragged` = (first rows [B] int32, lengths [B] int32 on
+        the device, lengths on the host): a padded batch, every kernel still launched once; rows outside a sequence
+        come back as zeros."""
         B, L, H, D = q.shape
         G = k.shape[2]
         dev = q.device
         T = -(-L // self.tile_size)
         fan = self._next_fanout(B, L, H, D, dev) if self._peer_store else None      # None: not in use (or not available)
-        out = torch.empty(B, L, H, D, dtype=torch.float16, device=dev) if fan is None else None
+        rg = nat.ragged(ragged[0], ragged[1]) if ragged is not None else None
+        if fan is not None:
+            out = None
+        elif rg is not None:
+            out = torch.zeros(B, L, H, D, dtype=torch.float16, device=dev)
+        else:
+            out = torch.empty(B, L, H, D, dtype=torch.float16, device=dev)
         if self.is_anchor(layer):
-            kk = topk_budget(self.k, L, self.tile_size)
+            kk = topk_budget(self.k, L, self.tile_size) if ragged is None else \
+                max(1, max(topk_budget(self.k, n, self.tile_size) for n in ragged[2]))
             lse2 = self._scratch("lse2", (B, L, H), torch.float32, dev)
             if layer == 0 and fan is not None:
                 nat.prefill_dense(q, k, v, scaling, None, lse2, fanout=fan)
             else:
-                nat.prefill_dense(q, k, v if layer == 0 else None, scaling, out if layer == 0 else None, lse2)
+                nat.prefill_dense(q, k, v if layer == 0 else None, scaling, out if layer == 0 else None, lse2, ragged=rg)
             stride = -(-L // 128) * 128
             pooled = self._scratch("pooled", (B, G, T, stride), torch.float32, dev)
-            nat.prefill_pool_scores(q, k, lse2, scaling, pooled)
+            nat.prefill_pool_scores(q, k, lse2, scaling, pooled, ragged=rg)
             n_valid = self._scratch("n_valid", (B, G, T), torch.int32, dev)
             k_row = self._scratch("k_row", (B, G, T), torch.int32, dev)
-            nat.prefill_budgets(n_valid, k_row, B, G, T, kk, self.k, self.rolling_prefill and L > 128)
+            if ragged is None:
+                nat.prefill_budgets(n_valid, k_row, B, G, T, kk, self.k, self.rolling_prefill and L > 128)
+            else:
+                nat.prefill_budgets_ragged(n_valid, k_row, ragged[1], B, G, T, kk, self.k, self.rolling_prefill)
             self._tile_idx = self._scratch("tile_idx", (B, G, T, max(kk, 1)), torch.int32, dev)
             self._tile_count = self._scratch("tile_count", (B, G, T), torch.int32, dev)
             nat.topk_select(pooled, n_valid, k_row, kk, self._tile_idx, self._tile_count, n_cols=L)
@@ -341,7 +367,7 @@ class EfficientKascadeStrategy(Strategy):
             if self._tile_idx is None:
                 raise RuntimeError("reuse layer called before any anchor layer")
             head_map = self._mapping(layer, dev)
-        nat.prefill_sparse(q, k, v, self._tile_idx, self._tile_count, head_map, scaling, out, fanout=fan)
+        nat.prefill_sparse(q, k, v, self._tile_idx, self._tile_count, head_map, scaling, out, fanout=fan, ragged=rg)
         return self._publish(out)
 
     def _publish(self, out: torch.Tensor) -> torch.Tensor:
@@ -404,7 +430,14 @@ class EfficientKascadeStrategy(Strategy):
                 self._peer_store, self._exchange = False, "nccl"
                 return None
             n = self._copies
-            if self._exchange == "push":
+            if self._exchange == "multicast" and not (self._peer.multicast and all(self._peer.multicast)):
+                import warnings
+                warnings.warn("no NVLink multicast mapping for the output buffers: exchange 'multicast' -> 'peer_store'")
+                self._exchange = "peer_store"
+            if self._exchange == "multicast":
+                self._peer_fans = [nat.out_fanout([self._peer.multicast[c]], H * world, rank * H, multicast=True)
+                                   for c in range(n)]
+            elif self._exchange == "push":
                 self._peer_fans = [nat.out_fanout([self._peer.pointers[c][rank]], H * world, rank * H) for c in range(n)]
                 streams = [torch.cuda.Stream(device=dev) for _ in range(world - 1)]
                 done = [[torch.cuda.Event() for _ in range(world - 1)] for _ in range(n)]

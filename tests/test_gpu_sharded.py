@@ -53,14 +53,14 @@ def _worker(rank, world, port, ret, exchange):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["nccl", "peer_store", "push"])
+@pytest.mark.parametrize("exchange", ["nccl", "peer_store", "push", "multicast"])
 def test_sharded_prefill_matches_unsharded(exchange):
     """Outputs of every layer, gathered by an NCCL all-gather, by the kernels' own peer stores, or by copy-engine
     pushes on side streams, equal the unsharded strategy's bit for bit."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
-    port = 29600 + (os.getpid() % 1000) + {"nccl": 0, "peer_store": 500, "push": 1000}[exchange]
+    port = 29600 + (os.getpid() % 1000) + {"nccl": 0, "peer_store": 500, "push": 1000, "multicast": 1500}[exchange]
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, port, ret, exchange), nprocs=world, join=True)
