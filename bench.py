@@ -364,7 +364,11 @@ def bench_decode(args, dev, world, peaks, batch=None, ragged=False, rank=0):
               "reuse_layer_us": t_reuse,
               "roofline": {"kernel": "decode_attn_kernel<sparse>", "bound": "hbm", "achieved": gbs_reuse,
                            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs_reuse / peaks["hbm_gbs"],
-                           "traffic": None, "peak_source": peaks["source"]},
+                           # dram__bytes_read + write of the ncu capture at batch 8, context 32 768 (110.5 MB per launch,
+                           # profiles/decode_sparse_paged_ncu.md), scaled by the gathered keys: every row is touched once
+                           "traffic": (110.5e6 * dw.bytes_reuse() / DecodeWorkload(batch=8).bytes_reuse()),
+                           "traffic_note": "bytes per launch, ncu capture at batch 8 scaled by the gathered keys",
+                           "peak_source": peaks["source"]},
               "dense_layer_us": t_dense, "dense_us_per_step": t_dense * dw.layers,
               "dense_layer_gbs": 2 * dw.bytes_dense_k() / (t_dense * 1e-6) / 1e9,
               "speedup_vs_dense": t_dense * dw.layers / us_step}

@@ -1081,7 +1081,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
       {
         const int tok = it.tile_start + (key_lane >> 2);
         lse_s[key_lane] =
-            tok < it.L ? p.lse2_in[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (key_lane & 3)] : INFINITY;
+            tok < it.L ? -p.lse2_in[((int64_t)it.b * p.L + tok) * p.H + it.g * kHg + (key_lane & 3)] : -INFINITY;
         mbar_arrive(&sh.bar_lse[wg]);
         ok = mbar_wait(&sh.bar_lse[wg], tiles_seen & 1, &give_up, 43);
         if (!ok) break;
@@ -1092,7 +1092,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         ok = mbar_wait(&bar_sfull[wg], (done_mine + jj) & 1, &give_up, 41);
         if (!ok) break;
         tc_fence_after();
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        uint64_t a01 = 0ull, a23 = 0ull;                    // four partial sums, two per register pair
+        const uint64_t scale_2 = pair_f(p.scale2, p.scale2);
         uint32_t sr[4][32];
 #pragma unroll
         for (int part = 0; part < 4; ++part) tmem_ld32(ts + part * 32, sr[part]);
@@ -1104,12 +1105,16 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             // the four rows' lse2 with one 16-byte shared-memory load (the same address for the whole warp)
-            const float4 l4 = reinterpret_cast<const float4*>(lse_s)[part * 8 + (i >> 2)];
-            a0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -l4.x));
-            a1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -l4.y));
-            a2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -l4.z));
-            a3 += ex2_fma(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -l4.w));
+            const float4 l4 = reinterpret_cast<const float4*>(lse_s)[part * 8 + (i >> 2)];   // holds -lse2
+            float x0, x1, x2, x3;
+            unpair_f(fma2(pair_u(sr[part][i], sr[part][i + 1]), scale_2, pair_f(l4.x, l4.y)), x0, x1);
+            unpair_f(fma2(pair_u(sr[part][i + 2], sr[part][i + 3]), scale_2, pair_f(l4.z, l4.w)), x2, x3);
+            a01 = add2(a01, pair_f(ex2(x0), ex2(x1)));
+            a23 = add2(a23, pair_f(ex2(x2), ex2_fma(x3)));
           }
+        float a0, a1, a2, a3;
+        unpair_f(a01, a0, a1);
+        unpair_f(a23, a2, a3);
         const int key = j * 128 + key_lane;
         if (key < it.tile_start) prow[key] = (a0 + a1) + (a2 + a3);
       }
