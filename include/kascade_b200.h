@@ -30,6 +30,13 @@
 extern "C" {
 #endif
 
+/* storage types of activations and KV caches (field `dtype` of the layouts; 0 = fp16, so a zero-initialised
+ * layout is fp16).  bf16 is the native type of Qwen3; both go through the same tensor-core path
+ * (tcgen05 kind::f16 / mma.sync), probabilities are rounded to the activations' type, accumulation is fp32,
+ * outputs are written in the activations' type.  kb200_kv_write is fp16 only. */
+#define KB200_FP16 0
+#define KB200_BF16 1
+
 #define KB200_HEAD_DIM 128
 #define KB200_GROUP_SIZE 4
 #define KB200_TILE 32
@@ -86,8 +93,8 @@ int kb200_topk_select(const float* scores, int64_t row_stride, int n_cols, const
  * [B, G, L, D]: block_table = NULL, stride_batch = G*L*D, stride_page = page_size*D,
  * stride_token = D, stride_head = L*D. */
 typedef struct kb200_kv_layout {
-  const void* k;              /* fp16 */
-  const void* v;              /* fp16, may be NULL where a call says so */
+  const void* k;              /* fp16 or bf16, see dtype */
+  const void* v;              /* same type as k, may be NULL where a call says so */
   int64_t stride_batch;
   int64_t stride_page;
   int64_t stride_token;
@@ -95,6 +102,7 @@ typedef struct kb200_kv_layout {
   const int32_t* block_table; /* [B, block_table_stride] or NULL */
   int32_t block_table_stride;
   int32_t page_size;          /* power of two, >= 1 */
+  int32_t dtype;              /* KB200_FP16 / KB200_BF16: type of the cache, of q and of the output of a decode call */
 } kb200_kv_layout;
 
 /* Workspace for kb200_decode_sparse_paged / kb200_decode_anchor_paged (split-K partials). */
@@ -175,10 +183,11 @@ int kb200_decode_anchor_paged(const void* q, int64_t q_stride_b, int64_t q_strid
 /* Token-major activations: element (b, token, head, d) at
  *   base + b*stride_b + token*stride_t + head*stride_h + d. */
 typedef struct kb200_act_layout {
-  const void* ptr; /* fp16 */
+  const void* ptr; /* fp16 or bf16, see dtype */
   int64_t stride_b;
   int64_t stride_t;
   int64_t stride_h;
+  int32_t dtype;   /* KB200_FP16 / KB200_BF16; q, k and v of a call must agree, `out` is written in the same type */
 } kb200_act_layout;
 
 /* Dense causal attention of a whole prompt, one CTA per (32-query tile, KV head, batch).

@@ -17,6 +17,8 @@ LIB_PATH = os.path.join(_HERE, "libkascade_b200.so")
 HEAD_DIM = 128
 GROUP_SIZE = 4
 TILE = 32
+FP16, BF16 = 0, 1                     # KB200_FP16 / KB200_BF16
+DTYPES = {torch.float16: FP16, torch.bfloat16: BF16}
 
 EXPORTS = [
     "kb200_init", "kb200_last_error", "kb200_abi_version", "kb200_topk_select",
@@ -37,12 +39,12 @@ class KvLayout(C.Structure):
     _fields_ = [("k", C.c_void_p), ("v", C.c_void_p), ("stride_batch", C.c_int64),
                 ("stride_page", C.c_int64), ("stride_token", C.c_int64), ("stride_head", C.c_int64),
                 ("block_table", C.c_void_p), ("block_table_stride", C.c_int32),
-                ("page_size", C.c_int32)]
+                ("page_size", C.c_int32), ("dtype", C.c_int32)]
 
 
 class ActLayout(C.Structure):
     _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_t", C.c_int64),
-                ("stride_h", C.c_int64)]
+                ("stride_h", C.c_int64), ("dtype", C.c_int32)]
 
 
 MAX_FANOUT = 8
@@ -224,6 +226,13 @@ def _want(t: torch.Tensor, dtype, name: str):
         raise KascadeNativeError(f"{name}: expected a CUDA {dtype} tensor, got {t.dtype} on {t.device}")
 
 
+def _half_code(t: torch.Tensor, name: str) -> int:
+    """KB200_FP16 / KB200_BF16 of a CUDA fp16 or bf16 tensor."""
+    if t.dtype not in DTYPES or not t.is_cuda:
+        raise KascadeNativeError(f"{name}: expected a CUDA fp16 or bf16 tensor, got {t.dtype} on {t.device}")
+    return DTYPES[t.dtype]
+
+
 # ------------------------------------------------------------------------------------------------
 @_on_device_of(0)
 def topk_select(scores: torch.Tensor, n_valid: Optional[torch.Tensor], k_row: Optional[torch.Tensor],
@@ -259,24 +268,24 @@ def prefill_budgets_ragged(n_valid, k_row, seq_len, batch, groups, tiles, k_cap,
 
 def kv_layout_paged(k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], block_table: torch.Tensor) -> KvLayout:
     """vLLM-style cache [num_pages, page_size, G, D] and block table [B, max_pages] int32."""
-    _want(k_cache, torch.float16, "k_cache")
+    code = _half_code(k_cache, "k_cache")
     assert k_cache.dim() == 4 and k_cache.stride(3) == 1
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     if v_cache is not None:
-        assert v_cache.shape == k_cache.shape and v_cache.stride() == k_cache.stride()
+        assert v_cache.shape == k_cache.shape and v_cache.stride() == k_cache.stride() and v_cache.dtype == k_cache.dtype
     return KvLayout(k_cache.data_ptr(), 0 if v_cache is None else v_cache.data_ptr(), 0, k_cache.stride(0),
                     k_cache.stride(1), k_cache.stride(2), block_table.data_ptr(), block_table.stride(0),
-                    k_cache.shape[1])
+                    k_cache.shape[1], code)
 
 
 def kv_layout_contiguous(k: torch.Tensor, v: Optional[torch.Tensor], page_size: int = 16) -> KvLayout:
     """HF cache view [B, G, L, D] (any batch / head / token strides, D contiguous)."""
-    _want(k, torch.float16, "k")
+    code = _half_code(k, "k")
     assert k.dim() == 4 and k.stride(3) == 1
     if v is not None:
-        assert v.shape == k.shape and v.stride() == k.stride()
+        assert v.shape == k.shape and v.stride() == k.stride() and v.dtype == k.dtype
     return KvLayout(k.data_ptr(), 0 if v is None else v.data_ptr(), k.stride(0), k.stride(2) * page_size,
-                    k.stride(2), k.stride(1), 0, 0, page_size)
+                    k.stride(2), k.stride(1), 0, 0, page_size, code)
 
 
 def decode_workspace(batch: int, heads: int, splits: int, device) -> torch.Tensor:
@@ -294,8 +303,9 @@ def decode_sparse_paged(q, kv: KvLayout, topk_idx, topk_count, k_max, head_map, 
                         workspace=None, num_splits=0):
     """q [B,H,D] fp16; topk_idx [B,G,kstride] int32; out [B,H,D] fp16 contiguous."""
     lib = init(q.device.index)
-    _want(q, torch.float16, "q")
-    _want(out, torch.float16, "out")
+    if _half_code(q, "q") != kv.dtype:
+        raise KascadeNativeError(f"q is {q.dtype} but the KV cache has dtype code {kv.dtype}")
+    _want(out, q.dtype, "out")
     _want(topk_idx, torch.int32, "topk_idx")
     _want_opt(topk_count, torch.int32, "topk_count")
     _want_opt(head_map, torch.int32, "head_map")
@@ -321,8 +331,9 @@ def decode_sparse_paged_noalloc(q, kv: KvLayout, topk_idx, topk_count, k_max, he
     partials live in a fixed array inside the library (batch * heads * splits <= NOALLOC_MAX_SLOTS).
     Calls that overlap on the GPU race on that array; the first call on a device belongs in set-up."""
     lib = init(q.device.index)
-    _want(q, torch.float16, "q")
-    _want(out, torch.float16, "out")
+    if _half_code(q, "q") != kv.dtype:
+        raise KascadeNativeError(f"q is {q.dtype} but the KV cache has dtype code {kv.dtype}")
+    _want(out, q.dtype, "out")
     _want(topk_idx, torch.int32, "topk_idx")
     _want_opt(topk_count, torch.int32, "topk_count")
     _want_opt(head_map, torch.int32, "head_map")
@@ -341,7 +352,9 @@ def decode_anchor_paged(q, kv: KvLayout, seq_lens, max_seq_len, scale, logits, p
                         workspace=None, num_splits=0):
     """q [B,H,D]; logits [B,H,stride] fp32; pooled [B,G,stride] fp32; out [B,H,D] fp16 or None."""
     lib = init(q.device.index)
-    _want(q, torch.float16, "q")
+    if _half_code(q, "q") != kv.dtype:
+        raise KascadeNativeError(f"q is {q.dtype} but the KV cache has dtype code {kv.dtype}")
+    _want_opt(out, q.dtype, "out")
     _want(logits, torch.float32, "logits")
     _want(pooled, torch.float32, "pooled")
     B, H, D = q.shape
@@ -358,9 +371,9 @@ def decode_anchor_paged(q, kv: KvLayout, seq_lens, max_seq_len, scale, logits, p
 
 def act_layout(x: torch.Tensor) -> ActLayout:
     """x indexed [B, L, heads, D] (any strides, D contiguous)."""
-    _want(x, torch.float16, "activation")
+    code = _half_code(x, "activation")
     assert x.dim() == 4 and x.stride(3) == 1 and x.shape[3] == HEAD_DIM
-    return ActLayout(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2))
+    return ActLayout(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2), code)
 
 
 @_on_device_of(0)
@@ -372,10 +385,10 @@ def prefill_dense(q, k, v, scale, out, lse2, fanout: Optional[OutFanout] = None,
     B, L, H, _ = q.shape
     G = k.shape[2]
     ql, kl = act_layout(q), act_layout(k)
-    vl = act_layout(v) if v is not None else ActLayout(0, 0, 0, 0)
+    vl = act_layout(v) if v is not None else ActLayout(0, 0, 0, 0, 0)
     if ragged is not None:
         if out is not None:
-            _want(out, torch.float16, "out")
+            _want(out, q.dtype, "out")
             assert out.is_contiguous()
         _check(lib.kb200_prefill_dense_ragged(C.byref(ql), C.byref(kl), C.byref(vl), float(scale), _ptr(out), _ptr(lse2),
                                               C.byref(ragged), B, L, H, G, _stream()), "kb200_prefill_dense_ragged")
@@ -387,7 +400,7 @@ def prefill_dense(q, k, v, scale, out, lse2, fanout: Optional[OutFanout] = None,
         _launched(1)
         return
     if out is not None:
-        _want(out, torch.float16, "out")
+        _want(out, q.dtype, "out")
         assert out.is_contiguous()
     _check(lib.kb200_prefill_dense(C.byref(ql), C.byref(kl), C.byref(vl), float(scale), _ptr(out), _ptr(lse2),
                                    B, L, H, G, _stream()), "kb200_prefill_dense")
@@ -435,7 +448,7 @@ def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=Non
                                                _stream()), "kb200_prefill_sparse_fanout")
         _launched(1)
         return
-    _want(out, torch.float16, "out")
+    _want(out, q.dtype, "out")
     assert out.is_contiguous()
     if ragged is not None:
         _check(lib.kb200_prefill_sparse_ragged(C.byref(ql), C.byref(kl), C.byref(vl), _ptr(tile_idx), tile_idx.shape[-1],
@@ -458,7 +471,7 @@ def kv_write(q_in, q_out, k_new, v_new, start_pos, n_new, kv: KvLayout, q_gain=N
     lib = init(k_new.device.index)
     B, T, G, _ = k_new.shape
     kl, vl = act_layout(k_new), act_layout(v_new)
-    ql = act_layout(q_in) if q_in is not None else ActLayout(0, 0, 0, 0)
+    ql = act_layout(q_in) if q_in is not None else ActLayout(0, 0, 0, 0, 0)
     H = q_in.shape[2] if q_in is not None else 0
     if q_in is not None:
         _want(q_out, torch.float16, "q_out")

@@ -56,7 +56,7 @@ int check_on_current_device(const void* ptr, const char* what) {
 
 }  // namespace kb200
 
-extern "C" int kb200_abi_version(void) { return 1; }
+extern "C" int kb200_abi_version(void) { return 2; }
 
 extern "C" const char* kb200_last_error(void) { return kb200::g_err; }
 

@@ -12,6 +12,8 @@
 // Replaces kernels/flash_decoding/reuse_kascade_gqa_decode.py:50-200 (gathered split-K decode and
 // its combine) and recompute_kascade_gqa_decode.py:49-315 (dense split-K pass with raw-score dump,
 // combine, per-KV-head pooled score).
+#include <cuda_bf16.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -48,6 +50,7 @@ struct DecodeParams {
   float* ws_l;                   // [B,H,S]
   float* ws_o;                   // [B,H,S,D]
   int32_t H, G, num_splits;
+  int32_t bf16;                  // host side: cache, q and the output are bf16, not fp16
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -71,23 +74,43 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
+template <bool BF16>
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  if (BF16) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
 }
+template <bool BF16>
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  if (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
+}
+// one output element in the storage type
+template <bool BF16>
+__device__ __forceinline__ void store_half(__half* dst, float x) {
+  if (BF16) *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16_rn(x);
+  else *dst = __float2half_rn(x);
 }
 
 // byte offset of 16-byte chunk `c` of row `r` inside a [16 rows x 256 B] sub-tile buffer
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 256 + ((c ^ (r & 7)) << 4)); }
 
-template <bool DENSE, bool HAS_V, bool WRITE_LOGITS>
+template <bool DENSE, bool HAS_V, bool WRITE_LOGITS, bool BF16>
 __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
@@ -202,8 +225,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
         int r = nt * 8 + (lane & 7);
         int c = kk * 4 + (lane >> 3);
         ldmatrix_x4(bfr, kbuf + swz(r, c));
-        mma16816(s[nt], qa0[kk * 2], 0u, qa2[kk * 2], 0u, bfr[0], bfr[1]);
-        mma16816(s[nt], qa0[kk * 2 + 1], 0u, qa2[kk * 2 + 1], 0u, bfr[2], bfr[3]);
+        mma16816<BF16>(s[nt], qa0[kk * 2], 0u, qa2[kk * 2], 0u, bfr[0], bfr[1]);
+        mma16816<BF16>(s[nt], qa0[kk * 2 + 1], 0u, qa2[kk * 2 + 1], 0u, bfr[2], bfr[3]);
       }
     }
     // ---- scale, mask the tail, dump logits ----------------------------------------------------
@@ -239,8 +262,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
       float p00 = exp2f(s[0][0] - m_new), p01 = exp2f(s[0][1] - m_new);
       float p10 = exp2f(s[1][0] - m_new), p11 = exp2f(s[1][1] - m_new);
       psum = p00 + p01 + p10 + p11;
-      pa0 = pack_half2(p00, p01);
-      pa2 = pack_half2(p10, p11);
+      pa0 = pack_half2<BF16>(p00, p01);
+      pa2 = pack_half2<BF16>(p10, p11);
     }
     psum += __shfl_xor_sync(0xFFFFFFFFu, psum, 1);
     psum += __shfl_xor_sync(0xFFFFFFFFu, psum, 2);
@@ -257,8 +280,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
         ldmatrix_x4_trans(bfr, vbuf + swz(r, c));
 #pragma unroll
         for (int e = 0; e < 4; ++e) { o_acc[dt * 2][e] *= alpha; o_acc[dt * 2 + 1][e] *= alpha; }
-        mma16816(o_acc[dt * 2], pa0, 0u, pa2, 0u, bfr[0], bfr[1]);
-        mma16816(o_acc[dt * 2 + 1], pa0, 0u, pa2, 0u, bfr[2], bfr[3]);
+        mma16816<BF16>(o_acc[dt * 2], pa0, 0u, pa2, 0u, bfr[0], bfr[1]);
+        mma16816<BF16>(o_acc[dt * 2 + 1], pa0, 0u, pa2, 0u, bfr[2], bfr[3]);
       }
     }
   }
@@ -296,7 +319,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
     }
     const int64_t bh = (int64_t)b * p.H + g * kHg + h;
     if (p.num_splits == 1) {
-      if (HAS_V) p.out[bh * kD + d] = __float2half_rn(L > 0.f ? O / L : 0.f);
+      if (HAS_V) store_half<BF16>(p.out + bh * kD + d, L > 0.f ? O / L : 0.f);
       if (d == 0 && p.lse2) p.lse2[bh] = L > 0.f ? M + log2f(L) : -INFINITY;
     } else {
       const int64_t slot = bh * p.num_splits + split;
@@ -307,7 +330,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
 }
 
 // merge the split partials: grid (H, B), 128 threads (one per output element)
-template <bool HAS_V>
+template <bool HAS_V, bool BF16>
 __global__ void __launch_bounds__(kD) decode_combine_kernel(const float* __restrict__ ws_m,
                                                             const float* __restrict__ ws_l,
                                                             const float* __restrict__ ws_o,
@@ -325,7 +348,7 @@ __global__ void __launch_bounds__(kD) decode_combine_kernel(const float* __restr
     L += ws_l[bh * num_splits + s] * f;
     if (HAS_V) O += ws_o[(bh * num_splits + s) * kD + d] * f;
   }
-  if (HAS_V) out[bh * kD + d] = __float2half_rn(L > 0.f ? O / L : 0.f);
+  if (HAS_V) store_half<BF16>(out + bh * kD + d, L > 0.f ? O / L : 0.f);
   if (d == 0 && lse2) lse2[bh] = L > 0.f ? M + log2f(L) : -INFINITY;
 }
 
@@ -362,11 +385,17 @@ __global__ void __launch_bounds__(256) decode_pool_kernel(const float* __restric
 }
 
 int init_decode() {
-  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<false, true, false>,
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<false, true, false, false>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
-  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, true, true>,
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, true, true, false>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
-  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, false, true>,
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, false, true, false>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<false, true, false, true>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, true, true, true>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, false, true, true>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
   return 0;
 }
@@ -382,6 +411,8 @@ static int fill_kv(DecodeParams& p, const kb200_kv_layout* kv, bool need_v) {
   KB_REQUIRE(kv->stride_batch % 8 == 0 && kv->stride_page % 8 == 0 && kv->stride_token % 8 == 0 &&
                  kv->stride_head % 8 == 0,
              "decode: KV strides must be multiples of 8 elements (16 bytes)");
+  KB_REQUIRE(kv->dtype == KB200_FP16 || kv->dtype == KB200_BF16, "decode: unknown dtype code %d of the KV cache", kv->dtype);
+  p.bf16 = kv->dtype == KB200_BF16;
   p.k = static_cast<const __half*>(kv->k);
   p.v = static_cast<const __half*>(kv->v);
   p.kv_stride_batch = kv->stride_batch;
@@ -516,11 +547,16 @@ extern "C" int kb200_decode_sparse_paged(const void* q, int64_t q_stride_b, int6
   p.num_splits = splits;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(splits, num_kv_heads, batch);
-  decode_attn_kernel<false, true, false><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  if (p.bf16) decode_attn_kernel<false, true, false, true><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else decode_attn_kernel<false, true, false, false><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
   KB_CHECK_LAUNCH("decode_attn_kernel<sparse>");
   if (splits > 1) {
-    decode_combine_kernel<true><<<dim3(num_q_heads, batch), kD, 0, st>>>(
-        p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2, num_q_heads, splits);
+    if (p.bf16)
+      decode_combine_kernel<true, true><<<dim3(num_q_heads, batch), kD, 0, st>>>(p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2,
+                                                                                 num_q_heads, splits);
+    else
+      decode_combine_kernel<true, false><<<dim3(num_q_heads, batch), kD, 0, st>>>(p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2,
+                                                                                  num_q_heads, splits);
     KB_CHECK_LAUNCH("decode_combine_kernel");
   }
   return 0;
@@ -569,20 +605,21 @@ extern "C" int kb200_decode_anchor_paged(const void* q, int64_t q_stride_b, int6
   p.num_splits = splits;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(splits, num_kv_heads, batch);
-  if (has_v) {
-    decode_attn_kernel<true, true, true><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  } else {
-    decode_attn_kernel<true, false, true><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  }
+  if (has_v && p.bf16) decode_attn_kernel<true, true, true, true><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else if (has_v) decode_attn_kernel<true, true, true, false><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else if (p.bf16) decode_attn_kernel<true, false, true, true><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else decode_attn_kernel<true, false, true, false><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
   KB_CHECK_LAUNCH("decode_attn_kernel<dense>");
   if (splits > 1) {
-    if (has_v) {
-      decode_combine_kernel<true><<<dim3(num_q_heads, batch), kD, 0, st>>>(
-          p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2, num_q_heads, splits);
-    } else {
-      decode_combine_kernel<false><<<dim3(num_q_heads, batch), kD, 0, st>>>(
-          p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2, num_q_heads, splits);
-    }
+    if (has_v && p.bf16)
+      decode_combine_kernel<true, true><<<dim3(num_q_heads, batch), kD, 0, st>>>(p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2,
+                                                                                 num_q_heads, splits);
+    else if (has_v)
+      decode_combine_kernel<true, false><<<dim3(num_q_heads, batch), kD, 0, st>>>(p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2,
+                                                                                  num_q_heads, splits);
+    else
+      decode_combine_kernel<false, false><<<dim3(num_q_heads, batch), kD, 0, st>>>(p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2,
+                                                                                   num_q_heads, splits);
     KB_CHECK_LAUNCH("decode_combine_kernel");
   }
   if (max_seq_len > 0) {
@@ -647,11 +684,16 @@ extern "C" int kb200_decode_sparse_paged_noalloc(const void* q, int64_t q_stride
   p.num_splits = splits;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(splits, num_kv_heads, batch);
-  decode_attn_kernel<false, true, false><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  if (p.bf16) decode_attn_kernel<false, true, false, true><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else decode_attn_kernel<false, true, false, false><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
   KB_CHECK_LAUNCH("decode_attn_kernel<sparse, noalloc>");
   if (splits > 1) {
-    decode_combine_kernel<true><<<dim3(num_q_heads, batch), kD, 0, st>>>(p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2,
-                                                                       num_q_heads, splits);
+    if (p.bf16)
+      decode_combine_kernel<true, true><<<dim3(num_q_heads, batch), kD, 0, st>>>(p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2,
+                                                                                 num_q_heads, splits);
+    else
+      decode_combine_kernel<true, false><<<dim3(num_q_heads, batch), kD, 0, st>>>(p.ws_m, p.ws_l, p.ws_o, p.out, p.lse2,
+                                                                                  num_q_heads, splits);
     KB_CHECK_LAUNCH("decode_combine_kernel<noalloc>");
   }
   return 0;

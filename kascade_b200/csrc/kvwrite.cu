@@ -131,6 +131,9 @@ extern "C" int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const k
   KB_REQUIRE(k_new && k_new->ptr && v_new && v_new->ptr && start_pos && kv && kv->k && kv->v,
              "kv_write: null pointer");
   KB_REQUIRE(batch >= 0 && max_new >= 0 && num_kv_heads > 0 && num_q_heads >= 0, "kv_write: bad sizes");
+  KB_REQUIRE(k_new->dtype == KB200_FP16 && v_new->dtype == KB200_FP16 && kv->dtype == KB200_FP16 &&
+                 (!q_in || !q_in->ptr || q_in->dtype == KB200_FP16),
+             "kv_write: fp16 only (its arithmetic follows the Hugging Face fp16 modules step by step)");
   KB_REQUIRE(kv->page_size >= 1 && (kv->page_size & (kv->page_size - 1)) == 0,
              "kv_write: page_size must be a power of two (got %d)", kv->page_size);
   KB_REQUIRE(!inv_freq || (reinterpret_cast<uintptr_t>(inv_freq) & 7) == 0, "kv_write: inv_freq must be 8-byte aligned");

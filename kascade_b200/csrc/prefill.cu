@@ -41,6 +41,8 @@
 #include <atomic>
 #include <mutex>
 
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 #include "umma.cuh"
 
@@ -64,6 +66,7 @@ struct PrefillParams {
   const int32_t* tile_count;
   const int32_t* head_map;
   float scale2;
+  int bf16;                       // host side: the activations (and the outputs) are bf16, not fp16
   __half* out;                    // == out_fan[0] unless the output goes to several GPUs
   __half* out_fan[KB200_MAX_FANOUT];   // outputs [B, L, H_out, D]: this GPU's own buffer and its peers'
   int n_fan, H_out, h_off;        // number of outputs, heads of an output row, first head written by this call
@@ -154,7 +157,13 @@ __device__ __forceinline__ void multimem_st16(void* mc_addr, uint4 v) {
                "f"(__uint_as_float(v.w))
                : "memory");
 }
+// two fp32 values -> one 32-bit pair in the storage type of the activations (fp16, or bf16 when BF16)
+template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
 }
@@ -243,7 +252,7 @@ struct PfCfg {
   static constexpr int kMmaWarp = kGather ? 12 : (kHasV ? 9 : 13);
 };
 
-template <int MODE>
+template <int MODE, bool BF16>
 __global__ void __launch_bounds__(PfCfg<MODE>::kThreads, 1)
 tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_constant__ CUtensorMap tm_q,
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
@@ -484,7 +493,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   // phases back: the issuer of block n passes a token to the other one as soon as its own "S buffer
   // free" wait is over, and the other one starts its waits for block n+1 only then.
   auto mma_role = [&](const int me) {
-    constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
+    constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0, BF16);
     constexpr int NS = Cfg::kStreams;                   // S buffers = softmax streams; block j goes to buffer j % NS
     constexpr int kIssuers = Cfg::kIssuers;
     int k_st = 0, k_ph = 0, qn = 0, gb = 0, turns = 0;  // K ring, Q tiles, global block count, tokens taken
@@ -561,7 +570,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
   // Products of different warps are not ordered; every dependency between them goes through a
   // barrier (S consumed -> next Q.K^T into that buffer; P written -> P.V; P.V done -> P rewritten).
   auto mma_qk_v = [&]() {
-    constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0);
+    constexpr uint32_t idesc_qk = idesc_f16(128, 128, 0, 0, BF16);
     constexpr uint32_t kStage16 = kStageBytes >> 4;      // descriptor address units are 16 bytes
     const uint32_t q_lo = desc_lo(q_s, 16), k_lo0 = desc_lo(k_s, 16);
     int k_st = 0, k_ph = 0, qn = 0;                      // K ring position / parity, Q tiles seen
@@ -635,7 +644,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
     }
   };
   auto mma_pv_v = [&]() {
-    constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1);
+    constexpr uint32_t idesc_pv = idesc_f16(128, 128, 0, 1, BF16);
     constexpr uint32_t kStage16 = kStageBytes >> 4;
     const uint32_t t_acc = tmem + 384, t_p = tmem + 256;
     const uint32_t v_lo0 = desc_lo(v_s, kStageBytes / 2);
@@ -810,8 +819,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
               a0 = ex2(a0); a1 = ex2(a1); a2 = ex2(a2); a3 = ex2(a3);
               s01 = add2(s01, pair_f(a0, a1));
               s23 = add2(s23, pair_f(a2, a3));
-              pr[i] = pack2(a0, a1);
-              pr[i + 1] = pack2(a2, a3);
+              pr[i] = pack2<BF16>(a0, a1);
+              pr[i + 1] = pack2<BF16>(a2, a3);
             }
             tmem_st16(tp + part * 16, pr);                 // P columns [part*16, +16) = keys [part*32, +32)
           }
@@ -828,8 +837,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
               float a2 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 2]), p.scale2, -ref));
               float a3 = ex2(fmaf(__uint_as_float(sr[part][2 * i + 3]), p.scale2, -ref));
               s0 += a0; s1 += a1; s2 += a2; s3 += a3;
-              pr[i] = pack2(a0, a1);
-              pr[i + 1] = pack2(a2, a3);
+              pr[i] = pack2<BF16>(a0, a1);
+              pr[i + 1] = pack2<BF16>(a2, a3);
             }
             tmem_st16(tp + part * 16, pr);                 // P columns [part*16, +16) = keys [part*32, +32)
           }
@@ -889,10 +898,10 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
         tmem_wait_ld();
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          w[part * 4 + e].x = pack2(__uint_as_float(oa[e * 8 + 0]) * inv, __uint_as_float(oa[e * 8 + 1]) * inv);
-          w[part * 4 + e].y = pack2(__uint_as_float(oa[e * 8 + 2]) * inv, __uint_as_float(oa[e * 8 + 3]) * inv);
-          w[part * 4 + e].z = pack2(__uint_as_float(oa[e * 8 + 4]) * inv, __uint_as_float(oa[e * 8 + 5]) * inv);
-          w[part * 4 + e].w = pack2(__uint_as_float(oa[e * 8 + 6]) * inv, __uint_as_float(oa[e * 8 + 7]) * inv);
+          w[part * 4 + e].x = pack2<BF16>(__uint_as_float(oa[e * 8 + 0]) * inv, __uint_as_float(oa[e * 8 + 1]) * inv);
+          w[part * 4 + e].y = pack2<BF16>(__uint_as_float(oa[e * 8 + 2]) * inv, __uint_as_float(oa[e * 8 + 3]) * inv);
+          w[part * 4 + e].z = pack2<BF16>(__uint_as_float(oa[e * 8 + 4]) * inv, __uint_as_float(oa[e * 8 + 5]) * inv);
+          w[part * 4 + e].w = pack2<BF16>(__uint_as_float(oa[e * 8 + 6]) * inv, __uint_as_float(oa[e * 8 + 7]) * inv);
         }
       }
       // O and the exchange buffer have been read: the next tile's first P.V may overwrite the accumulator
@@ -1231,10 +1240,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 static EncodeTiledFn g_encode_tiled = nullptr;
 
 int init_prefill() {
-  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kDenseAttn>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn));
-  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kSparse>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn));
-  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kDenseLse>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemNoV));
-  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kPool>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemNoV));
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kDenseAttn, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn));
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kSparse, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn));
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kDenseLse, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemNoV));
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kPool, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemNoV));
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kDenseAttn, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn));
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kSparse, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttn));
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kDenseLse, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemNoV));
+  KB_CUDA(cudaFuncSetAttribute(tile_prefill_kernel<kPool, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemNoV));
   if (!g_encode_tiled) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult res;
@@ -1307,6 +1320,7 @@ static int fill_act(const kb200_act_layout* a, const __half** ptr, int64_t* sb, 
   KB_REQUIRE((reinterpret_cast<uintptr_t>(a->ptr) & 15) == 0 && a->stride_b % 8 == 0 && a->stride_t % 8 == 0 &&
                  a->stride_h % 8 == 0,
              "prefill: %s must be 16-byte aligned with strides that are multiples of 8 elements", what);
+  KB_REQUIRE(a->dtype == KB200_FP16 || a->dtype == KB200_BF16, "prefill: %s has an unknown dtype code %d", what, a->dtype);
   *ptr = static_cast<const __half*>(a->ptr);
   *sb = a->stride_b;
   *st = a->stride_t;
@@ -1399,6 +1413,15 @@ extern "C" int kb200_selftest_wait_timeout(int32_t* result, uint64_t limit_ns, i
 }
 
 namespace kb200 {
+// q, k (and v) must share one storage type; the outputs are written in it
+static int same_dtype(PrefillParams* p, const kb200_act_layout* q, const kb200_act_layout* k, const kb200_act_layout* v,
+                      const char* what) {
+  KB_REQUIRE(q->dtype == k->dtype && (!v || !v->ptr || v->dtype == q->dtype),
+             "%s: q, k and v must have the same dtype (codes %d / %d / %d)", what, q->dtype, k->dtype, v ? v->dtype : -1);
+  p->bf16 = q->dtype == KB200_BF16;
+  return 0;
+}
+
 static int set_ragged(PrefillParams* p, const kb200_ragged* rg, const char* what) {
   p->seq_start = nullptr;
   p->seq_len = nullptr;
@@ -1433,10 +1456,15 @@ static int prefill_dense_impl(const kb200_act_layout* q, const kb200_act_layout*
   tv = tk;
   if (out && make_act_map(&tv, p.v, p.v_sb, p.v_st, p.v_sh, num_kv_heads, seq_len, batch, 1, 128, "v") != 0) return -1;
   dim3 grid(persistent_grid(p));
-  if (out)
-    tile_prefill_kernel<kDenseAttn><<<grid, PfCfg<kDenseAttn>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, tq, tk, tv);
+  if (same_dtype(&p, q, k, out ? v : nullptr, "prefill_dense") != 0) return -1;
+  if (out && p.bf16)
+    tile_prefill_kernel<kDenseAttn, true><<<grid, PfCfg<kDenseAttn>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, tq, tk, tv);
+  else if (out)
+    tile_prefill_kernel<kDenseAttn, false><<<grid, PfCfg<kDenseAttn>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, tq, tk, tv);
+  else if (p.bf16)
+    tile_prefill_kernel<kDenseLse, true><<<grid, PfCfg<kDenseLse>::kThreads, kSmemNoV, (cudaStream_t)stream>>>(p, tq, tk, tv);
   else
-    tile_prefill_kernel<kDenseLse><<<grid, PfCfg<kDenseLse>::kThreads, kSmemNoV, (cudaStream_t)stream>>>(p, tq, tk, tv);
+    tile_prefill_kernel<kDenseLse, false><<<grid, PfCfg<kDenseLse>::kThreads, kSmemNoV, (cudaStream_t)stream>>>(p, tq, tk, tv);
   KB_CHECK_LAUNCH("tile_prefill_kernel<dense>");
   return 0;
 }
@@ -1482,7 +1510,11 @@ static int prefill_pool_impl(const kb200_act_layout* q, const kb200_act_layout* 
   if (make_act_map(&tq, p.q, p.q_sb, p.q_st, p.q_sh, num_q_heads, seq_len, batch, kHg, kTile, "q") != 0) return -1;
   if (make_act_map(&tk, p.k, p.k_sb, p.k_st, p.k_sh, num_kv_heads, seq_len, batch, 1, 128, "k") != 0) return -1;
   dim3 grid(persistent_grid(p));
-  tile_prefill_kernel<kPool><<<grid, PfCfg<kPool>::kThreads, kSmemNoV, (cudaStream_t)stream>>>(p, tq, tk, tk);
+  if (same_dtype(&p, q, k, nullptr, "prefill_pool_scores") != 0) return -1;
+  if (p.bf16)
+    tile_prefill_kernel<kPool, true><<<grid, PfCfg<kPool>::kThreads, kSmemNoV, (cudaStream_t)stream>>>(p, tq, tk, tk);
+  else
+    tile_prefill_kernel<kPool, false><<<grid, PfCfg<kPool>::kThreads, kSmemNoV, (cudaStream_t)stream>>>(p, tq, tk, tk);
   KB_CHECK_LAUNCH("tile_prefill_kernel<pool>");
   return 0;
 }
@@ -1550,7 +1582,11 @@ static int prefill_sparse_impl(const kb200_act_layout* q, const kb200_act_layout
   CUtensorMap tq, none{};                                // Q tiles by TMA; the K / V rows are gathered without maps
   if (make_act_map(&tq, p.q, p.q_sb, p.q_st, p.q_sh, num_q_heads, seq_len, batch, kHg, kTile, "q") != 0) return -1;
   dim3 grid(persistent_grid(p));
-  tile_prefill_kernel<kSparse><<<grid, PfCfg<kSparse>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, tq, none, none);
+  if (same_dtype(&p, q, k, v, "prefill_sparse") != 0) return -1;
+  if (p.bf16)
+    tile_prefill_kernel<kSparse, true><<<grid, PfCfg<kSparse>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, tq, none, none);
+  else
+    tile_prefill_kernel<kSparse, false><<<grid, PfCfg<kSparse>::kThreads, kSmemAttn, (cudaStream_t)stream>>>(p, tq, none, none);
   KB_CHECK_LAUNCH("tile_prefill_kernel<sparse>");
   return 0;
 }

@@ -184,10 +184,10 @@ constexpr uint64_t kDescFixed = (1ull << 46) /* descriptor version for sm_100 */
 //   reduction index is 2048 bytes.
 // The low word holds (address >> 4) and (leading offset >> 4) << 16; the high word is the same for all.
 
-// instruction descriptor: fp16 x fp16 -> fp32, M x N tile, operand majors (0 = K-major, 1 = MN)
-__host__ __device__ constexpr uint32_t idesc_f16(int M, int N, int a_mn, int b_mn) {
-  return (1u << 4) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(N >> 3) << 17) |
-         ((uint32_t)(M >> 4) << 24);
+// instruction descriptor: fp16 x fp16 (or bf16 x bf16) -> fp32, M x N tile, operand majors (0 = K-major, 1 = MN)
+__host__ __device__ constexpr uint32_t idesc_f16(int M, int N, int a_mn, int b_mn, bool bf16 = false) {
+  return (1u << 4) | (bf16 ? ((1u << 7) | (1u << 10)) : 0u) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // ---- MMA issue (one thread) ------------------------------------------------------------------------

@@ -237,8 +237,9 @@ class EfficientKascadeStrategy(Strategy):
         causal and unpadded, a decode step attends to the whole cache.  Here the mask is read for one
         thing only, LEFT padding of a batch (leading key positions that no query may see): every
         sequence then goes through the kernels on its own unpadded views, with its own index rows."""
-        if query.dtype != torch.float16:
-            raise nat.KascadeNativeError(f"efficient_kascade computes in fp16; got {query.dtype}")
+        if query.dtype not in nat.DTYPES or key.dtype != query.dtype or value.dtype != query.dtype:
+            raise nat.KascadeNativeError(f"efficient_kascade takes fp16 or bf16 q / k / v of one type; got {query.dtype}, "
+                                         f"{key.dtype}, {value.dtype}")
         B, H, Lq, D = query.shape
         G, Lk = key.shape[1], key.shape[2]
         layer = int(module.layer_idx)
@@ -268,7 +269,7 @@ class EfficientKascadeStrategy(Strategy):
             self.check_status(query.device)
         q, k, v = self._token_major(query), self._token_major(key), self._token_major(value)
         if Lk <= 128:
-            out = torch.empty(B, Lq, H, D, dtype=torch.float16, device=query.device)
+            out = torch.empty(B, Lq, H, D, dtype=query.dtype, device=query.device)
             nat.prefill_dense(q, k, v, scaling, out, None)
             return out, None
         return self._prefill(layer, q, k, v, scaling), None
@@ -306,7 +307,7 @@ class EfficientKascadeStrategy(Strategy):
                                                        rolling_prefill=self.rolling_prefill,
                                                        head_mapping=self._head_mapping, register=False)
                               for _ in range(B)]
-        out = torch.zeros(B, Lq, H, D, dtype=torch.float16, device=query.device)
+        out = torch.zeros(B, Lq, H, D, dtype=query.dtype, device=query.device)
         for b, (s0, n, child) in enumerate(zip(starts, lens, self._children)):
             if n == 0:
                 continue                                                           # nothing to attend to
@@ -330,14 +331,15 @@ class EfficientKascadeStrategy(Strategy):
         G = k.shape[2]
         dev = q.device
         T = -(-L // self.tile_size)
+        self._out_dtype = q.dtype
         fan = self._next_fanout(B, L, H, D, dev) if self._peer_store else None      # None: not in use (or not available)
         rg = nat.ragged(ragged[0], ragged[1]) if ragged is not None else None
         if fan is not None:
             out = None
         elif rg is not None:
-            out = torch.zeros(B, L, H, D, dtype=torch.float16, device=dev)
+            out = torch.zeros(B, L, H, D, dtype=q.dtype, device=dev)
         else:
-            out = torch.empty(B, L, H, D, dtype=torch.float16, device=dev)
+            out = torch.empty(B, L, H, D, dtype=q.dtype, device=dev)
         if self.is_anchor(layer):
             kk = topk_budget(self.k, L, self.tile_size) if ragged is None else \
                 max(1, max(topk_budget(self.k, n, self.tile_size) for n in ragged[2]))
@@ -418,10 +420,10 @@ class EfficientKascadeStrategy(Strategy):
         kb200_out_fanout — every rank's buffer in peer-store mode, this rank's own buffer in push mode."""
         rank, world = self._shard
         shape = (B, L, H * world, D)
-        if self._peer is None or tuple(self._peer.tensors[0].shape) != shape:
+        if self._peer is None or tuple(self._peer.tensors[0].shape) != shape or self._peer.tensors[0].dtype != self._out_dtype:
             from .peer import alloc_peer_buffers
             try:
-                self._peer = alloc_peer_buffers(shape, torch.float16, dev, copies=self._copies)
+                self._peer = alloc_peer_buffers(shape, self._out_dtype, dev, copies=self._copies)
             except RuntimeError as e:
                 # no peer mapping in this job (every rank gets here together): keep the sharded prefill
                 # running with the NCCL all-gather of the outputs
@@ -472,7 +474,7 @@ class EfficientKascadeStrategy(Strategy):
         dev = q.device
         if q.stride(2) != 1 or q.stride(0) % 2 or q.stride(1) % 2:
             q = q.contiguous()
-        out = torch.empty(B, H, D, dtype=torch.float16, device=dev)
+        out = torch.empty(B, H, D, dtype=q.dtype, device=dev)
         splits_a = nat.decode_default_splits(B, G, max_len)
         if dense_only or self.is_anchor(layer):
             stride = -(-max_len // 4) * 4

@@ -10,8 +10,8 @@ def paged_from_contiguous(k, v, page_size=16, seed=0, extra_pages=3):
     total = B * npg + extra_pages
     g = torch.Generator().manual_seed(seed)
     perm = torch.randperm(total, generator=g)[: B * npg].view(B, npg)
-    k_cache = torch.randn(total, page_size, G, D, generator=g).to(torch.float16).to(k.device)
-    v_cache = torch.randn(total, page_size, G, D, generator=g).to(torch.float16).to(k.device)
+    k_cache = torch.randn(total, page_size, G, D, generator=g).to(k.dtype).to(k.device)
+    v_cache = torch.randn(total, page_size, G, D, generator=g).to(k.dtype).to(k.device)
     pad = npg * page_size - L
     kp = torch.nn.functional.pad(k, (0, 0, 0, pad)).view(B, G, npg, page_size, D).permute(0, 2, 3, 1, 4)
     vp = torch.nn.functional.pad(v, (0, 0, 0, pad)).view(B, G, npg, page_size, D).permute(0, 2, 3, 1, 4)

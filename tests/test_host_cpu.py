@@ -19,7 +19,7 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in include/kascade_b200.h but not exported"
     assert sorted(nat.EXPORTS) == [d for d in declared if d in nat.EXPORTS]
     assert set(declared) <= set(nat.EXPORTS), set(declared) - set(nat.EXPORTS)
-    assert lib.kb200_abi_version() == 1
+    assert lib.kb200_abi_version() == 2          # 2: the layouts carry a dtype field (fp16 / bf16)
     assert lib.kb200_decode_workspace_bytes(64, 32, 2) == 64 * 32 * 2 * 130 * 4
 
 
