@@ -36,6 +36,7 @@ extern "C" {
  * outputs are written in the activations' type.  kb200_kv_write is fp16 only. */
 #define KB200_FP16 0
 #define KB200_BF16 1
+#define KB200_FP8_E4M3 2   /* KV caches of the decode calls only, see kb200_kv_layout */
 
 #define KB200_HEAD_DIM 128
 #define KB200_GROUP_SIZE 4
@@ -102,7 +103,19 @@ typedef struct kb200_kv_layout {
   const int32_t* block_table; /* [B, block_table_stride] or NULL */
   int32_t block_table_stride;
   int32_t page_size;          /* power of two, >= 1 */
-  int32_t dtype;              /* KB200_FP16 / KB200_BF16: type of the cache, of q and of the output of a decode call */
+  int32_t dtype;              /* KB200_FP16 / KB200_BF16: type of the cache, of q and of the output of a decode call;
+                                 KB200_FP8_E4M3: the cache holds e4m3 bytes (strides in bytes, multiples of 16), q and
+                                 the output are fp16 */
+  /* FP8 caches: value = stored e4m3 value x scale, one fp32 scale per (page, KV head), K and V separately:
+   *   k_scale[b * scale_stride_batch + page * scale_stride_page + g * scale_stride_head]   (page as in the address
+   * rule above: physical page with a block table).  The kernels turn the stored bytes into fp16 exactly and
+   * apply the scales in fp32 (on the key's logit, on its probability before P.V).  Halves the bytes a decode
+   * step moves.  The reference has no quantised cache. */
+  const float* k_scale;
+  const float* v_scale;
+  int64_t scale_stride_batch;
+  int64_t scale_stride_page;
+  int64_t scale_stride_head;
 } kb200_kv_layout;
 
 /* Workspace for kb200_decode_sparse_paged / kb200_decode_anchor_paged (split-K partials). */

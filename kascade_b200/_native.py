@@ -17,8 +17,9 @@ LIB_PATH = os.path.join(_HERE, "libkascade_b200.so")
 HEAD_DIM = 128
 GROUP_SIZE = 4
 TILE = 32
-FP16, BF16 = 0, 1                     # KB200_FP16 / KB200_BF16
+FP16, BF16, FP8_E4M3 = 0, 1, 2        # KB200_FP16 / KB200_BF16 / KB200_FP8_E4M3
 DTYPES = {torch.float16: FP16, torch.bfloat16: BF16}
+FP8_TORCH = (torch.float8_e4m3fn, torch.uint8)   # an FP8 cache may be handed over as raw bytes
 
 EXPORTS = [
     "kb200_init", "kb200_last_error", "kb200_abi_version", "kb200_topk_select",
@@ -39,7 +40,9 @@ class KvLayout(C.Structure):
     _fields_ = [("k", C.c_void_p), ("v", C.c_void_p), ("stride_batch", C.c_int64),
                 ("stride_page", C.c_int64), ("stride_token", C.c_int64), ("stride_head", C.c_int64),
                 ("block_table", C.c_void_p), ("block_table_stride", C.c_int32),
-                ("page_size", C.c_int32), ("dtype", C.c_int32)]
+                ("page_size", C.c_int32), ("dtype", C.c_int32),
+                ("k_scale", C.c_void_p), ("v_scale", C.c_void_p), ("scale_stride_batch", C.c_int64),
+                ("scale_stride_page", C.c_int64), ("scale_stride_head", C.c_int64)]
 
 
 class ActLayout(C.Structure):
@@ -266,8 +269,30 @@ def prefill_budgets_ragged(n_valid, k_row, seq_len, batch, groups, tiles, k_cap,
     _launched(1)
 
 
-def kv_layout_paged(k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], block_table: torch.Tensor) -> KvLayout:
-    """vLLM-style cache [num_pages, page_size, G, D] and block table [B, max_pages] int32."""
+def _fp8_scales(k_scale, v_scale, need_v: bool):
+    if k_scale is None or (need_v and v_scale is None):
+        raise KascadeNativeError("an FP8 cache needs k_scale (and v_scale): one fp32 scale per (page, KV head)")
+    _want(k_scale, torch.float32, "k_scale")
+    _want_opt(v_scale, torch.float32, "v_scale")
+    if v_scale is not None and (v_scale.shape != k_scale.shape or v_scale.stride() != k_scale.stride()):
+        raise KascadeNativeError("k_scale and v_scale must have the same shape and strides")
+
+
+def kv_layout_paged(k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], block_table: torch.Tensor,
+                    k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None) -> KvLayout:
+    """vLLM-style cache [num_pages, page_size, G, D] and block table [B, max_pages] int32.  An FP8 cache
+    (torch.float8_e4m3fn or raw uint8) comes with k_scale / v_scale [num_pages, G] fp32."""
+    if k_cache.dtype in FP8_TORCH:
+        assert k_cache.is_cuda and k_cache.dim() == 4 and k_cache.stride(3) == 1
+        assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
+        if v_cache is not None:
+            assert v_cache.shape == k_cache.shape and v_cache.stride() == k_cache.stride() and v_cache.dtype == k_cache.dtype
+        _fp8_scales(k_scale, v_scale, v_cache is not None)
+        assert k_scale.shape == (k_cache.shape[0], k_cache.shape[2])
+        return KvLayout(k_cache.data_ptr(), 0 if v_cache is None else v_cache.data_ptr(), 0, k_cache.stride(0),
+                        k_cache.stride(1), k_cache.stride(2), block_table.data_ptr(), block_table.stride(0),
+                        k_cache.shape[1], FP8_E4M3, k_scale.data_ptr(), 0 if v_scale is None else v_scale.data_ptr(),
+                        0, k_scale.stride(0), k_scale.stride(1))
     code = _half_code(k_cache, "k_cache")
     assert k_cache.dim() == 4 and k_cache.stride(3) == 1
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
@@ -278,8 +303,19 @@ def kv_layout_paged(k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], bloc
                     k_cache.shape[1], code)
 
 
-def kv_layout_contiguous(k: torch.Tensor, v: Optional[torch.Tensor], page_size: int = 16) -> KvLayout:
-    """HF cache view [B, G, L, D] (any batch / head / token strides, D contiguous)."""
+def kv_layout_contiguous(k: torch.Tensor, v: Optional[torch.Tensor], page_size: int = 16,
+                         k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None) -> KvLayout:
+    """HF cache view [B, G, L, D] (any batch / head / token strides, D contiguous).  An FP8 cache comes with
+    k_scale / v_scale [B, G, ceil(L / page_size)] fp32."""
+    if k.dtype in FP8_TORCH:
+        assert k.is_cuda and k.dim() == 4 and k.stride(3) == 1
+        if v is not None:
+            assert v.shape == k.shape and v.stride() == k.stride() and v.dtype == k.dtype
+        _fp8_scales(k_scale, v_scale, v is not None)
+        assert k_scale.dim() == 3 and k_scale.shape[:2] == k.shape[:2]
+        return KvLayout(k.data_ptr(), 0 if v is None else v.data_ptr(), k.stride(0), k.stride(2) * page_size,
+                        k.stride(2), k.stride(1), 0, 0, page_size, FP8_E4M3, k_scale.data_ptr(),
+                        0 if v_scale is None else v_scale.data_ptr(), k_scale.stride(0), k_scale.stride(2), k_scale.stride(1))
     code = _half_code(k, "k")
     assert k.dim() == 4 and k.stride(3) == 1
     if v is not None:
@@ -303,8 +339,8 @@ def decode_sparse_paged(q, kv: KvLayout, topk_idx, topk_count, k_max, head_map, 
                         workspace=None, num_splits=0):
     """q [B,H,D] fp16; topk_idx [B,G,kstride] int32; out [B,H,D] fp16 contiguous."""
     lib = init(q.device.index)
-    if _half_code(q, "q") != kv.dtype:
-        raise KascadeNativeError(f"q is {q.dtype} but the KV cache has dtype code {kv.dtype}")
+    if _half_code(q, "q") != (FP16 if kv.dtype == FP8_E4M3 else kv.dtype):
+        raise KascadeNativeError(f"q is {q.dtype} but the KV cache has dtype code {kv.dtype} (an FP8 cache takes fp16 q)")
     _want(out, q.dtype, "out")
     _want(topk_idx, torch.int32, "topk_idx")
     _want_opt(topk_count, torch.int32, "topk_count")
@@ -331,8 +367,8 @@ def decode_sparse_paged_noalloc(q, kv: KvLayout, topk_idx, topk_count, k_max, he
     partials live in a fixed array inside the library (batch * heads * splits <= NOALLOC_MAX_SLOTS).
     Calls that overlap on the GPU race on that array; the first call on a device belongs in set-up."""
     lib = init(q.device.index)
-    if _half_code(q, "q") != kv.dtype:
-        raise KascadeNativeError(f"q is {q.dtype} but the KV cache has dtype code {kv.dtype}")
+    if _half_code(q, "q") != (FP16 if kv.dtype == FP8_E4M3 else kv.dtype):
+        raise KascadeNativeError(f"q is {q.dtype} but the KV cache has dtype code {kv.dtype} (an FP8 cache takes fp16 q)")
     _want(out, q.dtype, "out")
     _want(topk_idx, torch.int32, "topk_idx")
     _want_opt(topk_count, torch.int32, "topk_count")
@@ -352,8 +388,8 @@ def decode_anchor_paged(q, kv: KvLayout, seq_lens, max_seq_len, scale, logits, p
                         workspace=None, num_splits=0):
     """q [B,H,D]; logits [B,H,stride] fp32; pooled [B,G,stride] fp32; out [B,H,D] fp16 or None."""
     lib = init(q.device.index)
-    if _half_code(q, "q") != kv.dtype:
-        raise KascadeNativeError(f"q is {q.dtype} but the KV cache has dtype code {kv.dtype}")
+    if _half_code(q, "q") != (FP16 if kv.dtype == FP8_E4M3 else kv.dtype):
+        raise KascadeNativeError(f"q is {q.dtype} but the KV cache has dtype code {kv.dtype} (an FP8 cache takes fp16 q)")
     _want_opt(out, q.dtype, "out")
     _want(logits, torch.float32, "logits")
     _want(pooled, torch.float32, "pooled")

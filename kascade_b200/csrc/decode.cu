@@ -51,6 +51,11 @@ struct DecodeParams {
   float* ws_o;                   // [B,H,S,D]
   int32_t H, G, num_splits;
   int32_t bf16;                  // host side: cache, q and the output are bf16, not fp16
+  // FP8 (e4m3) cache: one fp32 scale per (page, KV head) for K and for V; q and the output are fp16
+  int32_t fp8;
+  const float* k_scale;
+  const float* v_scale;
+  int64_t sc_stride_batch, sc_stride_page, sc_stride_head;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -110,8 +115,23 @@ __device__ __forceinline__ void store_half(__half* dst, float x) {
 // byte offset of 16-byte chunk `c` of row `r` inside a [16 rows x 256 B] sub-tile buffer
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 256 + ((c ^ (r & 7)) << 4)); }
 
-template <bool DENSE, bool HAS_V, bool WRITE_LOGITS, bool BF16>
+// two e4m3 values (16 bits) -> two fp16 values, exactly
+__device__ __forceinline__ uint32_t fp8x2_to_half2(uint32_t two_bytes) {
+  uint32_t r;
+  asm("{\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, t;\n\t}\n" : "=r"(r) : "r"(two_bytes));
+  return r;
+}
+
+// KV: storage of the cache.  0 fp16, 1 bf16 (q and the output have the same type), 2 FP8 e4m3 with one scale
+// per (page, KV head): rows of 128 bytes are copied as they are, turned into fp16 in shared memory (exact), and
+// the scales are applied in fp32 where a row's contribution appears: on the logit of its key and on its
+// probability before P.V.  q and the output are fp16 then.
+constexpr int kRawStage = kSub * kD * 2;                  // FP8: K + V rows of a sub-tile as stored (4 KB)
+constexpr int kWarpSmemFp8 = kDecStages * kRawStage + kDecStageBytes;   // three raw stages + one fp16 working copy
+
+template <bool DENSE, bool HAS_V, bool WRITE_LOGITS, int KV>
 __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const DecodeParams p) {
+  constexpr bool BF16 = KV == 1, FP8 = KV == 2;
   extern __shared__ __align__(1024) uint8_t smem[];
   const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -152,8 +172,9 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
 
   const int64_t kv_base = (int64_t)b * p.kv_stride_batch + (int64_t)g * p.kv_stride_head;
   const int32_t* table = p.block_table ? p.block_table + (int64_t)b * p.block_table_stride : nullptr;
-  uint8_t* my_smem = smem + warp * kDecStages * kDecStageBytes;
+  uint8_t* my_smem = smem + warp * (FP8 ? kWarpSmemFp8 : kDecStages * kDecStageBytes);
   const uint32_t my_smem_u32 = smem_u32(my_smem);
+  const uint32_t work_u32 = my_smem_u32 + kDecStages * kRawStage;       // FP8: the fp16 copy the MMAs read
 
   // position of key `lane` (lanes 0..15) of sub-tile j of this warp, clamped into the list
   auto load_pos = [&](int j) -> int {
@@ -170,31 +191,60 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
     if (j < my_count) {
       int64_t off = kv_base + (int64_t)page * p.kv_stride_page +
                     (int64_t)(pos & p.page_mask) * p.kv_stride_token;
-      uint32_t dst = my_smem_u32 + (j % kDecStages) * kDecStageBytes;
-      const int c = lane & 15;
+      if (FP8) {
+        // rows of 128 bytes: 8 lanes per row, 4 rows per instruction, stored as they are
+        const uint32_t dst = my_smem_u32 + (j % kDecStages) * kRawStage;
+        const uint8_t* k8 = reinterpret_cast<const uint8_t*>(p.k);
+        const uint8_t* v8 = reinterpret_cast<const uint8_t*>(p.v);
+        const int c = lane & 7;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        int r = i * 2 + (lane >> 4);
-        int64_t roff = __shfl_sync(0xFFFFFFFFu, off, r);
-        cp_async16(dst + swz(r, c), p.k + roff + c * 8);
-        if (HAS_V) cp_async16(dst + kSub * kD * 2 + swz(r, c), p.v + roff + c * 8);
+        for (int i = 0; i < 4; ++i) {
+          int r = i * 4 + (lane >> 3);
+          int64_t roff = __shfl_sync(0xFFFFFFFFu, off, r);
+          cp_async16(dst + r * 128 + c * 16, k8 + roff + c * 16);
+          if (HAS_V) cp_async16(dst + kSub * kD + r * 128 + c * 16, v8 + roff + c * 16);
+        }
+      } else {
+        uint32_t dst = my_smem_u32 + (j % kDecStages) * kDecStageBytes;
+        const int c = lane & 15;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          int r = i * 2 + (lane >> 4);
+          int64_t roff = __shfl_sync(0xFFFFFFFFu, off, r);
+          cp_async16(dst + swz(r, c), p.k + roff + c * 8);
+          if (HAS_V) cp_async16(dst + kSub * kD * 2 + swz(r, c), p.v + roff + c * 8);
+        }
       }
     }
     cp_async_commit();
   };
+  // FP8: scales of the row this lane (0..15) stands for, from the page it lives in
+  const int64_t sc_base = FP8 ? (int64_t)b * p.sc_stride_batch + (int64_t)g * p.sc_stride_head : 0;
+  auto load_scale = [&](int page, float& sk, float& sv) {
+    if (FP8) {
+      const int64_t at = sc_base + (int64_t)page * p.sc_stride_page;
+      sk = __ldg(p.k_scale + at);
+      sv = HAS_V ? __ldg(p.v_scale + at) : 1.f;
+    }
+  };
 
   // ---- software pipeline: positions 2 ahead, pages 1 ahead, copies kDecStages-1 ahead ----------
   int pos_a = 0, page_a = 0, pos_b = 0;
+  float sk0 = 1.f, sv0 = 1.f, sk1 = 1.f, sv1 = 1.f, sk2 = 1.f, sv2 = 1.f;   // FP8: scales of sub-tiles j, j+1, j+2
   // prologue
   {
     int pz = load_pos(0);
     int pgz = load_page(pz);
     pos_a = pz; page_a = pgz;
-    for (int j = 0; j < kDecStages - 1; ++j) {
-      issue(j, pos_a, page_a);
-      pos_a = load_pos(j + 1);
-      page_a = load_page(pos_a);
-    }
+    static_assert(kDecStages == 3, "the scale registers below assume two sub-tiles in flight");
+    issue(0, pos_a, page_a);
+    load_scale(page_a, sk0, sv0);
+    pos_a = load_pos(1);
+    page_a = load_page(pos_a);
+    issue(1, pos_a, page_a);
+    load_scale(page_a, sk1, sv1);
+    pos_a = load_pos(2);
+    page_a = load_page(pos_a);
     pos_b = load_pos(kDecStages);
   }
 
@@ -206,13 +256,36 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
   for (int j = 0; j < my_count; ++j) {
     __syncwarp();                      // every lane is done with the buffer about to be refilled
     issue(j + kDecStages - 1, pos_a, page_a);
+    load_scale(page_a, sk2, sv2);
     pos_a = pos_b;
     page_a = load_page(pos_a);
     pos_b = load_pos(j + kDecStages + 1);
     cp_async_wait<kDecStages - 1>();
     __syncwarp();
 
-    const uint32_t kbuf = my_smem_u32 + (j % kDecStages) * kDecStageBytes;
+    if (FP8) {
+      // the sub-tile as stored -> fp16 in the layout the fragment loads expect (16 bytes -> two 16-byte chunks)
+      const uint8_t* raw = my_smem + (j % kDecStages) * kRawStage;
+      const int c = lane & 7;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = i * 4 + (lane >> 3);
+#pragma unroll
+        for (int kv = 0; kv < (HAS_V ? 2 : 1); ++kv) {
+          const uint4 x = *reinterpret_cast<const uint4*>(raw + kv * kSub * kD + r * 128 + c * 16);
+          uint4 lo, hi;
+          lo.x = fp8x2_to_half2(x.x); lo.y = fp8x2_to_half2(x.x >> 16);
+          lo.z = fp8x2_to_half2(x.y); lo.w = fp8x2_to_half2(x.y >> 16);
+          hi.x = fp8x2_to_half2(x.z); hi.y = fp8x2_to_half2(x.z >> 16);
+          hi.z = fp8x2_to_half2(x.w); hi.w = fp8x2_to_half2(x.w >> 16);
+          uint8_t* dst = my_smem + kDecStages * kRawStage + kv * kSub * kD * 2;
+          *reinterpret_cast<uint4*>(dst + swz(r, 2 * c)) = lo;
+          *reinterpret_cast<uint4*>(dst + swz(r, 2 * c + 1)) = hi;
+        }
+      }
+      __syncwarp();
+    }
+    const uint32_t kbuf = FP8 ? work_u32 : my_smem_u32 + (j % kDecStages) * kDecStageBytes;
     const uint32_t vbuf = kbuf + kSub * kD * 2;
     // ---- S = Q K^T : two 8-key n-tiles x 8 k-steps ------------------------------------------
     float s[2][4];
@@ -238,6 +311,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
       for (int e = 0; e < 2; ++e) {
         int key = key0 + nt * 8 + quad * 2 + e;
         float x = s[nt][e] * p.scale2;
+        if (FP8) x *= __shfl_sync(0xFFFFFFFFu, sk0, nt * 8 + quad * 2 + e);    // the key's own scale
         x = key < n ? x : -INFINITY;
         s[nt][e] = x;
         tmax = fmaxf(tmax, x);
@@ -262,6 +336,12 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
       float p00 = exp2f(s[0][0] - m_new), p01 = exp2f(s[0][1] - m_new);
       float p10 = exp2f(s[1][0] - m_new), p11 = exp2f(s[1][1] - m_new);
       psum = p00 + p01 + p10 + p11;
+      if (FP8 && HAS_V) {                       // P.V sees the stored values: the rows' scales go on the probabilities
+        p00 *= __shfl_sync(0xFFFFFFFFu, sv0, quad * 2);
+        p01 *= __shfl_sync(0xFFFFFFFFu, sv0, quad * 2 + 1);
+        p10 *= __shfl_sync(0xFFFFFFFFu, sv0, 8 + quad * 2);
+        p11 *= __shfl_sync(0xFFFFFFFFu, sv0, 8 + quad * 2 + 1);
+      }
       pa0 = pack_half2<BF16>(p00, p01);
       pa2 = pack_half2<BF16>(p10, p11);
     }
@@ -284,6 +364,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
         mma16816<BF16>(o_acc[dt * 2 + 1], pa0, 0u, pa2, 0u, bfr[2], bfr[3]);
       }
     }
+    if (FP8) { sk0 = sk1; sv0 = sv1; sk1 = sk2; sv1 = sv2; }
   }
   cp_async_wait<0>();
   __syncthreads();
@@ -385,17 +466,23 @@ __global__ void __launch_bounds__(256) decode_pool_kernel(const float* __restric
 }
 
 int init_decode() {
-  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<false, true, false, false>,
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<false, true, false, 0>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
-  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, true, true, false>,
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, true, true, 0>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
-  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, false, true, false>,
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, false, true, 0>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
-  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<false, true, false, true>,
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<false, true, false, 1>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
-  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, true, true, true>,
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, true, true, 1>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
-  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, false, true, true>,
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, false, true, 1>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<false, true, false, 2>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, true, true, 2>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
+  KB_CUDA(cudaFuncSetAttribute(decode_attn_kernel<true, false, true, 2>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem));
   return 0;
 }
@@ -411,8 +498,21 @@ static int fill_kv(DecodeParams& p, const kb200_kv_layout* kv, bool need_v) {
   KB_REQUIRE(kv->stride_batch % 8 == 0 && kv->stride_page % 8 == 0 && kv->stride_token % 8 == 0 &&
                  kv->stride_head % 8 == 0,
              "decode: KV strides must be multiples of 8 elements (16 bytes)");
-  KB_REQUIRE(kv->dtype == KB200_FP16 || kv->dtype == KB200_BF16, "decode: unknown dtype code %d of the KV cache", kv->dtype);
+  KB_REQUIRE(kv->dtype == KB200_FP16 || kv->dtype == KB200_BF16 || kv->dtype == KB200_FP8_E4M3,
+             "decode: unknown dtype code %d of the KV cache", kv->dtype);
   p.bf16 = kv->dtype == KB200_BF16;
+  p.fp8 = kv->dtype == KB200_FP8_E4M3;
+  if (p.fp8) {
+    KB_REQUIRE(kv->k_scale && (!need_v || kv->v_scale), "decode: an FP8 cache needs k_scale / v_scale");
+    KB_REQUIRE(kv->stride_batch % 16 == 0 && kv->stride_page % 16 == 0 && kv->stride_token % 16 == 0 &&
+                   kv->stride_head % 16 == 0,
+               "decode: strides of an FP8 cache must be multiples of 16 elements (16 bytes)");
+    p.k_scale = kv->k_scale;
+    p.v_scale = kv->v_scale;
+    p.sc_stride_batch = kv->scale_stride_batch;
+    p.sc_stride_page = kv->scale_stride_page;
+    p.sc_stride_head = kv->scale_stride_head;
+  }
   p.k = static_cast<const __half*>(kv->k);
   p.v = static_cast<const __half*>(kv->v);
   p.kv_stride_batch = kv->stride_batch;
@@ -547,8 +647,9 @@ extern "C" int kb200_decode_sparse_paged(const void* q, int64_t q_stride_b, int6
   p.num_splits = splits;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(splits, num_kv_heads, batch);
-  if (p.bf16) decode_attn_kernel<false, true, false, true><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else decode_attn_kernel<false, true, false, false><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  if (p.fp8) decode_attn_kernel<false, true, false, 2><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else if (p.bf16) decode_attn_kernel<false, true, false, 1><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else decode_attn_kernel<false, true, false, 0><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
   KB_CHECK_LAUNCH("decode_attn_kernel<sparse>");
   if (splits > 1) {
     if (p.bf16)
@@ -605,10 +706,12 @@ extern "C" int kb200_decode_anchor_paged(const void* q, int64_t q_stride_b, int6
   p.num_splits = splits;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(splits, num_kv_heads, batch);
-  if (has_v && p.bf16) decode_attn_kernel<true, true, true, true><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else if (has_v) decode_attn_kernel<true, true, true, false><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else if (p.bf16) decode_attn_kernel<true, false, true, true><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else decode_attn_kernel<true, false, true, false><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  if (has_v && p.fp8) decode_attn_kernel<true, true, true, 2><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else if (has_v && p.bf16) decode_attn_kernel<true, true, true, 1><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else if (has_v) decode_attn_kernel<true, true, true, 0><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else if (p.fp8) decode_attn_kernel<true, false, true, 2><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else if (p.bf16) decode_attn_kernel<true, false, true, 1><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else decode_attn_kernel<true, false, true, 0><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
   KB_CHECK_LAUNCH("decode_attn_kernel<dense>");
   if (splits > 1) {
     if (has_v && p.bf16)
@@ -684,8 +787,9 @@ extern "C" int kb200_decode_sparse_paged_noalloc(const void* q, int64_t q_stride
   p.num_splits = splits;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(splits, num_kv_heads, batch);
-  if (p.bf16) decode_attn_kernel<false, true, false, true><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else decode_attn_kernel<false, true, false, false><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  if (p.fp8) decode_attn_kernel<false, true, false, 2><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else if (p.bf16) decode_attn_kernel<false, true, false, 1><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  else decode_attn_kernel<false, true, false, 0><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
   KB_CHECK_LAUNCH("decode_attn_kernel<sparse, noalloc>");
   if (splits > 1) {
     if (p.bf16)

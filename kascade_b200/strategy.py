@@ -524,12 +524,13 @@ class EfficientKascadeStrategy(Strategy):
         return q_out
 
     def paged_decode_forward(self, layer_idx: int, query, key_cache, value_cache, block_table, seq_lens, scaling,
-                             max_seq_len: Optional[int] = None) -> torch.Tensor:
-        """Paged-attention backend entry: query [B,H,D] fp16, key/value cache
-        [num_pages, page_size, G, D] fp16, block_table [B, max_pages] int32, seq_lens [B] int32
-        -> out [B,H,D] fp16.  The reference has no paged kernel (README.md:135); the nearest
+                             max_seq_len: Optional[int] = None, k_scale=None, v_scale=None) -> torch.Tensor:
+        """Paged-attention backend entry: query [B,H,D] fp16 / bf16, key/value cache
+        [num_pages, page_size, G, D] of the same type, block_table [B, max_pages] int32, seq_lens [B] int32
+        -> out [B,H,D].  An FP8 (e4m3) cache comes with k_scale / v_scale [num_pages, G] fp32 and takes fp16
+        queries.  The reference has no paged kernel (README.md:135); the nearest
         signature is kernels/flash_decoding/reuse_kascade_gqa_decode_with_kvcache.py:160-171."""
         if max_seq_len is None:
             max_seq_len = int(seq_lens.max().item())
-        kv = nat.kv_layout_paged(key_cache, value_cache, block_table)
+        kv = nat.kv_layout_paged(key_cache, value_cache, block_table, k_scale, v_scale)
         return self._decode(int(layer_idx), query, kv, seq_lens, int(max_seq_len), scaling, key_cache.shape[2])
