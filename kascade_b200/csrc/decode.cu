@@ -21,6 +21,7 @@
 namespace kb200 {
 
 constexpr int kDecWarps = 8;
+constexpr int kDecWarpsFp8 = 16;                           // FP8 rows are half as long: twice the warps in the same shared memory
 constexpr int kDecStages = 3;
 constexpr int kSub = 16;                                  // keys per sub-tile
 constexpr int kDecStageBytes = kSub * kD * 2 * 2;         // K + V rows of one sub-tile
@@ -79,6 +80,9 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
+__device__ __forceinline__ void lds128(uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d, uint32_t addr) {
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
+}
 template <bool BF16>
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -122,21 +126,54 @@ __device__ __forceinline__ uint32_t fp8x2_to_half2(uint32_t two_bytes) {
   return r;
 }
 
+// byte offset of 16-byte chunk `c` of row `r` inside a [16 rows x 128 B] sub-tile buffer of FP8 rows
+__device__ __forceinline__ uint32_t swz8(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
 // KV: storage of the cache.  0 fp16, 1 bf16 (q and the output have the same type), 2 FP8 e4m3 with one scale
-// per (page, KV head): rows of 128 bytes are copied as they are, turned into fp16 in shared memory (exact), and
-// the scales are applied in fp32 where a row's contribution appears: on the logit of its key and on its
+// per (page, KV head).  FP8 rows of 128 bytes are copied as they are and the MMA operands are made from them in
+// registers (cvt.rn.f16x2.e4m3x2, exact), without a second copy in shared memory:
+//   * Q.K^T sums over d, so the order of d inside the MMAs is free: lane (key n, quad q) reads the 32 contiguous
+//     bytes d = 32q .. 32q+31 of its key's row and uses 4 of them per k-step; the query fragments are loaded
+//     with the same assignment.
+//   * P.V needs pairs of keys per register: ldmatrix.trans over the bytes taken as 16-bit units gives
+//     (V[2q][d], V[2q][d+1], V[2q+1][d], V[2q+1][d+1]); a byte permute splits that into the operand of the
+//     even and of the odd columns, so a lane ends up with 4 contiguous d per 16-byte chunk.
+// The scales are applied in fp32 where a row's contribution appears: on the logit of its key and on its
 // probability before P.V.  q and the output are fp16 then.
 constexpr int kRawStage = kSub * kD * 2;                  // FP8: K + V rows of a sub-tile as stored (4 KB)
-constexpr int kWarpSmemFp8 = kDecStages * kRawStage + kDecStageBytes;   // three raw stages + one fp16 working copy
 
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(r) : "r"(x));
+  return r;
+}
+// the two 16-bit halves of a word of e4m3 bytes -> two fp16 pairs
+__device__ __forceinline__ void fp8x4_to_half2x2(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}\n"
+      : "=r"(lo), "=r"(hi)
+      : "r"(w));
+}
+
+__host__ __device__ constexpr int dec_warps(int kv) { return kv == 2 ? kDecWarpsFp8 : kDecWarps; }
+
+// The MMAs run "transposed": the 16 keys of a sub-tile are the M rows, the query heads the N columns (4 of 8
+// used), so that one m16n8k16 covers 16 keys x 16 d of Q.K^T and 16 d x 16 keys of P.V:
+//   S^T[key][head] = K[key][d] . Q^T[d][head]        A = K rows (ldmatrix), B = the query fragments
+//   O^T[d][head]   = V^T[d][key] . P^T[key][head]    A = V rows (ldmatrix.trans), B = P^T
+// The C fragment of S^T holds (key g | g+8, heads 2q, 2q+1) per lane (g = lane / 4, q = lane % 4); packed to
+// 16 bits and transposed with movmatrix it is the B fragment of P^T.  Lanes with q >= 2 carry the four unused
+// columns (zero queries).  Running max and sum are per lane for its two heads; the sum stays a per-lane
+// partial until the end.
 template <bool DENSE, bool HAS_V, bool WRITE_LOGITS, int KV>
-__global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(dec_warps(KV) * 32, 1) decode_attn_kernel(const DecodeParams p) {
   constexpr bool BF16 = KV == 1, FP8 = KV == 2;
+  constexpr int WARPS = dec_warps(KV);
+  constexpr uint32_t FULL = 0xFFFFFFFFu;
   extern __shared__ __align__(1024) uint8_t smem[];
   const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row_head = lane >> 2;          // A/C fragment row = query head (valid when < 4)
-  const int quad = lane & 3;
+  const int grp = lane >> 2;               // C fragment row: key grp (and grp + 8); B fragment column: head grp
+  const int quad = lane & 3;               // C fragment columns: heads 2*quad, 2*quad + 1 (valid when quad < 2)
 
   // ---- this CTA's slice of the key list -----------------------------------------------------
   int n;
@@ -154,31 +191,32 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
   const int per = (nst + p.num_splits - 1) / p.num_splits;
   const int st_begin = min(split * per, nst);
   const int st_end = min(st_begin + per, nst);
-  // sub-tiles of this warp: st_begin + warp, + kDecWarps, ...
-  const int my_count = (st_end - st_begin - warp + kDecWarps - 1) / kDecWarps;  // may be <= 0
+  // sub-tiles of this warp: st_begin + warp, + WARPS, ...
+  const int my_count = (st_end - st_begin - warp + WARPS - 1) / WARPS;  // may be <= 0
 
-  // ---- query fragments (rows 0..3 = heads, rows 4..15 zero) ----------------------------------
-  uint32_t qa0[8], qa2[8];
+  // ---- query fragments: B operand Q^T[d][head], column = head grp (zero for grp >= 4) ---------------
+  uint32_t qb0[8], qb1[8];
   {
-    const __half* qp = p.q + b * p.q_stride_b + (int64_t)(g * kHg + (row_head & 3)) * p.q_stride_h;
+    const __half* qp = p.q + b * p.q_stride_b + (int64_t)(g * kHg + (grp & 3)) * p.q_stride_h;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      uint32_t x0 = *reinterpret_cast<const uint32_t*>(qp + ks * 16 + quad * 2);
-      uint32_t x2 = *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8 + quad * 2);
-      qa0[ks] = row_head < kHg ? x0 : 0u;
-      qa2[ks] = row_head < kHg ? x2 : 0u;
+      // FP8: k-step ks of quad q covers d = 32q + 4ks .. + 3 (the order of d inside the sum is free)
+      uint32_t x0 = *reinterpret_cast<const uint32_t*>(qp + (FP8 ? quad * 32 + ks * 4 : ks * 16 + quad * 2));
+      uint32_t x1 = *reinterpret_cast<const uint32_t*>(qp + (FP8 ? quad * 32 + ks * 4 + 2 : ks * 16 + 8 + quad * 2));
+      qb0[ks] = grp < kHg ? x0 : 0u;
+      qb1[ks] = grp < kHg ? x1 : 0u;
     }
   }
 
   const int64_t kv_base = (int64_t)b * p.kv_stride_batch + (int64_t)g * p.kv_stride_head;
   const int32_t* table = p.block_table ? p.block_table + (int64_t)b * p.block_table_stride : nullptr;
-  uint8_t* my_smem = smem + warp * (FP8 ? kWarpSmemFp8 : kDecStages * kDecStageBytes);
+  constexpr int kStage = FP8 ? kRawStage : kDecStageBytes;
+  uint8_t* my_smem = smem + warp * (kDecStages * kStage);
   const uint32_t my_smem_u32 = smem_u32(my_smem);
-  const uint32_t work_u32 = my_smem_u32 + kDecStages * kRawStage;       // FP8: the fp16 copy the MMAs read
 
   // position of key `lane` (lanes 0..15) of sub-tile j of this warp, clamped into the list
   auto load_pos = [&](int j) -> int {
-    int s = (st_begin + warp + j * kDecWarps) * kSub + (lane & 15);
+    int s = (st_begin + warp + j * WARPS) * kSub + (lane & 15);
     if (j >= my_count) return 0;
     s = min(s, n - 1);
     return DENSE ? s : __ldg(idx_row + s);
@@ -191,26 +229,25 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
     if (j < my_count) {
       int64_t off = kv_base + (int64_t)page * p.kv_stride_page +
                     (int64_t)(pos & p.page_mask) * p.kv_stride_token;
+      const uint32_t dst = my_smem_u32 + (j % kDecStages) * kStage;
       if (FP8) {
         // rows of 128 bytes: 8 lanes per row, 4 rows per instruction, stored as they are
-        const uint32_t dst = my_smem_u32 + (j % kDecStages) * kRawStage;
         const uint8_t* k8 = reinterpret_cast<const uint8_t*>(p.k);
         const uint8_t* v8 = reinterpret_cast<const uint8_t*>(p.v);
         const int c = lane & 7;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           int r = i * 4 + (lane >> 3);
-          int64_t roff = __shfl_sync(0xFFFFFFFFu, off, r);
-          cp_async16(dst + r * 128 + c * 16, k8 + roff + c * 16);
-          if (HAS_V) cp_async16(dst + kSub * kD + r * 128 + c * 16, v8 + roff + c * 16);
+          int64_t roff = __shfl_sync(FULL, off, r);
+          cp_async16(dst + swz8(r, c), k8 + roff + c * 16);
+          if (HAS_V) cp_async16(dst + kSub * kD + swz8(r, c), v8 + roff + c * 16);
         }
       } else {
-        uint32_t dst = my_smem_u32 + (j % kDecStages) * kDecStageBytes;
         const int c = lane & 15;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           int r = i * 2 + (lane >> 4);
-          int64_t roff = __shfl_sync(0xFFFFFFFFu, off, r);
+          int64_t roff = __shfl_sync(FULL, off, r);
           cp_async16(dst + swz(r, c), p.k + roff + c * 8);
           if (HAS_V) cp_async16(dst + kSub * kD * 2 + swz(r, c), p.v + roff + c * 8);
         }
@@ -231,27 +268,26 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
   // ---- software pipeline: positions 2 ahead, pages 1 ahead, copies kDecStages-1 ahead ----------
   int pos_a = 0, page_a = 0, pos_b = 0;
   float sk0 = 1.f, sv0 = 1.f, sk1 = 1.f, sv1 = 1.f, sk2 = 1.f, sv2 = 1.f;   // FP8: scales of sub-tiles j, j+1, j+2
-  // prologue
   {
-    int pz = load_pos(0);
-    int pgz = load_page(pz);
-    pos_a = pz; page_a = pgz;
     static_assert(kDecStages == 3, "the scale registers below assume two sub-tiles in flight");
-    issue(0, pos_a, page_a);
-    load_scale(page_a, sk0, sv0);
-    pos_a = load_pos(1);
-    page_a = load_page(pos_a);
-    issue(1, pos_a, page_a);
-    load_scale(page_a, sk1, sv1);
-    pos_a = load_pos(2);
-    page_a = load_page(pos_a);
+    // all index loads first, then all page look-ups: the three dependent chains overlap
+    const int pz0 = load_pos(0), pz1 = load_pos(1), pz2 = load_pos(2);
+    const int pg0 = load_page(pz0), pg1 = load_page(pz1), pg2 = load_page(pz2);
+    issue(0, pz0, pg0);
+    load_scale(pg0, sk0, sv0);
+    issue(1, pz1, pg1);
+    load_scale(pg1, sk1, sv1);
+    pos_a = pz2;
+    page_a = pg2;
     pos_b = load_pos(kDecStages);
   }
 
-  float o_acc[16][4];
+  // O^T accumulators: o_acc[t][0|1] = (d_lo(t), heads 2q | 2q+1), o_acc[t][2|3] = (d_hi(t), ...) with
+  // d_lo = 16t + grp, d_hi = d_lo + 8 (fp16 / bf16) or d_lo = 16t + 2 grp, d_hi = d_lo + 1 (FP8)
+  float o_acc[8][4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
-  float m_run = -INFINITY, l_run = 0.f;   // per head (row_head), replicated over the quad
+  for (int i = 0; i < 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};
 
   for (int j = 0; j < my_count; ++j) {
     __syncwarp();                      // every lane is done with the buffer about to be refilled
@@ -263,105 +299,106 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
     cp_async_wait<kDecStages - 1>();
     __syncwarp();
 
+    const uint32_t kbuf = my_smem_u32 + (j % kDecStages) * kStage;
+    const uint32_t vbuf = kbuf + kSub * kD * (FP8 ? 1 : 2);
+    // ---- S^T = K Q^T : 8 k-steps, two accumulators to shorten the dependency chain ---------------
+    float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
     if (FP8) {
-      // the sub-tile as stored -> fp16 in the layout the fragment loads expect (16 bytes -> two 16-byte chunks)
-      const uint8_t* raw = my_smem + (j % kDecStages) * kRawStage;
-      const int c = lane & 7;
+      uint32_t wa[8], wb[8];                     // bytes d = 32q .. 32q+31 of key grp and of key grp + 8
+      lds128(wa[0], wa[1], wa[2], wa[3], kbuf + swz8(grp, quad * 2));
+      lds128(wa[4], wa[5], wa[6], wa[7], kbuf + swz8(grp, quad * 2 + 1));
+      lds128(wb[0], wb[1], wb[2], wb[3], kbuf + swz8(grp + 8, quad * 2));
+      lds128(wb[4], wb[5], wb[6], wb[7], kbuf + swz8(grp + 8, quad * 2 + 1));
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = i * 4 + (lane >> 3);
-#pragma unroll
-        for (int kv = 0; kv < (HAS_V ? 2 : 1); ++kv) {
-          const uint4 x = *reinterpret_cast<const uint4*>(raw + kv * kSub * kD + r * 128 + c * 16);
-          uint4 lo, hi;
-          lo.x = fp8x2_to_half2(x.x); lo.y = fp8x2_to_half2(x.x >> 16);
-          lo.z = fp8x2_to_half2(x.y); lo.w = fp8x2_to_half2(x.y >> 16);
-          hi.x = fp8x2_to_half2(x.z); hi.y = fp8x2_to_half2(x.z >> 16);
-          hi.z = fp8x2_to_half2(x.w); hi.w = fp8x2_to_half2(x.w >> 16);
-          uint8_t* dst = my_smem + kDecStages * kRawStage + kv * kSub * kD * 2;
-          *reinterpret_cast<uint4*>(dst + swz(r, 2 * c)) = lo;
-          *reinterpret_cast<uint4*>(dst + swz(r, 2 * c + 1)) = hi;
-        }
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t a0, a1, a2, a3;
+        fp8x4_to_half2x2(wa[ks], a0, a2);
+        fp8x4_to_half2x2(wb[ks], a1, a3);
+        mma16816<false>((ks & 1) ? s2 : s, a0, a1, a2, a3, qb0[ks], qb1[ks]);
       }
-      __syncwarp();
-    }
-    const uint32_t kbuf = FP8 ? work_u32 : my_smem_u32 + (j % kDecStages) * kDecStageBytes;
-    const uint32_t vbuf = kbuf + kSub * kD * 2;
-    // ---- S = Q K^T : two 8-key n-tiles x 8 k-steps ------------------------------------------
-    float s[2][4];
+    } else {
+      // matrices of one ldmatrix.x4: (keys 0-7, chunk 2ks) (keys 8-15, 2ks) (keys 0-7, 2ks+1) (keys 8-15, 2ks+1)
+      const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {        // 32 d per ldmatrix.x4
-        uint32_t bfr[4];
-        int r = nt * 8 + (lane & 7);
-        int c = kk * 4 + (lane >> 3);
-        ldmatrix_x4(bfr, kbuf + swz(r, c));
-        mma16816<BF16>(s[nt], qa0[kk * 2], 0u, qa2[kk * 2], 0u, bfr[0], bfr[1]);
-        mma16816<BF16>(s[nt], qa0[kk * 2 + 1], 0u, qa2[kk * 2 + 1], 0u, bfr[2], bfr[3]);
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t a[4];
+        ldmatrix_x4(a, kbuf + swz(r, ks * 2 + (lane >> 4)));
+        mma16816<BF16>((ks & 1) ? s2 : s, a[0], a[1], a[2], a[3], qb0[ks], qb1[ks]);
       }
     }
     // ---- scale, mask the tail, dump logits ----------------------------------------------------
-    const int key0 = (st_begin + warp + j * kDecWarps) * kSub;
-    float tmax = -INFINITY;
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        int key = key0 + nt * 8 + quad * 2 + e;
-        float x = s[nt][e] * p.scale2;
-        if (FP8) x *= __shfl_sync(0xFFFFFFFFu, sk0, nt * 8 + quad * 2 + e);    // the key's own scale
-        x = key < n ? x : -INFINITY;
-        s[nt][e] = x;
-        tmax = fmaxf(tmax, x);
+    const int key0 = (st_begin + warp + j * WARPS) * kSub;
+    float x[4];                                  // (key grp, head 2q) (grp, 2q+1) (grp+8, 2q) (grp+8, 2q+1)
+    {
+      float fa = p.scale2, fb = p.scale2;
+      if (FP8) {                                 // the key's own scale
+        fa *= __shfl_sync(FULL, sk0, grp);
+        fb *= __shfl_sync(FULL, sk0, grp + 8);
       }
-      if (WRITE_LOGITS && row_head < kHg) {
-        int key = key0 + nt * 8 + quad * 2;
-        float* lp = p.logits + ((int64_t)b * p.H + g * kHg + row_head) * p.logit_stride + key;
-        if (key + 1 < n) {
-          *reinterpret_cast<float2*>(lp) = make_float2(s[nt][0], s[nt][1]);
-        } else if (key < n) {
-          lp[0] = s[nt][0];
+      const bool va = key0 + grp < n, vb = key0 + grp + 8 < n;
+      x[0] = va ? (s[0] + s2[0]) * fa : -INFINITY;
+      x[1] = va ? (s[1] + s2[1]) * fa : -INFINITY;
+      x[2] = vb ? (s[2] + s2[2]) * fb : -INFINITY;
+      x[3] = vb ? (s[3] + s2[3]) * fb : -INFINITY;
+      if (WRITE_LOGITS && quad < 2) {
+        float* lp = p.logits + ((int64_t)b * p.H + g * kHg + quad * 2) * p.logit_stride + key0 + grp;
+        if (va) { lp[0] = x[0]; lp[p.logit_stride] = x[1]; }
+        if (vb) { lp[8] = x[2]; lp[p.logit_stride + 8] = x[3]; }
+      }
+    }
+    float t0 = fmaxf(x[0], x[2]), t1 = fmaxf(x[1], x[3]);
+#pragma unroll
+    for (int sh = 4; sh <= 16; sh <<= 1) {
+      t0 = fmaxf(t0, __shfl_xor_sync(FULL, t0, sh));
+      t1 = fmaxf(t1, __shfl_xor_sync(FULL, t1, sh));
+    }
+    const float m0 = fmaxf(m_run[0], t0), m1 = fmaxf(m_run[1], t1);   // finite: every sub-tile has >= 1 valid key
+    const float alpha0 = exp2f(m_run[0] - m0), alpha1 = exp2f(m_run[1] - m1);
+    m_run[0] = m0; m_run[1] = m1;
+    float p0 = exp2f(x[0] - m0), p1 = exp2f(x[1] - m1), p2 = exp2f(x[2] - m0), p3 = exp2f(x[3] - m1);
+    l_part[0] = l_part[0] * alpha0 + (p0 + p2);
+    l_part[1] = l_part[1] * alpha1 + (p1 + p3);
+    if (HAS_V) {
+      if (FP8) {                                 // P.V sees the stored values: the rows' scales go on the probabilities
+        const float va = __shfl_sync(FULL, sv0, grp), vb = __shfl_sync(FULL, sv0, grp + 8);
+        p0 *= va; p1 *= va; p2 *= vb; p3 *= vb;
+      }
+      // B operand P^T[key][head]: column = head grp, rows = keys 2q, 2q+1 (b0) and 2q+8, 2q+9 (b1)
+      const uint32_t pb0 = movmatrix_trans(pack_half2<BF16>(p0, p1));
+      const uint32_t pb1 = movmatrix_trans(pack_half2<BF16>(p2, p3));
+      // ---- O^T = O^T * alpha + V^T P^T : 8 d-tiles of 16 -----------------------------------------
+      if (!__all_sync(FULL, alpha0 == 1.f && alpha1 == 1.f)) {         // a factor of exactly 1 changes nothing
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          o_acc[t][0] *= alpha0; o_acc[t][1] *= alpha1; o_acc[t][2] *= alpha0; o_acc[t][3] *= alpha1;
         }
       }
-    }
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, 1));
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, 2));
-    const float m_new = fmaxf(m_run, tmax);       // finite: every sub-tile has >= 1 valid key
-    const float alpha = exp2f(m_run - m_new);
-    float psum = 0.f;
-    uint32_t pa0, pa2;
-    {
-      float p00 = exp2f(s[0][0] - m_new), p01 = exp2f(s[0][1] - m_new);
-      float p10 = exp2f(s[1][0] - m_new), p11 = exp2f(s[1][1] - m_new);
-      psum = p00 + p01 + p10 + p11;
-      if (FP8 && HAS_V) {                       // P.V sees the stored values: the rows' scales go on the probabilities
-        p00 *= __shfl_sync(0xFFFFFFFFu, sv0, quad * 2);
-        p01 *= __shfl_sync(0xFFFFFFFFu, sv0, quad * 2 + 1);
-        p10 *= __shfl_sync(0xFFFFFFFFu, sv0, 8 + quad * 2);
-        p11 *= __shfl_sync(0xFFFFFFFFu, sv0, 8 + quad * 2 + 1);
-      }
-      pa0 = pack_half2<BF16>(p00, p01);
-      pa2 = pack_half2<BF16>(p10, p11);
-    }
-    psum += __shfl_xor_sync(0xFFFFFFFFu, psum, 1);
-    psum += __shfl_xor_sync(0xFFFFFFFFu, psum, 2);
-    l_run = l_run * alpha + psum;
-    m_run = m_new;
-    if (HAS_V) {
-      if (row_head >= kHg) { pa0 = 0u; pa2 = 0u; }
-      // ---- O = O*alpha + P V : 16 d-tiles of 8 -------------------------------------------------
+      if (FP8) {
+        // ldmatrix.trans over the bytes as 16-bit units: lane gets (V[2q][d], V[2q][d+1], V[2q+1][d], V[2q+1][d+1]),
+        // d = 16c + 2 grp; matrices of one x4: (keys 0-7, chunk 2t) (keys 8-15, 2t) (keys 0-7, 2t+1) (keys 8-15, 2t+1)
+        const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
-      for (int dt = 0; dt < 8; ++dt) {            // two 8-wide d tiles per ldmatrix.x4.trans
-        uint32_t bfr[4];
-        int r = (lane & 7) + ((lane >> 3) & 1) * 8;   // matrices: (k0-7,d0) (k8-15,d0) (k0-7,d1) (k8-15,d1)
-        int c = dt * 2 + (lane >> 4);
-        ldmatrix_x4_trans(bfr, vbuf + swz(r, c));
+        for (int t2 = 0; t2 < 4; ++t2) {
+          uint32_t rr[4];
+          ldmatrix_x4_trans(rr, vbuf + swz8(r, t2 * 2 + (lane >> 4)));
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { o_acc[dt * 2][e] *= alpha; o_acc[dt * 2 + 1][e] *= alpha; }
-        mma16816<BF16>(o_acc[dt * 2], pa0, 0u, pa2, 0u, bfr[0], bfr[1]);
-        mma16816<BF16>(o_acc[dt * 2 + 1], pa0, 0u, pa2, 0u, bfr[2], bfr[3]);
+          for (int h = 0; h < 2; ++h) {
+            // A rows 0-7: d = 16c + 2 grp (even bytes), rows 8-15: d + 1 (odd bytes); k = keys 2q.. (a0, a1), 2q+8.. (a2, a3)
+            mma16816<false>(o_acc[t2 * 2 + h], fp8x2_to_half2(__byte_perm(rr[2 * h], 0u, 0x4420)),
+                            fp8x2_to_half2(__byte_perm(rr[2 * h], 0u, 0x4431)),
+                            fp8x2_to_half2(__byte_perm(rr[2 * h + 1], 0u, 0x4420)),
+                            fp8x2_to_half2(__byte_perm(rr[2 * h + 1], 0u, 0x4431)), pb0, pb1);
+          }
+        }
+      } else {
+        // matrices of one ldmatrix.x4.trans: (keys 0-7, chunk 2t) (keys 0-7, 2t+1) (keys 8-15, 2t) (keys 8-15, 2t+1)
+        const int r = (lane & 7) + (lane >> 4) * 8;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          uint32_t a[4];
+          ldmatrix_x4_trans(a, vbuf + swz(r, t * 2 + ((lane >> 3) & 1)));
+          mma16816<BF16>(o_acc[t], a[0], a[1], a[2], a[3], pb0, pb1);
+        }
       }
     }
     if (FP8) { sk0 = sk1; sv0 = sv1; sk1 = sk2; sv1 = sv2; }
@@ -370,29 +407,39 @@ __global__ void __launch_bounds__(kDecWarps * 32, 1) decode_attn_kernel(const De
   __syncthreads();
 
   // ---- merge the warps of this CTA through shared memory ------------------------------------------
-  float* sm_m = reinterpret_cast<float*>(smem);                  // [warps][4]
-  float* sm_l = sm_m + kDecWarps * kHg;                          // [warps][4]
-  float* sm_o = sm_l + kDecWarps * kHg;                          // [warps][4][128]
-  if (row_head < kHg) {
-    if (quad == 0) { sm_m[warp * kHg + row_head] = m_run; sm_l[warp * kHg + row_head] = l_run; }
-    if (HAS_V) {
 #pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
-        float* dst = sm_o + (warp * kHg + row_head) * kD + nt * 8 + quad * 2;
-        dst[0] = o_acc[nt][0];
-        dst[1] = o_acc[nt][1];
+  for (int sh = 4; sh <= 16; sh <<= 1) {
+    l_part[0] += __shfl_xor_sync(FULL, l_part[0], sh);
+    l_part[1] += __shfl_xor_sync(FULL, l_part[1], sh);
+  }
+  float* sm_m = reinterpret_cast<float*>(smem);                  // [warps][4]
+  float* sm_l = sm_m + WARPS * kHg;                              // [warps][4]
+  float* sm_o = sm_l + WARPS * kHg;                              // [warps][4][128]
+  if (quad < 2) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int h = quad * 2 + e;
+      if (grp == 0) { sm_m[warp * kHg + h] = m_run[e]; sm_l[warp * kHg + h] = l_part[e]; }
+      if (HAS_V) {
+        float* dst = sm_o + (warp * kHg + h) * kD;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const int d_lo = FP8 ? t * 16 + grp * 2 : t * 16 + grp;
+          dst[d_lo] = o_acc[t][e];
+          dst[d_lo + (FP8 ? 1 : 8)] = o_acc[t][2 + e];
+        }
       }
     }
   }
   __syncthreads();
-  for (int t = threadIdx.x; t < kHg * kD; t += blockDim.x) {
+  for (int t = threadIdx.x; t < kHg * kD; t += WARPS * 32) {
     const int h = t / kD, d = t % kD;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kDecWarps; ++w) M = fmaxf(M, sm_m[w * kHg + h]);
+    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_m[w * kHg + h]);
     float L = 0.f, O = 0.f;
 #pragma unroll
-    for (int w = 0; w < kDecWarps; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
       float mw = sm_m[w * kHg + h];
       float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
       L += sm_l[w * kHg + h] * f;
@@ -528,11 +575,14 @@ static int fill_kv(DecodeParams& p, const kb200_kv_layout* kv, bool need_v) {
   return 0;
 }
 
+// Splits per (sequence, KV head): as many as it takes to put about one CTA on every SM, and none beyond that -
+// a CTA has a fixed cost (pipeline fill, merge of its warps, the partials and their combine pass) that measured
+// larger than what a second wave of smaller CTAs gains.  At least 256 keys per split.
 static int default_splits(int batch, int G, int max_keys) {
   int64_t ctas = (int64_t)batch * G;
   if (ctas <= 0) return 1;
-  int want = (int)((4LL * sm_count() + ctas - 1) / ctas);
-  int cap = max_keys / 512;
+  int want = (int)(sm_count() / ctas);
+  int cap = max_keys / 256;
   if (cap < 1) cap = 1;
   int s = want < cap ? want : cap;
   if (s < 1) s = 1;
@@ -647,9 +697,9 @@ extern "C" int kb200_decode_sparse_paged(const void* q, int64_t q_stride_b, int6
   p.num_splits = splits;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(splits, num_kv_heads, batch);
-  if (p.fp8) decode_attn_kernel<false, true, false, 2><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else if (p.bf16) decode_attn_kernel<false, true, false, 1><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else decode_attn_kernel<false, true, false, 0><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  if (p.fp8) decode_attn_kernel<false, true, false, 2><<<grid, dec_warps(2) * 32, kDecSmem, st>>>(p);
+  else if (p.bf16) decode_attn_kernel<false, true, false, 1><<<grid, dec_warps(1) * 32, kDecSmem, st>>>(p);
+  else decode_attn_kernel<false, true, false, 0><<<grid, dec_warps(0) * 32, kDecSmem, st>>>(p);
   KB_CHECK_LAUNCH("decode_attn_kernel<sparse>");
   if (splits > 1) {
     if (p.bf16)
@@ -706,12 +756,12 @@ extern "C" int kb200_decode_anchor_paged(const void* q, int64_t q_stride_b, int6
   p.num_splits = splits;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(splits, num_kv_heads, batch);
-  if (has_v && p.fp8) decode_attn_kernel<true, true, true, 2><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else if (has_v && p.bf16) decode_attn_kernel<true, true, true, 1><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else if (has_v) decode_attn_kernel<true, true, true, 0><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else if (p.fp8) decode_attn_kernel<true, false, true, 2><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else if (p.bf16) decode_attn_kernel<true, false, true, 1><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else decode_attn_kernel<true, false, true, 0><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  if (has_v && p.fp8) decode_attn_kernel<true, true, true, 2><<<grid, dec_warps(2) * 32, kDecSmem, st>>>(p);
+  else if (has_v && p.bf16) decode_attn_kernel<true, true, true, 1><<<grid, dec_warps(1) * 32, kDecSmem, st>>>(p);
+  else if (has_v) decode_attn_kernel<true, true, true, 0><<<grid, dec_warps(0) * 32, kDecSmem, st>>>(p);
+  else if (p.fp8) decode_attn_kernel<true, false, true, 2><<<grid, dec_warps(2) * 32, kDecSmem, st>>>(p);
+  else if (p.bf16) decode_attn_kernel<true, false, true, 1><<<grid, dec_warps(1) * 32, kDecSmem, st>>>(p);
+  else decode_attn_kernel<true, false, true, 0><<<grid, dec_warps(0) * 32, kDecSmem, st>>>(p);
   KB_CHECK_LAUNCH("decode_attn_kernel<dense>");
   if (splits > 1) {
     if (has_v && p.bf16)
@@ -787,9 +837,9 @@ extern "C" int kb200_decode_sparse_paged_noalloc(const void* q, int64_t q_stride
   p.num_splits = splits;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(splits, num_kv_heads, batch);
-  if (p.fp8) decode_attn_kernel<false, true, false, 2><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else if (p.bf16) decode_attn_kernel<false, true, false, 1><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
-  else decode_attn_kernel<false, true, false, 0><<<grid, kDecWarps * 32, kDecSmem, st>>>(p);
+  if (p.fp8) decode_attn_kernel<false, true, false, 2><<<grid, dec_warps(2) * 32, kDecSmem, st>>>(p);
+  else if (p.bf16) decode_attn_kernel<false, true, false, 1><<<grid, dec_warps(1) * 32, kDecSmem, st>>>(p);
+  else decode_attn_kernel<false, true, false, 0><<<grid, dec_warps(0) * 32, kDecSmem, st>>>(p);
   KB_CHECK_LAUNCH("decode_attn_kernel<sparse, noalloc>");
   if (splits > 1) {
     if (p.bf16)
