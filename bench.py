@@ -51,13 +51,16 @@ class _Module:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    """Samples SM clocks and throttle reasons with nvidia-smi (every 100 ms, each sample with nvidia-smi's own
+    timestamp) and reports those that fall into a window of host time.  nvidia-smi takes a good part of a second to
+    produce its first sample, so the sampler is started before the warm-up."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
+        self.thread = None
         self.lines = []
 
     def start(self):
@@ -74,7 +77,9 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """t_begin / t_end: datetime.now() taken around the window; None = every sample."""
+        import datetime
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -82,18 +87,24 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for ln in list(self.lines):
             parts = [x.strip() for x in ln.split(",")]
-            if len(parts) < 6:
+            if len(parts) < 7:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx = float(parts[1])
+                when = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+                clock, top = float(parts[1]), float(parts[2])
             except ValueError:
                 continue
-            for n, v in zip(names, parts[2:6]):
+            if (t_begin is not None and when < t_begin) or (t_end is not None and when > t_end):
+                continue
+            sm.append(clock)
+            mx = top
+            for n, v in zip(names, parts[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         sm.sort()
@@ -646,16 +657,18 @@ def main():
             strat.wait_gathers()
         result["out"] = out
 
+    import datetime
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
     n0 = nat.launch_count
     torch.cuda.synchronize()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = datetime.datetime.now()
     s.record()
     for _ in range(args.steps):
         step()
@@ -664,11 +677,22 @@ def main():
     launches = (nat.launch_count - n0) // max(args.steps, 1)
     if world > 1:
         dist.barrier()
-    clocks = sampler.stop()
     ms = torch.tensor([s.elapsed_time(e) / args.steps], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_step = float(ms.item())
+    # A timed region shorter than a few sampling periods holds no clock sample: the same steps go on, untimed,
+    # until the load has lasted 0.6 s (every rank derives the same count from the all-reduced step time).
+    repeat = 0
+    if ms_step * args.steps < 600.0:
+        repeat = min(500, int((600.0 - ms_step * args.steps) / max(ms_step, 1e-3)) + 1)
+        for _ in range(repeat):
+            step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+    clocks = sampler.stop(t_begin, datetime.datetime.now())
+    clocks["window"] = "timed region" if repeat == 0 else f"timed region + {repeat} more of the same steps, untimed"
     status = nat.read_status()
 
     # ---------------- per-kernel timing and the roofline of the dominant kernel ------------------

@@ -324,6 +324,19 @@ def kv_layout_contiguous(k: torch.Tensor, v: Optional[torch.Tensor], page_size: 
                     k.stride(2), k.stride(1), 0, 0, page_size, code)
 
 
+def kv_layout_rows(k: torch.Tensor, v: Optional[torch.Tensor], row_table: torch.Tensor) -> KvLayout:
+    """HF cache view [B, G, L, D] whose sequences do not start at row 0 (a padded batch): row_table [B, n] int32 gives
+    the cache row of every logical position - a block table with one-token pages, which the decode kernels already
+    know how to walk."""
+    code = _half_code(k, "k")
+    assert k.dim() == 4 and k.stride(3) == 1
+    assert row_table.dtype == torch.int32 and row_table.dim() == 2 and row_table.stride(1) == 1
+    if v is not None:
+        assert v.shape == k.shape and v.stride() == k.stride() and v.dtype == k.dtype
+    return KvLayout(k.data_ptr(), 0 if v is None else v.data_ptr(), k.stride(0), k.stride(2), k.stride(2), k.stride(1),
+                    row_table.data_ptr(), row_table.stride(0), 1, code)
+
+
 def decode_workspace(batch: int, heads: int, splits: int, device) -> torch.Tensor:
     n = load().kb200_decode_workspace_bytes(batch, heads, splits)
     return torch.empty(max(n, 16), dtype=torch.uint8, device=device)

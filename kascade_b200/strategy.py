@@ -235,8 +235,8 @@ class EfficientKascadeStrategy(Strategy):
 
         The reference (strategies/EfficientKascadeStrategy.py:126-161) never reads the mask: prompts are
         causal and unpadded, a decode step attends to the whole cache.  Here the mask is read for one
-        thing only, LEFT padding of a batch (leading key positions that no query may see): every
-        sequence then goes through the kernels on its own unpadded views, with its own index rows."""
+        thing only, padding of a batch (leading / trailing key positions that no query may see): the kernels
+        then get every sequence's first row and length and treat it as if it had been run alone."""
         if query.dtype not in nat.DTYPES or key.dtype != query.dtype or value.dtype != query.dtype:
             raise nat.KascadeNativeError(f"efficient_kascade takes fp16 or bf16 q / k / v of one type; got {query.dtype}, "
                                          f"{key.dtype}, {value.dtype}")
@@ -298,23 +298,26 @@ class EfficientKascadeStrategy(Strategy):
         return self._pads
 
     def _decode_padded(self, pad, module, query, key, value, scaling) -> torch.Tensor:
-        """One decode step of a padded batch: every sequence runs on its own unpadded cache views with its own
-        index rows (a padded cache has no single layout the decode kernels could walk)."""
+        """One decode step of a padded batch, every kernel launched once: the cache rows of sequence b are
+        starts[b] .. starts[b] + lens[b] - 1, described to the decode kernels as a block table with one-token pages
+        (logical position -> cache row), so index rows, budgets and lengths are those of the unpadded sequences."""
         starts, lens = pad
         B, H, Lq, D = query.shape
-        if getattr(self, "_children", None) is None or len(self._children) != B:
-            self._children = [EfficientKascadeStrategy(self.recompute_layers, "", k=self.k, tile_size=self.tile_size,
-                                                       rolling_prefill=self.rolling_prefill,
-                                                       head_mapping=self._head_mapping, register=False)
-                              for _ in range(B)]
-        out = torch.zeros(B, Lq, H, D, dtype=query.dtype, device=query.device)
-        for b, (s0, n, child) in enumerate(zip(starts, lens, self._children)):
-            if n == 0:
-                continue                                                           # nothing to attend to
-            ob, _ = child.attention_forward(module, query[b:b + 1], key[b:b + 1, :, s0:s0 + n], value[b:b + 1, :, s0:s0 + n],
-                                            None, scaling)
-            out[b:b + 1] = ob
-        return out
+        G, Lk = key.shape[1], key.shape[2]
+        dev = query.device
+        max_len = max(lens)
+        if max_len == 0:
+            return torch.zeros(B, Lq, H, D, dtype=query.dtype, device=dev)
+        cached = getattr(self, "_pad_rows", None)
+        if cached is None or cached[0] is not pad or cached[1].device != dev:
+            first = torch.tensor(starts, dtype=torch.int32, device=dev)
+            rows = (first[:, None] + torch.arange(Lk, dtype=torch.int32, device=dev)[None, :]).clamp_(max=Lk - 1)
+            cached = self._pad_rows = (pad, rows.contiguous(), torch.tensor(lens, dtype=torch.int32, device=dev))
+        key, value = self._cache_views(key, value)
+        kv = nat.kv_layout_rows(key, value, cached[1])
+        out = self._decode(int(module.layer_idx), query[:, :, 0], kv, cached[2], max_len, scaling, G,
+                           dense_only=max_len <= 128)              # strategies/EfficientKascadeStrategy.py:137-140
+        return out.unsqueeze(1)
 
     @staticmethod
     def _cache_views(key, value):

@@ -1,5 +1,6 @@
 """Padded batches through the strategy (GPU): each sequence must come out exactly as if it had been run alone and
-unpadded; padded query rows are zero; a padded prefill launches every kernel once for the whole batch.  The
+unpadded; padded query rows are zero; a padded prefill and a padded decode step launch every kernel once for the
+whole batch.  The
 reference ignores the mask altogether (strategies/EfficientKascadeStrategy.py:126-161), which is only right for
 unpadded batches."""
 import pytest
@@ -61,6 +62,8 @@ def test_left_padded_batch_equals_separate_runs(as_bool):
             got, _ = batch.attention_forward(m, q, k, v, mask, D ** -0.5)
             if phase == "prefill":                       # one launch per kernel kind for the whole padded batch
                 assert nat.launch_count - n0 == {0: 4, 1: 1, 2: 5}[l], f"layer {l}: {nat.launch_count - n0} launches"
+            else:                                        # and so does a padded decode step (no loop over sequences)
+                assert nat.launch_count - n0 == {0: 3, 1: 1, 2: 4}[l], f"decode layer {l}: {nat.launch_count - n0} launches"
             for b, pad in enumerate(pads):
                 qb = q[b:b + 1, :, pad:] if phase == "prefill" else q[b:b + 1]
                 want, _ = alone[b].attention_forward(m, qb, k[b:b + 1, :, pad:], v[b:b + 1, :, pad:], None, D ** -0.5)
