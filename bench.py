@@ -300,12 +300,13 @@ def bench_decode(args, dev, world, peaks, batch=None, ragged=False, rank=0):
     caches = [dw.make_cache(i, dev) for i in range(dw.distinct_caches)]
     qs = [dw.query(l, dev) for l in range(dw.layers)]
     seq_lens = torch.tensor(dw.seq_lens(), dtype=torch.int32, device=dev)
+    mean_len = sum(dw.seq_lens()) / len(dw.seq_lens())            # the host knows its batch: a hint for the split count
     dout = {}
 
     def dstep(_i=0):
         for l in range(dw.layers):
             kc, vc, bt = caches[l % len(caches)]
-            dout["o"] = dstrat.paged_decode_forward(l, qs[l], kc, vc, bt, seq_lens, scaling, dw.context)
+            dout["o"] = dstrat.paged_decode_forward(l, qs[l], kc, vc, bt, seq_lens, scaling, dw.context, mean_seq_len=mean_len)
 
     for _ in range(args.warmup):
         dstep()
@@ -449,6 +450,7 @@ def bench_decoder_generate(args, dev, world, rank):
     max_len = dw.context + gen
     tokens = torch.randint(0, cfg.vocab, (dw.batch,), device=dev, generator=torch.Generator(device=dev).manual_seed(11))
     model._qkv_cache = [None] * cfg.layers
+    model.mean_len = sum(dw.seq_lens()) / len(dw.seq_lens())
 
     def step():
         nxt = model.step(tokens, lambda l: caches[l % len(caches)], block_table, seq_lens, max_len)
@@ -553,7 +555,7 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-dense", action="store_true")
-    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "peer_store", "multicast", "nccl", "local"],
+    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "push_slices", "peer_store", "multicast", "nccl", "local"],
                     help="N > 1: how the per-head outputs reach the other GPUs: copy-engine pushes on side streams "
                          "(push), stores from the kernel epilogue to every peer (peer_store) or once to an NVLink multicast "
                          "address (multicast), NCCL all-gather (nccl); auto = peer_store on 2 GPUs, multicast from 4 on; local = measurement aid: like push with the copies left "

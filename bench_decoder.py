@@ -112,7 +112,7 @@ class KascadeLlamaDecoder:
                      v_new.view(B, 1, c.kv_heads, c.head_dim), seq_lens, None, kv, inv_freq=self.inv_freq)
         lens_after = self._lens_after
         return self.strategy.paged_decode_forward(layer, q_rot.view(B, c.heads, c.head_dim), kc, vc, block_table,
-                                                  lens_after, c.head_dim ** -0.5, max_len)
+                                                  lens_after, c.head_dim ** -0.5, max_len, mean_seq_len=self.mean_len)
 
     def step(self, tokens_or_hidden, caches_of_layer, block_table, seq_lens, max_len: int, attention_only: bool = False):
         """One decode step for the whole batch.  seq_lens [B] int32 = cache lengths BEFORE the step (the position
@@ -149,5 +149,6 @@ class KascadeLlamaDecoder:
         self.last_logits = F.linear(x, head)
         return self.last_logits.argmax(-1)
 
+    mean_len: Optional[float] = None      # the host's hint for batches of very different lengths (see paged_decode_forward)
     _qkv_cache: Optional[list] = None
     _lens_after: Optional[torch.Tensor] = None

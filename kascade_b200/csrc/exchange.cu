@@ -5,8 +5,9 @@
 // prefill kernels can store the rows into the peers themselves (kb200_out_fanout), but from four GPUs
 // on the NVLink time of a reuse layer exceeds its compute time and the stores hold the kernel up.  The
 // calls here take the exchange off the kernels' critical path: the kernel writes only its own buffer,
-// and the slice is then copied into every peer's buffer by the DMA engines (a strided 2-D copy per
-// peer, each on a stream of its own), while the next layer's kernels run.  No SM is used, nothing
+// and the slice is then copied into every peer's buffer by the DMA engines (one copy per peer, each on a
+// stream of its own: a strided 2-D copy for [B, L, H, D] buffers, one contiguous piece for rank-major
+// [ranks, B, L, H/ranks, D] buffers), while the next layer's kernels run.  No SM is used, nothing
 // waits across GPUs inside a kernel, no multicast.
 //
 // The reference has no counterpart (it runs on one GPU).
@@ -30,8 +31,11 @@ extern "C" int kb200_peer_push(const kb200_push_plan* plan, const void* src_base
     KB_REQUIRE(plan->dst[i] && plan->stream[i] && plan->done_event[i], "peer_push: peer %d has a null entry", i);
     cudaStream_t st = (cudaStream_t)plan->stream[i];
     KB_CUDA(cudaStreamWaitEvent(st, (cudaEvent_t)ready_event, 0));
-    KB_CUDA(cudaMemcpy2DAsync(static_cast<char*>(plan->dst[i]) + offset_bytes, pitch_bytes, src, pitch_bytes, width_bytes,
-                              rows, cudaMemcpyDeviceToDevice, st));
+    if (rows == 1)        // one contiguous piece: a plain copy runs at the full link rate, a pitched one does not
+      KB_CUDA(cudaMemcpyAsync(static_cast<char*>(plan->dst[i]) + offset_bytes, src, width_bytes, cudaMemcpyDeviceToDevice, st));
+    else
+      KB_CUDA(cudaMemcpy2DAsync(static_cast<char*>(plan->dst[i]) + offset_bytes, pitch_bytes, src, pitch_bytes,
+                                width_bytes, rows, cudaMemcpyDeviceToDevice, st));
     KB_CUDA(cudaEventRecord((cudaEvent_t)plan->done_event[i], st));
   }
   return 0;

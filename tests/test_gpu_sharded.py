@@ -44,23 +44,23 @@ def _worker(rank, world, port, ret, exchange):
         torch.cuda.synchronize()
         worst = max(worst, (out.float() - ref[:, :, qh].float()).abs().max().item())
         gathered = part.gathered_out
-        if exchange != "nccl":                                                          # [B,L,H,D], filled by both ranks
+        if gathered.dim() == 4:                                                         # [B,L,H,D], filled by both ranks
             whole = gathered
-        else:                                                                           # [world,B,L,H/world,D]
+        else:                                                                           # rank-major [world,B,L,H/world,D]
             whole = torch.cat([gathered[r] for r in range(world)], dim=2)
         worst = max(worst, (whole.float() - ref.float()).abs().max().item())
     ret[rank] = (worst, nat.read_status())
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["nccl", "peer_store", "push", "multicast"])
+@pytest.mark.parametrize("exchange", ["nccl", "peer_store", "push", "push_slices", "multicast"])
 def test_sharded_prefill_matches_unsharded(exchange):
-    """Outputs of every layer, gathered by an NCCL all-gather, by the kernels' own peer stores, or by copy-engine
-    pushes on side streams, equal the unsharded strategy's bit for bit."""
+    """Outputs of every layer, gathered by an NCCL all-gather, by the kernels' own peer stores (plain or multicast), or
+    by copy-engine pushes on side streams (pitched or contiguous slices), equal the unsharded strategy's bit for bit."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
-    port = 29600 + (os.getpid() % 1000) + {"nccl": 0, "peer_store": 500, "push": 1000, "multicast": 1500}[exchange]
+    port = 29600 + (os.getpid() % 1000) + {"nccl": 0, "peer_store": 500, "push": 1000, "multicast": 1500, "push_slices": 2000}[exchange]
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, port, ret, exchange), nprocs=world, join=True)
