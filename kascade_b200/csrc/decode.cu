@@ -536,10 +536,13 @@ int init_decode() {
 // per SM) while the grid is small; half-size CTAs, two per SM, once the grid is at least 1.5 x the SMs: then one
 // CTA's start (index -> block table -> row chain) and merge overlap the other's stream, which measured 3-9 %
 // faster at batch 32-64 and 5-10 % slower at batch <= 16.
+#ifndef KB200_DEC_HALF_FROM
+#define KB200_DEC_HALF_FROM 3      // half-size CTAs from this many CTAs per two SMs on
+#endif
 template <bool DENSE, bool HAS_V, bool WRITE_LOGITS, int KV>
 static void launch_attn(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   const long long total = (long long)grid.x * grid.y * grid.z;
-  const int warps = total * 2 >= 3LL * sm_count() ? dec_warps(KV) / 2 : dec_warps(KV);
+  const int warps = total * 2 >= (long long)KB200_DEC_HALF_FROM * sm_count() ? dec_warps(KV) / 2 : dec_warps(KV);
   const size_t smem = (size_t)warps * kDecStages * (KV == 2 ? kRawStage : kDecStageBytes);
   decode_attn_kernel<DENSE, HAS_V, WRITE_LOGITS, KV><<<grid, warps * 32, smem, st>>>(p);
 }
