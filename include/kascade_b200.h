@@ -33,7 +33,7 @@ extern "C" {
 /* storage types of activations and KV caches (field `dtype` of the layouts; 0 = fp16, so a zero-initialised
  * layout is fp16).  bf16 is the native type of Qwen3; both go through the same tensor-core path
  * (tcgen05 kind::f16 / mma.sync), probabilities are rounded to the activations' type, accumulation is fp32,
- * outputs are written in the activations' type.  kb200_kv_write is fp16 only. */
+ * outputs are written in the activations' type. */
 #define KB200_FP16 0
 #define KB200_BF16 1
 #define KB200_FP8_E4M3 2   /* KV caches of the decode calls only, see kb200_kv_layout */
@@ -343,14 +343,15 @@ int kb200_prefill_budgets(int32_t* n_valid, int32_t* k_row, int batch, int num_k
  * the attention kernels read.  The reference has no such kernel: it receives rotated q/k/v from the
  * Hugging Face attention module and pays transposes and `.contiguous()` copies before every kernel
  * call (strategies/EfficientKascadeStrategy.py:144-150).  Arithmetic follows the Hugging Face modules
- * step by step (LlamaRMSNorm, LlamaRotaryEmbedding, apply_rotary_pos_emb: fp32 norm rounded to fp16,
- * fp16 gain, cos / sin in fp32 rounded to fp16, fp16 products and sum).
- *   q_in        [B, T, H, D] fp16 view, or NULL (then q_out is ignored); q_out [B, T, H, D] fp16 contiguous
- *   k_new/v_new [B, T, G, D] fp16 views: the rows to append (T = max_new)
+ * step by step in the model's type - fp16 or bf16, the `dtype` of the layouts, which must all agree
+ * (LlamaRMSNorm, LlamaRotaryEmbedding, apply_rotary_pos_emb: fp32 norm rounded to that type, gain applied in
+ * that type, cos / sin in fp32 rounded to that type, products and sum in that type).
+ *   q_in        [B, T, H, D] view, or NULL (then q_out is ignored); q_out [B, T, H, D] contiguous, same type
+ *   k_new/v_new [B, T, G, D] views: the rows to append (T = max_new)
  *   start_pos   [B] int32: cache length of each sequence before the append (position of its first new token)
  *   n_new       [B] int32 number of new tokens per sequence (<= max_new), or NULL (= max_new)
  *   kv          the cache (written): paged with a block table that already covers the new positions, or contiguous
- *   q_norm_gain / k_norm_gain  [D] fp16 or NULL (no norm);  norm_eps
+ *   q_norm_gain / k_norm_gain  [D] in the same type, or NULL (no norm);  norm_eps
  *   inv_freq    [D/2] fp32 inverse frequencies of the model's rotary embedding (device memory), or NULL
  *               (no rotary);  rope_scale multiplies cos and sin (1 for the default rope type)
  */

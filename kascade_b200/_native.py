@@ -515,20 +515,21 @@ def prefill_sparse(q, k, v, tile_idx, tile_count, head_map, scale, out, lse2=Non
 @_on_device_of(2)
 def kv_write(q_in, q_out, k_new, v_new, start_pos, n_new, kv: KvLayout, q_gain=None, k_gain=None, eps=1e-6,
              inv_freq=None, rope_scale=1.0):
-    """q_in [B,T,H,D] (or None), k_new / v_new [B,T,G,D] fp16 views; start_pos [B] int32; n_new [B] int32 or None;
-    kv: the cache to append to (kv_layout_paged / kv_layout_contiguous); inv_freq [D/2] fp32 or None."""
+    """q_in [B,T,H,D] (or None), k_new / v_new [B,T,G,D] views, all fp16 or all bf16 like the cache and the gains;
+    start_pos [B] int32; n_new [B] int32 or None; kv: the cache to append to (kv_layout_paged /
+    kv_layout_contiguous); inv_freq [D/2] fp32 or None."""
     lib = init(k_new.device.index)
     B, T, G, _ = k_new.shape
     kl, vl = act_layout(k_new), act_layout(v_new)
     ql = act_layout(q_in) if q_in is not None else ActLayout(0, 0, 0, 0, 0)
     H = q_in.shape[2] if q_in is not None else 0
     if q_in is not None:
-        _want(q_out, torch.float16, "q_out")
+        _want(q_out, k_new.dtype, "q_out")
         assert q_out.is_contiguous() and q_out.shape == q_in.shape
     _want(start_pos, torch.int32, "start_pos")
     _want_opt(n_new, torch.int32, "n_new")
-    _want_opt(q_gain, torch.float16, "q_gain")
-    _want_opt(k_gain, torch.float16, "k_gain")
+    _want_opt(q_gain, k_new.dtype, "q_gain")
+    _want_opt(k_gain, k_new.dtype, "k_gain")
     if inv_freq is not None:
         _want(inv_freq, torch.float32, "inv_freq")
         assert inv_freq.is_contiguous() and inv_freq.numel() == HEAD_DIM // 2

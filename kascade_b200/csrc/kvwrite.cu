@@ -6,12 +6,14 @@
 // (strategies/EfficientKascadeStrategy.py:144-150).  Bound by HBM: each new row is read once and
 // written once.
 //
-// Arithmetic follows the Hugging Face modules step by step so that results agree to the last fp16
-// bit wherever sin / cos round the same way: the norm is computed in fp32 and rounded to fp16 before
-// the gain is applied (LlamaRMSNorm / Qwen3RMSNorm), cos and sin are computed in fp32 from
-// position * inv_freq[i] (the model's own inverse-frequency table, so every rope-scaling variant is
-// covered), scaled and rounded to fp16, and  x * cos + rotate_half(x) * sin  is evaluated in fp16 with
-// a rounding after each product and after the sum (apply_rotary_pos_emb).
+// Arithmetic follows the Hugging Face modules step by step, in the model's type (fp16 or bf16), so that
+// results agree to the last bit wherever sin / cos round the same way: the norm is computed in fp32 and
+// rounded to that type before the gain is applied (LlamaRMSNorm / Qwen3RMSNorm), cos and sin are computed
+// in fp32 from position * inv_freq[i] (the model's own inverse-frequency table, so every rope-scaling
+// variant is covered), scaled and rounded to that type, and  x * cos + rotate_half(x) * sin  is evaluated
+// in that type with a rounding after each product and after the sum (apply_rotary_pos_emb).
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace kb200 {
@@ -36,9 +38,27 @@ struct KvWriteParams {
 // a warp takes four rows at a time.
 constexpr int kKvWriteThreads = 192;
 
+// The storage type of the activations and the cache: fp16, or bf16 (the pointers of KvWriteParams are then
+// bf16 in disguise).  Every rounding step is the one the Hugging Face modules take in that type.
+template <bool BF16> struct Pair { using T = __half2; using S = __half; };
+template <> struct Pair<true> { using T = __nv_bfloat162; using S = __nv_bfloat16; };
+__device__ __forceinline__ float2 to_f2(__half2 x) { return __half22float2(x); }
+__device__ __forceinline__ float2 to_f2(__nv_bfloat162 x) { return __bfloat1622float2(x); }
+template <bool BF16> __device__ __forceinline__ typename Pair<BF16>::T from_f2(float a, float b) {
+  if constexpr (BF16) return __floats2bfloat162_rn(a, b);
+  else return __floats2half2_rn(a, b);
+}
+template <bool BF16> __device__ __forceinline__ typename Pair<BF16>::S from_f(float a) {
+  if constexpr (BF16) return __float2bfloat16_rn(a);
+  else return __float2half_rn(a);
+}
+
+template <bool BF16>
 __global__ void __launch_bounds__(kKvWriteThreads) kv_write_kernel(const KvWriteParams p) {
-  __shared__ __align__(16) __half cos_s[kD / 2];
-  __shared__ __align__(16) __half sin_s[kD / 2];
+  using H2 = typename Pair<BF16>::T;
+  using H1 = typename Pair<BF16>::S;
+  __shared__ __align__(16) H1 cos_s[kD / 2];
+  __shared__ __align__(16) H1 sin_s[kD / 2];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b = blockIdx.x / p.T, t = blockIdx.x - b * p.T;
   const int n = p.n_new ? p.n_new[b] : p.T;
@@ -47,8 +67,8 @@ __global__ void __launch_bounds__(kKvWriteThreads) kv_write_kernel(const KvWrite
   if (p.inv_freq && tid < kD / 2) {
     float sn, cs;
     sincosf((float)pos * p.inv_freq[tid], &sn, &cs);
-    cos_s[tid] = __float2half_rn(cs * p.rope_scale);
-    sin_s[tid] = __float2half_rn(sn * p.rope_scale);
+    cos_s[tid] = from_f<BF16>(cs * p.rope_scale);
+    sin_s[tid] = from_f<BF16>(sn * p.rope_scale);
   }
   __syncthreads();
   const int heads = p.H + 2 * p.G;                                   // Q heads, K heads, V heads
@@ -63,43 +83,43 @@ __global__ void __launch_bounds__(kKvWriteThreads) kv_write_kernel(const KvWrite
                                   : p.v_new + b * p.v_sb + t * p.v_st + hh * p.v_sh;
     uint4 lo4 = reinterpret_cast<const uint4*>(src)[c];              // elements 8c .. 8c+7
     uint4 hi4 = reinterpret_cast<const uint4*>(src + kD / 2)[c];     // elements 64+8c .. 64+8c+7
-    __half2* lo = reinterpret_cast<__half2*>(&lo4);
-    __half2* hi = reinterpret_cast<__half2*>(&hi4);
+    H2* lo = reinterpret_cast<H2*>(&lo4);
+    H2* hi = reinterpret_cast<H2*>(&hi4);
     const __half* gain = kind == 0 ? p.q_gain : (kind == 1 ? p.k_gain : nullptr);
     // sum of squares of the row: all lanes of the warp take part in the shuffles, whatever their row is
     float ss = 0.f;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const float2 a = __half22float2(lo[e]), d2 = __half22float2(hi[e]);
+      const float2 a = to_f2(lo[e]), d2 = to_f2(hi[e]);
       ss += a.x * a.x + a.y * a.y + d2.x * d2.x + d2.y * d2.y;
     }
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
     if (gain) {
-      // x.float() * rsqrt(mean(x^2) + eps), rounded to fp16, times the gain (fp16 product)
+      // x.float() * rsqrt(mean(x^2) + eps), rounded to the storage type, times the gain (a product in that type)
       const float r = rsqrtf(ss / kD + p.eps);
       const uint4 g_lo4 = reinterpret_cast<const uint4*>(gain)[c];
       const uint4 g_hi4 = reinterpret_cast<const uint4*>(gain + kD / 2)[c];
-      const __half2* g_lo = reinterpret_cast<const __half2*>(&g_lo4);
-      const __half2* g_hi = reinterpret_cast<const __half2*>(&g_hi4);
+      const H2* g_lo = reinterpret_cast<const H2*>(&g_lo4);
+      const H2* g_hi = reinterpret_cast<const H2*>(&g_hi4);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float2 a = __half22float2(lo[e]), d2 = __half22float2(hi[e]);
-        lo[e] = __hmul2_rn(g_lo[e], __floats2half2_rn(a.x * r, a.y * r));
-        hi[e] = __hmul2_rn(g_hi[e], __floats2half2_rn(d2.x * r, d2.y * r));
+        const float2 a = to_f2(lo[e]), d2 = to_f2(hi[e]);
+        lo[e] = __hmul2_rn(g_lo[e], from_f2<BF16>(a.x * r, a.y * r));
+        hi[e] = __hmul2_rn(g_hi[e], from_f2<BF16>(d2.x * r, d2.y * r));
       }
     }
     if (kind != 2 && p.inv_freq) {
       const uint4 cs4 = reinterpret_cast<const uint4*>(cos_s)[c];
       const uint4 sn4 = reinterpret_cast<const uint4*>(sin_s)[c];
-      const __half2* cs = reinterpret_cast<const __half2*>(&cs4);
-      const __half2* sn = reinterpret_cast<const __half2*>(&sn4);
+      const H2* cs = reinterpret_cast<const H2*>(&cs4);
+      const H2* sn = reinterpret_cast<const H2*>(&sn4);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         // first half:  x_lo * cos + (-x_hi) * sin ; second half:  x_hi * cos + x_lo * sin
         // (the _rn forms are never contracted into a fused multiply-add, which would skip a rounding)
-        const __half2 new_lo = __hadd2_rn(__hmul2_rn(lo[e], cs[e]), __hmul2_rn(__hneg2(hi[e]), sn[e]));
-        const __half2 new_hi = __hadd2_rn(__hmul2_rn(hi[e], cs[e]), __hmul2_rn(lo[e], sn[e]));
+        const H2 new_lo = __hadd2_rn(__hmul2_rn(lo[e], cs[e]), __hmul2_rn(__hneg2(hi[e]), sn[e]));
+        const H2 new_hi = __hadd2_rn(__hmul2_rn(hi[e], cs[e]), __hmul2_rn(lo[e], sn[e]));
         lo[e] = new_lo;
         hi[e] = new_hi;
       }
@@ -131,9 +151,11 @@ extern "C" int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const k
   KB_REQUIRE(k_new && k_new->ptr && v_new && v_new->ptr && start_pos && kv && kv->k && kv->v,
              "kv_write: null pointer");
   KB_REQUIRE(batch >= 0 && max_new >= 0 && num_kv_heads > 0 && num_q_heads >= 0, "kv_write: bad sizes");
-  KB_REQUIRE(k_new->dtype == KB200_FP16 && v_new->dtype == KB200_FP16 && kv->dtype == KB200_FP16 &&
-                 (!q_in || !q_in->ptr || q_in->dtype == KB200_FP16),
-             "kv_write: fp16 only (its arithmetic follows the Hugging Face fp16 modules step by step)");
+  KB_REQUIRE((k_new->dtype == KB200_FP16 || k_new->dtype == KB200_BF16) && v_new->dtype == k_new->dtype &&
+                 kv->dtype == k_new->dtype && (!q_in || !q_in->ptr || q_in->dtype == k_new->dtype),
+             "kv_write: q / k / v and the cache must all be fp16 or all bf16 (its arithmetic follows the Hugging Face "
+             "modules step by step in that type; gains are in the same type)");
+  const bool bf16 = k_new->dtype == KB200_BF16;
   KB_REQUIRE(kv->page_size >= 1 && (kv->page_size & (kv->page_size - 1)) == 0,
              "kv_write: page_size must be a power of two (got %d)", kv->page_size);
   KB_REQUIRE(!inv_freq || (reinterpret_cast<uintptr_t>(inv_freq) & 7) == 0, "kv_write: inv_freq must be 8-byte aligned");
@@ -178,7 +200,8 @@ extern "C" int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const k
   p.B = batch; p.T = max_new; p.H = with_q ? num_q_heads : 0; p.G = num_kv_heads;
   const int64_t blocks = (int64_t)batch * max_new;                   // one CTA per (sequence, new token)
   KB_REQUIRE(blocks < (1ll << 31), "kv_write: too many tokens for one launch");
-  kv_write_kernel<<<(unsigned)blocks, kKvWriteThreads, 0, (cudaStream_t)stream>>>(p);
+  if (bf16) kv_write_kernel<true><<<(unsigned)blocks, kKvWriteThreads, 0, (cudaStream_t)stream>>>(p);
+  else kv_write_kernel<false><<<(unsigned)blocks, kKvWriteThreads, 0, (cudaStream_t)stream>>>(p);
   KB_CHECK_LAUNCH("kv_write_kernel");
   return 0;
 }

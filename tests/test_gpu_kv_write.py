@@ -13,45 +13,48 @@ def _inv_freq(theta):
 
 
 def _close_fp16(got, want, what):
-    """Equal up to the last fp16 bit of cos / sin: the device's sincosf and the host's cos / sin may round a
-    value differently now and then, which moves one of the two products (magnitude up to ~4 for N(0,1) inputs)
-    by one unit in its last place, 2^-9; the sum can be much smaller than the products."""
+    """Equal up to the last bit of cos / sin in the storage type: the device's sincosf and the host's cos / sin may
+    round a value differently now and then, which moves one of the two products (magnitude up to ~4 for N(0,1)
+    inputs) by one unit in its last place, 2^-9 in fp16 (2^-6 in bf16); the sum can be much smaller than the
+    products."""
+    ulp = 2.0 ** -8 if got.dtype == torch.float16 else 2.0 ** -5
     got, want = got.float().cpu(), want.float().cpu()
     diff = (got - want).abs()
-    bad = diff > 2.0 ** -8
+    bad = diff > ulp
     assert not bool(bad.any()), f"{what}: {int(bad.sum())} elements differ, max {diff.max().item():.3e}"
     frac = float((diff > 0).float().mean())
     assert frac < 0.02, f"{what}: {frac:.3%} of the elements are not bit-identical"
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
 @pytest.mark.parametrize("with_norm", [False, True], ids=["llama", "qwen3_qknorm"])
 @pytest.mark.parametrize("with_q", [True, False], ids=["q", "no_q"])
-def test_kv_write_paged(with_norm, with_q):
+def test_kv_write_paged(with_norm, with_q, dtype):
     from kascade_b200 import _native as nat
     dev = torch.device("cuda")
     g = torch.Generator().manual_seed(3)
     B, T, H, G, page = 3, 37, 8, 2, 16
     start = [0, 70001, 4095]
     n_new = [37, 5, 20]
-    q = torch.randn(B, T, H, D, generator=g).half()
-    k = torch.randn(B, T, G, D, generator=g).half()
-    v = torch.randn(B, T, G, D, generator=g).half()
+    q = torch.randn(B, T, H, D, generator=g).to(dtype)
+    k = torch.randn(B, T, G, D, generator=g).to(dtype)
+    v = torch.randn(B, T, G, D, generator=g).to(dtype)
     max_len = max(s + n for s, n in zip(start, n_new))
     pps = -(-max_len // page)
     n_pages = B * pps + 2
     block_table = torch.randperm(n_pages, generator=g)[: B * pps].view(B, pps).to(torch.int32)
-    k_cache = torch.randn(n_pages, page, G, D, generator=g).half()
-    v_cache = torch.randn(n_pages, page, G, D, generator=g).half()
+    k_cache = torch.randn(n_pages, page, G, D, generator=g).to(dtype)
+    v_cache = torch.randn(n_pages, page, G, D, generator=g).to(dtype)
     inv_freq = _inv_freq(500000.0)
-    q_gain = (1 + 0.1 * torch.randn(D, generator=g)).half() if with_norm else None
-    k_gain = (1 + 0.1 * torch.randn(D, generator=g)).half() if with_norm else None
+    q_gain = (1 + 0.1 * torch.randn(D, generator=g)).to(dtype) if with_norm else None
+    k_gain = (1 + 0.1 * torch.randn(D, generator=g)).to(dtype) if with_norm else None
 
     ref_kc, ref_vc = k_cache.clone(), v_cache.clone()
     ref_q = oracle_kv_write(q if with_q else None, k, v, start, n_new, ref_kc, ref_vc, block_table, page,
                             q_gain, k_gain, 1e-6, inv_freq, 1.0)
 
     kc, vc, bt = k_cache.to(dev), v_cache.to(dev), block_table.to(dev)
-    q_out = torch.full((B, T, H, D), 9.0, dtype=torch.float16, device=dev)
+    q_out = torch.full((B, T, H, D), 9.0, dtype=dtype, device=dev)
     nat.kv_write(q.to(dev) if with_q else None, q_out if with_q else None, k.to(dev), v.to(dev),
                  torch.tensor(start, dtype=torch.int32, device=dev), torch.tensor(n_new, dtype=torch.int32, device=dev),
                  nat.kv_layout_paged(kc, vc, bt), None if q_gain is None else q_gain.to(dev),
