@@ -1,21 +1,108 @@
-// Exact per-row Top-k by radix select (one CTA per row).
+// Exact per-row Top-k (one CTA per row): the k-th largest score is bracketed from a sample, the few
+// candidates inside the bracket are selected among exactly in shared memory, and the selected positions are
+// written in ascending index order.
 //
 // Replaces the torch.topk call sites of the reference's efficient path
-// (strategies/EfficientKascadeStrategy.py:82,90,111).  The row is read from global memory (L2 after
-// the first pass): three 11/11/10-bit histogram passes find the k-th largest key exactly, a fourth pass
-// compacts the selected positions in ascending index order, taking ties at the threshold from the
-// lowest index upwards.
+// (strategies/EfficientKascadeStrategy.py:82,90,111).
+//
+//   1. Bracket: 4096 (8192 for rows beyond 65536) evenly spaced samples of the row go into a 2048-bin histogram
+//      over the samples' own key range, and those in the bins around the sample ranks k/n * samples -/+
+//      (5 sigma + 16) into a second one over just these bins; its bins give two keys lo <= hi.
+//   2. One pass over the row counts the scores above hi and appends the keys in [lo, hi] to a list in shared
+//      memory (a few per cent of the row).  If  count(> hi) < k <= count(> hi) + |list|  and the list fits, the
+//      k-th largest score is the (k - count(> hi))-th largest of the list: a radix select over the list (11-bit
+//      digits of key - lo, only as many as hi - lo has bits) finds it exactly.  Rows of up to 4096 scores skip
+//      the sample: the whole row is the list.
+//   3. Otherwise (the sample misjudged the row, which the check above detects) the k-th largest key is found
+//      by three 11/11/10-bit histogram passes over the row itself.
+//   4. Every warp owns a contiguous piece of the row: a counting pass gives each warp its number of scores
+//      above and equal to the threshold, and the last pass writes the selected positions in index order with
+//      warp-local prefix sums only, taking ties at the threshold from the lowest index upwards.
+// The row is read from HBM once; the later passes find it in L1 / L2.
 #include "common.cuh"
 
 namespace kb200 {
 
 constexpr int kTopkThreads = 512;
-constexpr int kTopkBins = 2048;                           // 11-bit digits: 3 passes cover the 32-bit key
+constexpr int kTopkWarps = kTopkThreads / 32;
+constexpr int kTopkBins = 2048;                           // 11-bit digits
+constexpr int kCandCap = 8192;                            // keys the candidate lists hold, one list per warp
+constexpr int kWarpList = kCandCap / kTopkWarps;          // 512
+constexpr int kListRow = 4096;                            // rows up to this length are selected from directly
+constexpr int kTopkUnroll = 4;                            // 16-byte loads a lane keeps in flight in the streaming passes
 
 // order-preserving map float -> uint32 (larger float <=> larger key)
 __device__ __forceinline__ uint32_t float_key(float x) {
-  uint32_t b = __float_as_uint(x);
-  return b ^ ((b >> 31) ? 0xFFFFFFFFu : 0x80000000u);
+  const uint32_t b = __float_as_uint(x);
+  return b ^ ((uint32_t)((int32_t)b >> 31) | 0x80000000u);   // flips all bits of a negative, the sign of the rest
+}
+// Keys of one 16-byte piece.  Positions beyond the row (only the row's last piece has any, and the lanes past
+// the end) get key 0, which no score has (it would be a NaN with all bits set) and which the passes below never
+// count: they compare against keys >= 1.
+__device__ __forceinline__ void piece_keys(const float4& x, int i4, int n4, int n, uint32_t (&u)[4]) {
+  u[0] = float_key(x.x); u[1] = float_key(x.y); u[2] = float_key(x.z); u[3] = float_key(x.w);
+  if (i4 >= n4 - 1) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (i4 * 4 + e >= n) u[e] = 0u;
+  }
+}
+
+struct TopkShared {
+  uint32_t hist[kTopkBins];
+  uint32_t cand[kCandCap];
+  uint32_t red[kTopkWarps], red2[kTopkWarps];
+  uint32_t warp_gt[kTopkWarps], warp_eq[kTopkWarps], list_len[kTopkWarps];
+  uint32_t digit, remaining;
+};
+
+// Bin d of sh.hist with  count(bins > d) < r <= count(bins >= d)  (1 <= r <= total); every thread gets d and
+// r - count(bins > d).  All threads of the CTA call it.
+__device__ __forceinline__ void find_bin(TopkShared& sh, uint32_t r, uint32_t& digit, uint32_t& rest) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t c[4], ssum = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { c[i] = sh.hist[tid * 4 + i]; ssum += c[i]; }
+  uint32_t suf = ssum;                                   // sum over lanes >= lane of this warp
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t v = __shfl_down_sync(0xFFFFFFFFu, suf, off);
+    if (lane + off < 32) suf += v;
+  }
+  if (lane == 0) sh.red[warp] = suf;
+  __syncthreads();
+  uint32_t higher = 0;
+#pragma unroll
+  for (int w = 0; w < kTopkWarps; ++w) higher += w > warp ? sh.red[w] : 0u;
+  const uint32_t above = higher + suf - ssum;            // candidates in bins of higher threads
+  if (above < r && r <= above + ssum) {
+    uint32_t acc = above;
+#pragma unroll
+    for (int i = 3; i >= 0; --i) {
+      if (acc < r && acc + c[i] >= r) {
+        sh.digit = (uint32_t)(tid * 4 + i);
+        sh.remaining = r - acc;
+      }
+      acc += c[i];
+    }
+  }
+  __syncthreads();
+  digit = sh.digit;
+  rest = sh.remaining;
+  __syncthreads();
+}
+
+__device__ __forceinline__ uint32_t block_sum(TopkShared& sh, uint32_t v) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+  if (lane == 0) sh.red[warp] = v;
+  __syncthreads();
+  uint32_t t = 0;
+#pragma unroll
+  for (int w = 0; w < kTopkWarps; ++w) t += sh.red[w];
+  __syncthreads();
+  return t;
 }
 
 __global__ void __launch_bounds__(kTopkThreads)
@@ -23,9 +110,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
                    const int32_t* __restrict__ n_valid, const int32_t* __restrict__ k_row, int k_max,
                    int32_t* __restrict__ out_idx, int64_t idx_stride, int32_t* __restrict__ out_count,
                    int64_t rows) {
-  __shared__ uint32_t hist[kTopkBins];
-  __shared__ uint32_t warp_tot[kTopkThreads / 32];
-  __shared__ uint32_t sh_digit, sh_remaining;
+  __shared__ TopkShared sh;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -42,119 +127,365 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
     }
     const float4* row4 = reinterpret_cast<const float4*>(scores + row * row_stride);
     const int n4 = (n + 3) >> 2;
-    const int iters = (n4 + kTopkThreads - 1) / kTopkThreads;
+    // warp w owns the 16-byte pieces [w_begin, w_end) of the row
+    const int seg4 = (n4 + kTopkWarps - 1) / kTopkWarps;
+    const int w_begin = min(warp * seg4, n4), w_end = min(w_begin + seg4, n4);
+    const int w_iters = (w_end - w_begin + 31) >> 5;
 
-    // three histogram passes over key bits [31:21], [20:10], [9:0]; post-softmax scores spread over
-    // many exponent / mantissa bins in every pass, so plain shared-memory atomics do
-    uint32_t prefix = 0, mask = 0, remaining = (uint32_t)k;
-#pragma unroll 1
-    for (int pass = 0; pass < 3; ++pass) {
-      const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
-      const uint32_t dmask = pass == 2 ? 1023u : 2047u;
-      for (int i = tid; i < kTopkBins; i += kTopkThreads) hist[i] = 0;
+    // ---- 1. bracket [lo_key, hi_key] of the k-th largest key from a sample ----------------------------
+    // Two histogram levels: 2048 bins over the sample's key range, then 2048 bins over the few bins the two
+    // ranks fell into - scores of a row often sit in a narrow band far below the row's maximum, and the first
+    // level alone would cut that band into a dozen bins.
+    uint32_t lo_key = 0u, hi_key = 0xFFFFFFFFu;
+    const bool sampled = n > kListRow;
+    if (sampled) {
+      const int f4 = n > 65536 ? 4 : 2;                  // 16-byte pieces per thread: 4096 or 8192 sampled scores
+      const int n_samp = f4 * kTopkThreads * 4;
+      uint32_t sk[16], smin = 0xFFFFFFFFu, smax = 0u;
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        if (it < f4) {
+          const int pos = (int)(((int64_t)(it * kTopkThreads + tid) * n4) >> (f4 == 4 ? 11 : 10));  // < n4 - 1
+          const float4 x = __ldg(row4 + pos);
+          sk[it * 4 + 0] = float_key(x.x); sk[it * 4 + 1] = float_key(x.y);
+          sk[it * 4 + 2] = float_key(x.z); sk[it * 4 + 3] = float_key(x.w);
+        } else {
+          sk[it * 4 + 0] = sk[it * 4 + 1] = sk[it * 4 + 2] = sk[it * 4 + 3] = sk[0];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) { smin = min(smin, sk[i]); smax = max(smax, sk[i]); }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        smin = min(smin, __shfl_xor_sync(0xFFFFFFFFu, smin, off));
+        smax = max(smax, __shfl_xor_sync(0xFFFFFFFFu, smax, off));
+      }
+      if (lane == 0) { sh.red[warp] = smin; sh.red2[warp] = smax; }
+      for (int i = tid; i < kTopkBins; i += kTopkThreads) sh.hist[i] = 0;
       __syncthreads();
-      for (int it = 0; it < iters; ++it) {
-        const int i4 = it * kTopkThreads + tid;
-        const bool in = i4 < n4;
-        const float4 x = in ? __ldg(row4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
-        const float xs[4] = {x.x, x.y, x.z, x.w};
+      uint32_t bottom = 0xFFFFFFFFu, top = 0u;
+#pragma unroll
+      for (int w = 0; w < kTopkWarps; ++w) { bottom = min(bottom, sh.red[w]); top = max(top, sh.red2[w]); }
+      const float ks = (float)k * (float)n_samp / (float)n;                          // sample rank of the threshold
+      const float margin = 5.f * sqrtf(ks) + 16.f;
+      int r_hi = (int)(ks - margin), r_lo = (int)(ks + margin) + 1;                  // ranks from the top, 1-based
+      // level 1
+      uint32_t z_lo = bottom, z_hi = top, above = 0;     // zoom window and the samples above it
+      {
+        const uint32_t range = top - bottom;
+        const int shift = (range >> 11) ? (32 - __clz(range) - 11) : 0;              // (range >> shift) <= 2047
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (i < f4 * 4) atomicAdd(&sh.hist[(sk[i] - bottom) >> shift], 1u);
+        __syncthreads();
+        uint32_t b, rest;
+        if (r_hi >= 1) {
+          find_bin(sh, (uint32_t)r_hi, b, rest);
+          above = (uint32_t)r_hi - rest;                                             // samples in the bins above b
+          const uint64_t edge = (uint64_t)bottom + ((uint64_t)(b + 1) << shift);      // first key above bin b
+          if (edge - 1 < (uint64_t)top) z_hi = (uint32_t)(edge - 1);
+        }
+        if (r_lo <= n_samp) {
+          find_bin(sh, (uint32_t)r_lo, b, rest);
+          z_lo = bottom + (b << shift);
+        }
+      }
+      // level 2: the samples inside [z_lo, z_hi]
+      {
+        const uint32_t range = z_hi - z_lo;
+        const int shift = (range >> 11) ? (32 - __clz(range) - 11) : 0;
+        for (int i = tid; i < kTopkBins; i += kTopkThreads) sh.hist[i] = 0;
+        __syncthreads();
+        uint32_t inside = 0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (i < f4 * 4 && sk[i] >= z_lo && sk[i] <= z_hi) {
+            atomicAdd(&sh.hist[(sk[i] - z_lo) >> shift], 1u);
+            ++inside;
+          }
+        }
+        const uint32_t n_inside = block_sum(sh, inside);  // (its barriers also publish the histogram)
+        r_hi -= (int)above;
+        r_lo -= (int)above;
+        uint32_t b, rest;
+        if (r_hi >= 1 && (uint32_t)r_hi <= n_inside) {    // keys above the bin of rank r_hi: (very likely) all selected
+          find_bin(sh, (uint32_t)r_hi, b, rest);
+          const uint64_t edge = (uint64_t)z_lo + ((uint64_t)(b + 1) << shift);
+          hi_key = edge - 1 < (uint64_t)z_hi ? (uint32_t)(edge - 1) : z_hi;
+        } else if (r_hi >= 1) {
+          hi_key = z_hi;
+        }
+        if (r_lo >= 1 && (uint32_t)r_lo <= n_inside) {    // keys below the bin of rank r_lo: (very likely) none selected
+          find_bin(sh, (uint32_t)r_lo, b, rest);
+          lo_key = z_lo + (b << shift);
+        } else if (r_lo > (int)n_inside && r_lo + (int)above <= n_samp) {
+          lo_key = z_lo;
+        }
+      }
+      if (hi_key < lo_key) { lo_key = 0u; hi_key = 0xFFFFFFFFu; }
+    }
+
+    // ---- 2. count the keys above hi_key, collect those in [lo_key, hi_key] --------------------------------
+    // Every warp walks its own piece of the row and appends to a list of its own, so that nothing is shared
+    // (one counter for the whole CTA would serialise a thousand atomics per row), and so that the list later
+    // tells the warp how many of its scores lie above / at the threshold.
+    lo_key = max(lo_key, 1u);
+    uint32_t cnt_gt = 0, my_cand = 0;                     // my_cand: entries in this warp's list (warp-uniform)
+    uint32_t* const my_list = sh.cand + warp * kWarpList;
+    {
+      for (int it0 = 0; it0 < w_iters; it0 += kTopkUnroll) {
+        float4 xs[kTopkUnroll];                           // several loads in flight per lane
+#pragma unroll
+        for (int j = 0; j < kTopkUnroll; ++j) {
+          const int i4 = w_begin + (it0 + j) * 32 + lane;
+          xs[j] = i4 < w_end ? __ldg(row4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < kTopkUnroll; ++j) {
+          const int i4 = w_begin + (it0 + j) * 32 + lane;
+          uint32_t u[4];
+          piece_keys(xs[j], i4 < w_end ? i4 : n4, n4, n, u);
+          bool cand[4];
+          uint32_t c = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const bool gt = u[e] > hi_key;
+            cand[e] = !gt && u[e] >= lo_key;
+            cnt_gt += gt;
+            c += cand[e];
+          }
+          if (__any_sync(0xFFFFFFFFu, c != 0)) {
+            uint32_t incl = c;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+              const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+              if (lane >= off) incl += v;
+            }
+            uint32_t pos = my_cand + incl - c;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (cand[e]) {
+                if (pos < (uint32_t)kWarpList) my_list[pos] = u[e];
+                ++pos;
+              }
+            }
+            my_cand += __shfl_sync(0xFFFFFFFFu, incl, 31);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) cnt_gt += __shfl_xor_sync(0xFFFFFFFFu, cnt_gt, off);
+    const uint32_t my_gt_hi = cnt_gt;                     // scores of this warp's piece above hi_key
+    if (lane != 0) cnt_gt = 0;
+    if (lane == 0) sh.list_len[warp] = my_cand;
+    const uint32_t n_gt = block_sum(sh, cnt_gt);          // (its barriers also publish the lists and their lengths)
+    uint32_t n_cand = 0;
+    bool fits = true;
+#pragma unroll
+    for (int w = 0; w < kTopkWarps; ++w) {
+      n_cand += sh.list_len[w];
+      fits = fits && sh.list_len[w] <= (uint32_t)kWarpList;
+    }
+    // entry s of the concatenated lists: list s / kWarpList, position s % kWarpList
+    auto list_valid = [&](uint32_t s_) { return (s_ & (kWarpList - 1)) < sh.list_len[s_ / kWarpList]; };
+
+    if (!sampled) {
+      // the whole row is the list: its own key range instead of all 32 bits, so that the first digit spreads
+      uint32_t cmin = 0xFFFFFFFFu, cmax = 0u;
+      for (uint32_t i = tid; i < (uint32_t)kCandCap; i += kTopkThreads)
+        if (list_valid(i)) { cmin = min(cmin, sh.cand[i]); cmax = max(cmax, sh.cand[i]); }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        cmin = min(cmin, __shfl_xor_sync(0xFFFFFFFFu, cmin, off));
+        cmax = max(cmax, __shfl_xor_sync(0xFFFFFFFFu, cmax, off));
+      }
+      if (lane == 0) { sh.red[warp] = cmin; sh.red2[warp] = cmax; }
+      __syncthreads();
+#pragma unroll
+      for (int w = 0; w < kTopkWarps; ++w) { cmin = min(cmin, sh.red[w]); cmax = max(cmax, sh.red2[w]); }
+      __syncthreads();
+      lo_key = cmin;
+      hi_key = cmax;
+    }
+    uint32_t tau = 0, need_eq = 0;
+    if (fits && n_gt < (uint32_t)k && (uint32_t)k <= n_gt + n_cand) {
+      // ---- the k-th largest key is the (k - n_gt)-th largest of the list --------------------------------
+      const uint32_t range = hi_key - lo_key;
+      const int nb = range ? 32 - __clz(range) : 0;
+      uint32_t prefix = 0, mask = 0, remaining = (uint32_t)k - n_gt;
+#pragma unroll 1
+      for (int hb = nb; hb > 0; hb -= 11) {
+        const int shift = max(hb - 11, 0);
+        const uint32_t dmask = (1u << (hb - shift)) - 1u;
+        for (int i = tid; i < kTopkBins; i += kTopkThreads) sh.hist[i] = 0;
+        __syncthreads();
+        for (uint32_t i = tid; i < (uint32_t)kCandCap; i += kTopkThreads) {
+          const uint32_t v = sh.cand[i] - lo_key;
+          if (list_valid(i) && (v & mask) == prefix) atomicAdd(&sh.hist[(v >> shift) & dmask], 1u);
+        }
+        __syncthreads();
+        uint32_t d;
+        find_bin(sh, remaining, d, remaining);
+        prefix |= d << shift;
+        mask |= dmask << shift;
+      }
+      tau = lo_key + prefix;
+      need_eq = remaining;
+      // this warp's scores above / at the threshold: those above hi_key, and what its own list says
+      uint32_t g = 0, q = 0;
+      for (uint32_t i = lane; i < my_cand; i += 32) {
+        const uint32_t v = my_list[i];
+        g += v > tau;
+        q += v == tau;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        g += __shfl_xor_sync(0xFFFFFFFFu, g, off);
+        q += __shfl_xor_sync(0xFFFFFFFFu, q, off);
+      }
+      if (lane == 0) { sh.warp_gt[warp] = my_gt_hi + g; sh.warp_eq[warp] = q; }
+    } else {
+      // ---- 3. the sample misjudged the row: three histogram passes over the row itself -------------------
+      const int iters = (n4 + kTopkThreads - 1) / kTopkThreads;
+      uint32_t prefix = 0, mask = 0, remaining = (uint32_t)k;
+#pragma unroll 1
+      for (int pass = 0; pass < 3; ++pass) {
+        const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
+        const uint32_t dmask = pass == 2 ? 1023u : 2047u;
+        for (int i = tid; i < kTopkBins; i += kTopkThreads) sh.hist[i] = 0;
+        __syncthreads();
+        for (int it = 0; it < iters; ++it) {
+          const int i4 = it * kTopkThreads + tid;
+          const bool in = i4 < n4;
+          const float4 x = in ? __ldg(row4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t u = float_key(xs[e]);
+            const bool valid = in && (i4 * 4 + e < n) && ((u & mask) == prefix);
+            const uint32_t digit = (u >> shift) & dmask;
+            if (pass == 0) {
+              // the leading bits of the scores of a row mostly coincide: aggregate within the warp
+              const uint32_t peers = __match_any_sync(0xFFFFFFFFu, valid ? digit : 0xFFFFu);
+              if (valid && (__ffs(peers) - 1) == lane) atomicAdd(&sh.hist[digit], (uint32_t)__popc(peers));
+            } else if (valid) {
+              atomicAdd(&sh.hist[digit], 1u);
+            }
+          }
+        }
+        __syncthreads();
+        uint32_t d;
+        find_bin(sh, remaining, d, remaining);
+        prefix |= d << shift;
+        mask |= dmask << shift;
+      }
+      tau = prefix;
+      need_eq = remaining;
+      // per warp: scores above / equal to the threshold in its piece (one more pass over the row)
+      {
+        uint32_t g = 0, q = 0;
+        for (int it0 = 0; it0 < w_iters; it0 += kTopkUnroll) {
+          float4 xs[kTopkUnroll];
+  #pragma unroll
+          for (int j = 0; j < kTopkUnroll; ++j) {
+            const int i4 = w_begin + (it0 + j) * 32 + lane;
+            xs[j] = i4 < w_end ? __ldg(row4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+  #pragma unroll
+          for (int j = 0; j < kTopkUnroll; ++j) {
+            const int i4 = w_begin + (it0 + j) * 32 + lane;
+            const bool in = i4 < w_end;
+            const uint32_t u[4] = {float_key(xs[j].x), float_key(xs[j].y), float_key(xs[j].z), float_key(xs[j].w)};
+  #pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const bool ok = in && (i4 * 4 + e < n);
+              g += ok && u[e] > tau;
+              q += ok && u[e] == tau;
+            }
+          }
+        }
+  #pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+          g += __shfl_xor_sync(0xFFFFFFFFu, g, off);
+          q += __shfl_xor_sync(0xFFFFFFFFu, q, off);
+        }
+        if (lane == 0) { sh.warp_gt[warp] = g; sh.warp_eq[warp] = q; }
+      }
+    }
+    // tau = key of the k-th largest score; `need_eq` keys equal to it are wanted, the lowest positions first
+
+    __syncthreads();
+    uint32_t gt_before = 0, eq_before = 0;                // in the pieces of the warps before this one
+#pragma unroll
+    for (int w = 0; w < kTopkWarps; ++w) {
+      gt_before += w < warp ? sh.warp_gt[w] : 0u;
+      eq_before += w < warp ? sh.warp_eq[w] : 0u;
+    }
+    // ---- 4. write the selected positions of this warp's piece, in index order -----------------------------
+    for (int it0 = 0; it0 < w_iters; it0 += kTopkUnroll) {
+      float4 xs[kTopkUnroll];
+#pragma unroll
+      for (int j = 0; j < kTopkUnroll; ++j) {
+        const int i4 = w_begin + (it0 + j) * 32 + lane;
+        xs[j] = i4 < w_end ? __ldg(row4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < kTopkUnroll; ++j) {
+        const int i4 = w_begin + (it0 + j) * 32 + lane;
+        uint32_t u[4];
+        piece_keys(xs[j], i4 < w_end ? i4 : n4, n4, n, u);
+        uint32_t gt[4], packed = 0;
+        bool any_eq = false;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const uint32_t u = float_key(xs[e]);
-          const bool valid = in && (i4 * 4 + e < n) && ((u & mask) == prefix);
-          const uint32_t digit = (u >> shift) & dmask;
-          if (pass == 0) {
-            // the leading bits of the scores of a row mostly coincide: aggregate within the warp
-            const uint32_t peers = __match_any_sync(0xFFFFFFFFu, valid ? digit : 0xFFFFu);
-            if (valid && (__ffs(peers) - 1) == lane) atomicAdd(&hist[digit], (uint32_t)__popc(peers));
-          } else if (valid) {
-            atomicAdd(&hist[digit], 1u);
+          gt[e] = u[e] > tau;
+          packed += gt[e];
+          any_eq |= u[e] == tau;
+        }
+        if (!__any_sync(0xFFFFFFFFu, any_eq)) {
+          // no score at the threshold among these 128: positions follow from the counts of the lanes before
+          uint32_t incl = packed;
+#pragma unroll
+          for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+            if (lane >= off) incl += v;
           }
-        }
-      }
-      __syncthreads();
-      // bin d with count(> d) < remaining <= count(>= d): suffix sums over 4 bins per thread
-      {
-        uint32_t c[4], ssum = 0;
+          uint32_t at = gt_before + min(eq_before, need_eq) + incl - packed;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { c[i] = hist[tid * 4 + i]; ssum += c[i]; }
-        uint32_t suf = ssum;                               // sum over lanes >= lane of this warp
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-          const uint32_t v = __shfl_down_sync(0xFFFFFFFFu, suf, off);
-          if (lane + off < 32) suf += v;
-        }
-        if (lane == 0) warp_tot[warp] = suf;
-        __syncthreads();
-        uint32_t higher = 0;
-#pragma unroll
-        for (int w = 0; w < kTopkThreads / 32; ++w) higher += w > warp ? warp_tot[w] : 0u;
-        const uint32_t above = higher + suf - ssum;        // candidates in bins of higher threads
-        if (above < remaining && remaining <= above + ssum) {
-          uint32_t acc = above;
-#pragma unroll
-          for (int i = 3; i >= 0; --i) {
-            if (acc < remaining && acc + c[i] >= remaining) {
-              sh_digit = (uint32_t)(tid * 4 + i);
-              sh_remaining = remaining - acc;
-            }
-            acc += c[i];
+          for (int e = 0; e < 4; ++e) {
+            if (gt[e]) out[at++] = i4 * 4 + e;
           }
+          gt_before += __shfl_sync(0xFFFFFFFFu, incl, 31);
+        } else {
+          uint32_t eq[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            eq[e] = u[e] == tau;
+            packed += eq[e] << 16;
+          }
+          uint32_t incl = packed;                          // (eq << 16 | gt) of the lanes up to this one
+#pragma unroll
+          for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+            if (lane >= off) incl += v;
+          }
+          const uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+          const uint32_t excl = incl - packed;
+          uint32_t g0 = gt_before + (excl & 0xFFFFu), q0 = eq_before + (excl >> 16);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const bool sel = gt[e] || (eq[e] && q0 < need_eq);
+            if (sel) out[g0 + min(q0, need_eq)] = i4 * 4 + e;
+            g0 += gt[e];
+            q0 += eq[e];
+          }
+          gt_before += total & 0xFFFFu;
+          eq_before += total >> 16;
         }
       }
-      __syncthreads();
-      prefix |= sh_digit << shift;
-      mask |= dmask << shift;
-      remaining = sh_remaining;
-      __syncthreads();
     }
-    // prefix = key of the k-th largest score; `remaining` keys equal to it are still wanted
-    const uint32_t tau = prefix, need_eq = remaining;
-    uint32_t gt_total = 0, eq_total = 0;
-    for (int it = 0; it < iters; ++it) {
-      int i4 = it * kTopkThreads + tid;
-      bool in = i4 < n4;
-      float4 x = in ? __ldg(row4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
-      float xs[4] = {x.x, x.y, x.z, x.w};
-      uint32_t gt[4], eq[4], packed = 0;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        uint32_t u = float_key(xs[e]);
-        bool ok = in && (i4 * 4 + e < n);
-        gt[e] = ok && (u > tau);
-        eq[e] = ok && (u == tau);
-        packed += gt[e] + (eq[e] << 16);
-      }
-      // block-wide exclusive scan of (eq << 16 | gt) in index order
-      uint32_t incl = packed;
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, off);
-        if (lane >= off) incl += v;
-      }
-      if (lane == 31) warp_tot[warp] = incl;
-      __syncthreads();
-      uint32_t base = 0, total = 0;
-#pragma unroll
-      for (int w = 0; w < kTopkThreads / 32; ++w) {
-        uint32_t v = warp_tot[w];
-        if (w < warp) base += v;
-        total += v;
-      }
-      uint32_t excl = base + incl - packed;
-      uint32_t gt_before = gt_total + (excl & 0xFFFFu);
-      uint32_t eq_before = eq_total + (excl >> 16);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        bool sel = gt[e] || (eq[e] && eq_before < need_eq);
-        if (sel) out[gt_before + min(eq_before, need_eq)] = i4 * 4 + e;
-        gt_before += gt[e];
-        eq_before += eq[e];
-      }
-      gt_total += total & 0xFFFFu;
-      eq_total += total >> 16;
-      __syncthreads();
-    }
+    __syncthreads();                                      // the shared arrays are reused by the next row
   }
 }
 
