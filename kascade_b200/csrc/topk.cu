@@ -8,16 +8,17 @@
 //   1. Bracket: 4096 (8192 for rows beyond 65536) evenly spaced samples of the row go into a 2048-bin histogram
 //      over the samples' own key range, and those in the bins around the sample ranks k/n * samples -/+
 //      (5 sigma + 16) into a second one over just these bins; its bins give two keys lo <= hi.
-//   2. One pass over the row counts the scores above hi and appends the keys in [lo, hi] to a list in shared
-//      memory (a few per cent of the row).  If  count(> hi) < k <= count(> hi) + |list|  and the list fits, the
-//      k-th largest score is the (k - count(> hi))-th largest of the list: a radix select over the list (11-bit
-//      digits of key - lo, only as many as hi - lo has bits) finds it exactly.  Rows of up to 4096 scores skip
-//      the sample: the whole row is the list.
-//   3. Otherwise (the sample misjudged the row, which the check above detects) the k-th largest key is found
-//      by three 11/11/10-bit histogram passes over the row itself.
-//   4. Every warp owns a contiguous piece of the row: a counting pass gives each warp its number of scores
-//      above and equal to the threshold, and the last pass writes the selected positions in index order with
-//      warp-local prefix sums only, taking ties at the threshold from the lowest index upwards.
+//   2. One pass over the row: every warp owns a contiguous piece of it, counts its scores above hi and appends
+//      its keys in [lo, hi] (a few per cent of the row) to a list of its own in shared memory.  If
+//      count(> hi) < k <= count(> hi) + |lists|  and the lists fit, the k-th largest score is the
+//      (k - count(> hi))-th largest of the lists: a radix select over them (11-bit digits of key - lo, only as
+//      many as hi - lo has bits) finds it exactly, and every warp learns from its own list how many of its scores
+//      lie above / at the threshold.  Rows of up to 4096 scores skip the sample: the whole row goes to the lists.
+//   3. Otherwise (the sample misjudged the row, which the check above detects, or a list overflowed) the k-th
+//      largest key is found by three 11/11/10-bit histogram passes over the row itself, and a counting pass
+//      gives the warps their numbers.
+//   4. The last pass writes the selected positions of every warp's piece in index order, with warp-local prefix
+//      sums only, taking ties at the threshold from the lowest index upwards.
 // The row is read from HBM once; the later passes find it in L1 / L2.
 #include "common.cuh"
 

@@ -1,4 +1,4 @@
-"""Radix-select Top-k against torch.topk / the tie-band rule (GPU)."""
+"""Top-k select against torch.topk / the tie-band rule (GPU)."""
 import pytest
 import torch
 
@@ -81,6 +81,49 @@ def test_clustered_post_softmax_like_scores():
     for r in range(4):
         ok, msg = band_check(scores[r], out[r].tolist(), k, n, rel=0.0)
         assert ok, msg
+
+
+def test_rows_the_sample_cannot_bracket():
+    """Rows on which the sampled bracket must fail, so that the histogram passes over the whole row decide: half of
+    a long row tied at the threshold (the candidate lists overflow), a threshold inside a run of equal values with
+    k beyond the distinct part, a step distribution, and a long row with negative values only."""
+    g = torch.Generator().manual_seed(17)
+    n = 40000
+    rows = torch.zeros(4, n)
+    rows[0] = torch.where(torch.rand(n, generator=g) < 0.5, torch.tensor(0.25), torch.rand(n, generator=g) * 0.2)
+    rows[0, :100] = torch.rand(100, generator=g) + 1.0                    # 100 distinct large values, ~20000 ties at 0.25
+    rows[1] = 0.125                                                        # everything tied except a few
+    rows[1, 1000:1010] = 3.0
+    rows[2] = (torch.arange(n) % 7).float()                                # seven plateaus
+    rows[3] = -torch.rand(n, generator=g) - 1.0
+    k = 5000
+    out, cnt = _run(rows, None, None, k)
+    assert cnt.tolist() == [k] * 4
+    for r in range(4):
+        vals = rows[r]
+        order = torch.sort(vals, descending=True, stable=True).indices     # ties: lowest index first
+        tau = vals[order[k - 1]]
+        above = (vals > tau).nonzero().flatten()
+        at = (vals == tau).nonzero().flatten()[: k - above.numel()]
+        want = torch.cat([above, at]).sort().values
+        assert torch.equal(out[r].long(), want), f"row {r}"
+
+
+@pytest.mark.parametrize("n,k", [(131072, 13000), (70000, 128), (4097, 4000), (4096, 4000), (100000, 99999)])
+def test_long_rows_and_extreme_budgets(n, k):
+    g = torch.Generator().manual_seed(n)
+    from kascade_b200 import _native as nat
+    dev = torch.device("cuda")
+    stride = (n + 3) // 4 * 4 + 8
+    scores = torch.exp(3 * torch.randn(3, stride, generator=g) - 6)        # heavy-tailed, like pooled attention mass
+    scores[:, n:] = 1e9                                                    # beyond n_cols: must be ignored
+    out = torch.full((3, k), -7, dtype=torch.int32, device=dev)
+    cnt = torch.zeros(3, dtype=torch.int32, device=dev)
+    nat.topk_select(scores.to(dev), None, None, k, out, cnt, n_cols=n)
+    torch.cuda.synchronize()
+    ref = torch.topk(scores[:, :n], k, dim=-1).indices.sort(-1).values
+    assert cnt.tolist() == [k] * 3
+    assert torch.equal(out.cpu().long(), ref)
 
 
 def test_rejects_bad_arguments():
