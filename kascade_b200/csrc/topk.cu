@@ -5,17 +5,17 @@
 // Replaces the torch.topk call sites of the reference's efficient path
 // (strategies/EfficientKascadeStrategy.py:82,90,111).
 //
-//   1. Bracket: 4096 (8192 for rows beyond 65536) evenly spaced samples of the row go into a 2048-bin histogram
+//   1. Bracket: 4096 (8192 for rows beyond 65536) evenly spaced samples of the row go into a 512-bin histogram
 //      over the samples' own key range, and those in the bins around the sample ranks k/n * samples -/+
 //      (5 sigma + 16) into a second one over just these bins; its bins give two keys lo <= hi.
 //   2. One pass over the row: every warp owns a contiguous piece of it, counts its scores above hi and appends
 //      its keys in [lo, hi] (a few per cent of the row) to a list of its own in shared memory.  If
 //      count(> hi) < k <= count(> hi) + |lists|  and the lists fit, the k-th largest score is the
-//      (k - count(> hi))-th largest of the lists: a radix select over them (11-bit digits of key - lo, only as
+//      (k - count(> hi))-th largest of the lists: a radix select over them (9-bit digits of key - lo, only as
 //      many as hi - lo has bits) finds it exactly, and every warp learns from its own list how many of its scores
 //      lie above / at the threshold.  Rows of up to 4096 scores skip the sample: the whole row goes to the lists.
 //   3. Otherwise (the sample misjudged the row, which the check above detects, or a list overflowed) the k-th
-//      largest key is found by three 11/11/10-bit histogram passes over the row itself, and a counting pass
+//      largest key is found by four 9/9/9/5-bit histogram passes over the row itself, and a counting pass
 //      gives the warps their numbers.
 //   4. The last pass writes the selected positions of every warp's piece in index order, with warp-local prefix
 //      sums only, taking ties at the threshold from the lowest index upwards.
@@ -26,7 +26,8 @@ namespace kb200 {
 
 constexpr int kTopkThreads = 512;
 constexpr int kTopkWarps = kTopkThreads / 32;
-constexpr int kTopkBins = 2048;                           // 11-bit digits
+constexpr int kDigit = 9;
+constexpr int kTopkBins = 1 << kDigit;                            // 9-bit digits: one warp can search a histogram
 constexpr int kCandCap = 8192;                            // keys the candidate lists hold, one list per warp
 constexpr int kWarpList = kCandCap / kTopkWarps;          // 512
 constexpr int kListRow = 4096;                            // rows up to this length are selected from directly
@@ -58,33 +59,33 @@ struct TopkShared {
 };
 
 // Bin d of sh.hist with  count(bins > d) < r <= count(bins >= d)  (1 <= r <= total); every thread gets d and
-// r - count(bins > d).  All threads of the CTA call it.
+// r - count(bins > d).  All threads of the CTA call it, after a barrier that completed the histogram; one warp
+// does the search (16 bins per lane) - the per-row costs of this kernel are instructions, and sixteen warps
+// searching together would issue ten times as many.
 __device__ __forceinline__ void find_bin(TopkShared& sh, uint32_t r, uint32_t& digit, uint32_t& rest) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  uint32_t c[4], ssum = 0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (warp == 0) {
+    constexpr int kPer = kTopkBins / 32;
+    uint32_t c[kPer], ssum = 0;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) { c[i] = sh.hist[tid * 4 + i]; ssum += c[i]; }
-  uint32_t suf = ssum;                                   // sum over lanes >= lane of this warp
+    for (int i = 0; i < kPer; ++i) { c[i] = sh.hist[lane * kPer + i]; ssum += c[i]; }
+    uint32_t suf = ssum;                                 // sum over lanes >= lane
 #pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    const uint32_t v = __shfl_down_sync(0xFFFFFFFFu, suf, off);
-    if (lane + off < 32) suf += v;
-  }
-  if (lane == 0) sh.red[warp] = suf;
-  __syncthreads();
-  uint32_t higher = 0;
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t v = __shfl_down_sync(0xFFFFFFFFu, suf, off);
+      if (lane + off < 32) suf += v;
+    }
+    const uint32_t above = suf - ssum;                   // in the bins of higher lanes
+    if (above < r && r <= above + ssum) {
+      uint32_t acc = above;
 #pragma unroll
-  for (int w = 0; w < kTopkWarps; ++w) higher += w > warp ? sh.red[w] : 0u;
-  const uint32_t above = higher + suf - ssum;            // candidates in bins of higher threads
-  if (above < r && r <= above + ssum) {
-    uint32_t acc = above;
-#pragma unroll
-    for (int i = 3; i >= 0; --i) {
-      if (acc < r && acc + c[i] >= r) {
-        sh.digit = (uint32_t)(tid * 4 + i);
-        sh.remaining = r - acc;
+      for (int i = kPer - 1; i >= 0; --i) {
+        if (acc < r && acc + c[i] >= r) {
+          sh.digit = (uint32_t)(lane * kPer + i);
+          sh.remaining = r - acc;
+        }
+        acc += c[i];
       }
-      acc += c[i];
     }
   }
   __syncthreads();
@@ -134,7 +135,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
     const int w_iters = (w_end - w_begin + 31) >> 5;
 
     // ---- 1. bracket [lo_key, hi_key] of the k-th largest key from a sample ----------------------------
-    // Two histogram levels: 2048 bins over the sample's key range, then 2048 bins over the few bins the two
+    // Two histogram levels: 512 bins over the sample's key range, then 512 bins over the few bins the two
     // ranks fell into - scores of a row often sit in a narrow band far below the row's maximum, and the first
     // level alone would cut that band into a dozen bins.
     uint32_t lo_key = 0u, hi_key = 0xFFFFFFFFu;
@@ -174,7 +175,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
       uint32_t z_lo = bottom, z_hi = top, above = 0;     // zoom window and the samples above it
       {
         const uint32_t range = top - bottom;
-        const int shift = (range >> 11) ? (32 - __clz(range) - 11) : 0;              // (range >> shift) <= 2047
+        const int shift = (range >> kDigit) ? (32 - __clz(range) - kDigit) : 0;      // (range >> shift) < kTopkBins
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           if (i < f4 * 4) atomicAdd(&sh.hist[(sk[i] - bottom) >> shift], 1u);
@@ -194,7 +195,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
       // level 2: the samples inside [z_lo, z_hi]
       {
         const uint32_t range = z_hi - z_lo;
-        const int shift = (range >> 11) ? (32 - __clz(range) - 11) : 0;
+        const int shift = (range >> kDigit) ? (32 - __clz(range) - kDigit) : 0;
         for (int i = tid; i < kTopkBins; i += kTopkThreads) sh.hist[i] = 0;
         __syncthreads();
         uint32_t inside = 0;
@@ -288,14 +289,12 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
       n_cand += sh.list_len[w];
       fits = fits && sh.list_len[w] <= (uint32_t)kWarpList;
     }
-    // entry s of the concatenated lists: list s / kWarpList, position s % kWarpList
-    auto list_valid = [&](uint32_t s_) { return (s_ & (kWarpList - 1)) < sh.list_len[s_ / kWarpList]; };
 
     if (!sampled) {
       // the whole row is the list: its own key range instead of all 32 bits, so that the first digit spreads
       uint32_t cmin = 0xFFFFFFFFu, cmax = 0u;
-      for (uint32_t i = tid; i < (uint32_t)kCandCap; i += kTopkThreads)
-        if (list_valid(i)) { cmin = min(cmin, sh.cand[i]); cmax = max(cmax, sh.cand[i]); }
+      if (fits)
+        for (uint32_t i = lane; i < my_cand; i += 32) { cmin = min(cmin, my_list[i]); cmax = max(cmax, my_list[i]); }
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) {
         cmin = min(cmin, __shfl_xor_sync(0xFFFFFFFFu, cmin, off));
@@ -316,14 +315,14 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
       const int nb = range ? 32 - __clz(range) : 0;
       uint32_t prefix = 0, mask = 0, remaining = (uint32_t)k - n_gt;
 #pragma unroll 1
-      for (int hb = nb; hb > 0; hb -= 11) {
-        const int shift = max(hb - 11, 0);
+      for (int hb = nb; hb > 0; hb -= kDigit) {
+        const int shift = max(hb - kDigit, 0);
         const uint32_t dmask = (1u << (hb - shift)) - 1u;
         for (int i = tid; i < kTopkBins; i += kTopkThreads) sh.hist[i] = 0;
         __syncthreads();
-        for (uint32_t i = tid; i < (uint32_t)kCandCap; i += kTopkThreads) {
-          const uint32_t v = sh.cand[i] - lo_key;
-          if (list_valid(i) && (v & mask) == prefix) atomicAdd(&sh.hist[(v >> shift) & dmask], 1u);
+        for (uint32_t i = lane; i < my_cand; i += 32) {    // every warp bins its own list
+          const uint32_t v = my_list[i] - lo_key;
+          if ((v & mask) == prefix) atomicAdd(&sh.hist[(v >> shift) & dmask], 1u);
         }
         __syncthreads();
         uint32_t d;
@@ -351,28 +350,23 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
       const int iters = (n4 + kTopkThreads - 1) / kTopkThreads;
       uint32_t prefix = 0, mask = 0, remaining = (uint32_t)k;
 #pragma unroll 1
-      for (int pass = 0; pass < 3; ++pass) {
-        const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
-        const uint32_t dmask = pass == 2 ? 1023u : 2047u;
+      for (int hb = 32; hb > 0; hb -= kDigit) {
+        const int shift = max(hb - kDigit, 0);
+        const uint32_t dmask = (1u << (hb - shift)) - 1u;
         for (int i = tid; i < kTopkBins; i += kTopkThreads) sh.hist[i] = 0;
         __syncthreads();
         for (int it = 0; it < iters; ++it) {
           const int i4 = it * kTopkThreads + tid;
-          const bool in = i4 < n4;
-          const float4 x = in ? __ldg(row4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
-          const float xs[4] = {x.x, x.y, x.z, x.w};
+          const float4 x = i4 < n4 ? __ldg(row4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          uint32_t u[4];
+          piece_keys(x, i4 < n4 ? i4 : n4, n4, n, u);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const uint32_t u = float_key(xs[e]);
-            const bool valid = in && (i4 * 4 + e < n) && ((u & mask) == prefix);
-            const uint32_t digit = (u >> shift) & dmask;
-            if (pass == 0) {
-              // the leading bits of the scores of a row mostly coincide: aggregate within the warp
-              const uint32_t peers = __match_any_sync(0xFFFFFFFFu, valid ? digit : 0xFFFFu);
-              if (valid && (__ffs(peers) - 1) == lane) atomicAdd(&sh.hist[digit], (uint32_t)__popc(peers));
-            } else if (valid) {
-              atomicAdd(&sh.hist[digit], 1u);
-            }
+            const bool valid = u[e] != 0u && ((u[e] & mask) == prefix);
+            const uint32_t digit = (u[e] >> shift) & dmask;
+            // equal digits are common here (that is why the sample failed): aggregate within the warp
+            const uint32_t peers = __match_any_sync(0xFFFFFFFFu, valid ? digit : 0xFFFFu);
+            if (valid && (__ffs(peers) - 1) == lane) atomicAdd(&sh.hist[digit], (uint32_t)__popc(peers));
           }
         }
         __syncthreads();
