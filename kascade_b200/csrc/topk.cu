@@ -94,15 +94,33 @@ __device__ __forceinline__ void find_bin(TopkShared& sh, uint32_t r, uint32_t& d
   __syncthreads();
 }
 
+// sum / minimum / maximum over the 16 per-warp values of an array in shared memory: one load per lane and four
+// shuffles instead of sixteen loads per thread
+__device__ __forceinline__ uint32_t warps_sum(const uint32_t* a) {
+  uint32_t v = a[threadIdx.x & (kTopkWarps - 1)];
+#pragma unroll
+  for (int off = kTopkWarps / 2; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+  return v;
+}
+__device__ __forceinline__ uint32_t warps_min(const uint32_t* a) {
+  uint32_t v = a[threadIdx.x & (kTopkWarps - 1)];
+#pragma unroll
+  for (int off = kTopkWarps / 2; off > 0; off >>= 1) v = min(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+  return v;
+}
+__device__ __forceinline__ uint32_t warps_max(const uint32_t* a) {
+  uint32_t v = a[threadIdx.x & (kTopkWarps - 1)];
+#pragma unroll
+  for (int off = kTopkWarps / 2; off > 0; off >>= 1) v = max(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+  return v;
+}
 __device__ __forceinline__ uint32_t block_sum(TopkShared& sh, uint32_t v) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
   if (lane == 0) sh.red[warp] = v;
   __syncthreads();
-  uint32_t t = 0;
-#pragma unroll
-  for (int w = 0; w < kTopkWarps; ++w) t += sh.red[w];
+  const uint32_t t = warps_sum(sh.red);
   __syncthreads();
   return t;
 }
@@ -165,9 +183,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
       if (lane == 0) { sh.red[warp] = smin; sh.red2[warp] = smax; }
       for (int i = tid; i < kTopkBins; i += kTopkThreads) sh.hist[i] = 0;
       __syncthreads();
-      uint32_t bottom = 0xFFFFFFFFu, top = 0u;
-#pragma unroll
-      for (int w = 0; w < kTopkWarps; ++w) { bottom = min(bottom, sh.red[w]); top = max(top, sh.red2[w]); }
+      const uint32_t bottom = warps_min(sh.red), top = warps_max(sh.red2);
       const float ks = (float)k * (float)n_samp / (float)n;                          // sample rank of the threshold
       const float margin = 5.f * sqrtf(ks) + 16.f;
       int r_hi = (int)(ks - margin), r_lo = (int)(ks + margin) + 1;                  // ranks from the top, 1-based
@@ -177,8 +193,11 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
         const uint32_t range = top - bottom;
         const int shift = (range >> kDigit) ? (32 - __clz(range) - kDigit) : 0;      // (range >> shift) < kTopkBins
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          if (i < f4 * 4) atomicAdd(&sh.hist[(sk[i] - bottom) >> shift], 1u);
+        for (int i = 0; i < 8; ++i) atomicAdd(&sh.hist[(sk[i] - bottom) >> shift], 1u);
+        if (f4 == 4) {
+#pragma unroll
+          for (int i = 8; i < 16; ++i) atomicAdd(&sh.hist[(sk[i] - bottom) >> shift], 1u);
+        }
         __syncthreads();
         uint32_t b, rest;
         if (r_hi >= 1) {
@@ -200,10 +219,19 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
         __syncthreads();
         uint32_t inside = 0;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          if (i < f4 * 4 && sk[i] >= z_lo && sk[i] <= z_hi) {
+        for (int i = 0; i < 8; ++i) {
+          if (sk[i] - z_lo <= range) {                     // z_lo <= key <= z_hi
             atomicAdd(&sh.hist[(sk[i] - z_lo) >> shift], 1u);
             ++inside;
+          }
+        }
+        if (f4 == 4) {
+#pragma unroll
+          for (int i = 8; i < 16; ++i) {
+            if (sk[i] - z_lo <= range) {
+              atomicAdd(&sh.hist[(sk[i] - z_lo) >> shift], 1u);
+              ++inside;
+            }
           }
         }
         const uint32_t n_inside = block_sum(sh, inside);  // (its barriers also publish the histogram)
@@ -244,6 +272,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
         }
 #pragma unroll
         for (int j = 0; j < kTopkUnroll; ++j) {
+          if (it0 + j >= w_iters) break;                  // (the same for the whole warp)
           const int i4 = w_begin + (it0 + j) * 32 + lane;
           uint32_t u[4];
           piece_keys(xs[j], i4 < w_end ? i4 : n4, n4, n, u);
@@ -282,13 +311,8 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
     if (lane != 0) cnt_gt = 0;
     if (lane == 0) sh.list_len[warp] = my_cand;
     const uint32_t n_gt = block_sum(sh, cnt_gt);          // (its barriers also publish the lists and their lengths)
-    uint32_t n_cand = 0;
-    bool fits = true;
-#pragma unroll
-    for (int w = 0; w < kTopkWarps; ++w) {
-      n_cand += sh.list_len[w];
-      fits = fits && sh.list_len[w] <= (uint32_t)kWarpList;
-    }
+    const uint32_t n_cand = warps_sum(sh.list_len);
+    const bool fits = warps_max(sh.list_len) <= (uint32_t)kWarpList;
 
     if (!sampled) {
       // the whole row is the list: its own key range instead of all 32 bits, so that the first digit spreads
@@ -302,8 +326,8 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
       }
       if (lane == 0) { sh.red[warp] = cmin; sh.red2[warp] = cmax; }
       __syncthreads();
-#pragma unroll
-      for (int w = 0; w < kTopkWarps; ++w) { cmin = min(cmin, sh.red[w]); cmax = max(cmax, sh.red2[w]); }
+      cmin = warps_min(sh.red);
+      cmax = warps_max(sh.red2);
       __syncthreads();
       lo_key = cmin;
       hi_key = cmax;
@@ -411,11 +435,17 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
     // tau = key of the k-th largest score; `need_eq` keys equal to it are wanted, the lowest positions first
 
     __syncthreads();
-    uint32_t gt_before = 0, eq_before = 0;                // in the pieces of the warps before this one
+    uint32_t gt_before, eq_before;                        // in the pieces of the warps before this one
+    {
+      const int w = lane & (kTopkWarps - 1);
+      uint32_t g = w < warp ? sh.warp_gt[w] : 0u, q = w < warp ? sh.warp_eq[w] : 0u;
 #pragma unroll
-    for (int w = 0; w < kTopkWarps; ++w) {
-      gt_before += w < warp ? sh.warp_gt[w] : 0u;
-      eq_before += w < warp ? sh.warp_eq[w] : 0u;
+      for (int off = kTopkWarps / 2; off > 0; off >>= 1) {
+        g += __shfl_xor_sync(0xFFFFFFFFu, g, off);
+        q += __shfl_xor_sync(0xFFFFFFFFu, q, off);
+      }
+      gt_before = g;
+      eq_before = q;
     }
     // ---- 4. write the selected positions of this warp's piece, in index order -----------------------------
     for (int it0 = 0; it0 < w_iters; it0 += kTopkUnroll) {
@@ -427,6 +457,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
       }
 #pragma unroll
       for (int j = 0; j < kTopkUnroll; ++j) {
+        if (it0 + j >= w_iters) break;                    // (the same for the whole warp)
         const int i4 = w_begin + (it0 + j) * 32 + lane;
         uint32_t u[4];
         piece_keys(xs[j], i4 < w_end ? i4 : n4, n4, n, u);
