@@ -125,7 +125,10 @@ __device__ __forceinline__ uint32_t block_sum(TopkShared& sh, uint32_t v) {
   return t;
 }
 
-__global__ void __launch_bounds__(kTopkThreads)
+#ifndef KB200_TOPK_MIN_CTAS
+#define KB200_TOPK_MIN_CTAS 2      // CTAs per SM the register allocation aims at (3, with a few spills, measured no faster)
+#endif
+__global__ void __launch_bounds__(kTopkThreads, KB200_TOPK_MIN_CTAS)
 topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_cols,
                    const int32_t* __restrict__ n_valid, const int32_t* __restrict__ k_row, int k_max,
                    int32_t* __restrict__ out_idx, int64_t idx_stride, int32_t* __restrict__ out_count,
