@@ -88,7 +88,7 @@ def test_mixed_or_unknown_dtypes_are_rejected():
         nat.prefill_dense(q, k, k, 0.1, out, None)
     with pytest.raises(nat.KascadeNativeError, match="fp16 or bf16"):
         nat.prefill_dense(q.float(), k, k, 0.1, out, None)
-    kb = k.bfloat16()
-    with pytest.raises(nat.KascadeNativeError, match="fp16 only"):
+    kb = k.bfloat16()                                      # bf16 rows into an fp16 cache: one type for all operands
+    with pytest.raises(nat.KascadeNativeError, match="all be fp16 or all bf16"):
         nat.kv_write(None, None, kb, kb, torch.zeros(1, dtype=torch.int32, device="cuda"), None,
-                     nat.kv_layout_contiguous(kb.transpose(1, 2), kb.transpose(1, 2)))
+                     nat.kv_layout_contiguous(k.transpose(1, 2), k.transpose(1, 2)))
