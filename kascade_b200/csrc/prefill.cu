@@ -104,6 +104,19 @@ __device__ __forceinline__ void cp_wait_all() { asm volatile("cp.async.wait_all;
 // which is what bounds the softmax; every fourth exponential goes this way instead.  x is rounded
 // to the nearest integer n by adding 1.5 * 2^23 (n lands in the low mantissa bits), 2^(x - n) on
 // [-0.5, 0.5] is a degree-4 polynomial (relative error 3e-6), and n is added to the exponent field.
+// Share of the exponentials of the lse and pool passes that goes to the FMA pipes: every fourth one, and with
+// EXTRA = n > 0 one more in every n-th group of four.  Measured at 32 768 tokens: the lse pass is fastest with
+// a quarter (3/8: +11 %), the pool pass, whose other arithmetic is packed two per instruction, with 3/8 (-4 %).
+#ifndef KB200_POLY_EXTRA_LSE
+#define KB200_POLY_EXTRA_LSE 0
+#endif
+#ifndef KB200_POLY_EXTRA_POOL
+#define KB200_POLY_EXTRA_POOL 2
+#endif
+template <int EXTRA>
+__device__ __forceinline__ constexpr bool poly_also(int i) {
+  return EXTRA > 0 && ((i >> 2) % (EXTRA > 0 ? EXTRA : 1)) == 0;
+}
 __device__ __forceinline__ float ex2_fma(float x) {
 #ifdef KB200_NO_FMA_EXP
   return ex2(x);
@@ -1028,7 +1041,8 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             s0 += ex2(fmaf(__uint_as_float(sr[part][i]), p.scale2, -m_new));
-            s1 += ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -m_new));
+            s1 += poly_also<KB200_POLY_EXTRA_LSE>(i) ? ex2_fma(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -m_new))
+                               : ex2(fmaf(__uint_as_float(sr[part][i + 1]), p.scale2, -m_new));
             s2 += ex2(fmaf(__uint_as_float(sr[part][i + 2]), p.scale2, -m_new));
             s3 += ex2_fma(fmaf(__uint_as_float(sr[part][i + 3]), p.scale2, -m_new));
           }
@@ -1118,7 +1132,7 @@ tile_prefill_kernel(const __grid_constant__ PrefillParams p, const __grid_consta
             float x0, x1, x2, x3;
             unpair_f(fma2(pair_u(sr[part][i], sr[part][i + 1]), scale_2, pair_f(l4.x, l4.y)), x0, x1);
             unpair_f(fma2(pair_u(sr[part][i + 2], sr[part][i + 3]), scale_2, pair_f(l4.z, l4.w)), x2, x3);
-            a01 = add2(a01, pair_f(ex2(x0), ex2(x1)));
+            a01 = add2(a01, pair_f(ex2(x0), poly_also<KB200_POLY_EXTRA_POOL>(i) ? ex2_fma(x1) : ex2(x1)));
             a23 = add2(a23, pair_f(ex2(x2), ex2_fma(x3)));
           }
         float a0, a1, a2, a3;
