@@ -297,7 +297,8 @@ class EfficientKascadeStrategy(Strategy):
             n_seen = seen.sum(-1)
             first = torch.where(n_seen > 0, seen.to(torch.int32).argmax(-1), torch.zeros_like(n_seen))
             both = torch.stack([first, n_seen]).tolist()
-            self.check_status(attention_mask.device)                              # the host has just synchronised
+            if attention_mask.is_cuda:
+                self.check_status(attention_mask.device)                          # the host has just synchronised
             starts, lens = [int(x) for x in both[0]], [int(x) for x in both[1]]
             self._pad_ref, self._pad_version = weakref.ref(attention_mask), attention_mask._version
             self._pads = None if all(n == Lk for n in lens) else (starts, lens)

@@ -119,3 +119,32 @@ def test_long_prompt_workload_is_normalised():
     assert (rms_q - 1).abs().max() < 5e-3 and (rms_k - 1).abs().max() < 5e-3
     hm = wl.head_mapping()
     assert len(hm) == 36 and all(hm[a] == list(range(8)) for a in QWEN3_ANCHORS)
+
+
+def test_padding_is_read_from_the_last_mask_row():
+    """Left / right / mixed padding of a batch, additive and boolean masks, from the key columns the last query row
+    may see (host logic only: no kernel runs)."""
+    import torch
+    from kascade_b200 import EfficientKascadeStrategy
+    s = EfficientKascadeStrategy([0], "x/y", k=10, tile_size=32, head_mapping=[list(range(8))] * 2, register=False)
+    L = 48
+    ok = torch.tril(torch.ones(L, L, dtype=torch.bool))[None].repeat(3, 1, 1)
+    ok[1, :, :7] = False                       # 7 padded positions on the left
+    ok[2, :, L - 5:] = False                   # 5 on the right
+    ok[2, :, :2] = False                       # and 2 on the left
+    additive = torch.zeros(3, 1, L, L).masked_fill_(~ok[:, None], torch.finfo(torch.float32).min)
+    assert s._padding(additive, 3, L) == ([0, 7, 2], [48, 41, 41])
+    assert s._padding(ok[:, None].clone(), 3, L) == ([0, 7, 2], [48, 41, 41])
+    assert s._padding(torch.zeros(3, 1, L, L), 3, L) is None           # nothing hidden: the batched path
+    assert s._padding(additive, 2, L) is None                          # not this batch's mask
+
+
+def test_row_table_layout_describes_one_token_pages():
+    import torch
+    from kascade_b200 import _native as nat
+    k = torch.zeros(2, 8, 40, 128, dtype=torch.float16)
+    table = torch.arange(40, dtype=torch.int32)[None].repeat(2, 1) + torch.tensor([[3], [0]], dtype=torch.int32)
+    kv = nat.kv_layout_rows(k, k.clone(), table.contiguous())
+    assert kv.page_size == 1 and kv.block_table_stride == 40
+    assert (kv.stride_batch, kv.stride_page, kv.stride_token, kv.stride_head) == (8 * 40 * 128, 128, 128, 40 * 128)
+    assert kv.dtype == nat.FP16 if hasattr(nat, "FP16") else kv.dtype == 0
