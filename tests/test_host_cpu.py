@@ -139,12 +139,12 @@ def test_padding_is_read_from_the_last_mask_row():
     assert s._padding(additive, 2, L) is None                          # not this batch's mask
 
 
-def test_row_table_layout_describes_one_token_pages():
+def test_layout_helpers_refuse_host_tensors():
+    import pytest
     import torch
     from kascade_b200 import _native as nat
     k = torch.zeros(2, 8, 40, 128, dtype=torch.float16)
-    table = torch.arange(40, dtype=torch.int32)[None].repeat(2, 1) + torch.tensor([[3], [0]], dtype=torch.int32)
-    kv = nat.kv_layout_rows(k, k.clone(), table.contiguous())
-    assert kv.page_size == 1 and kv.block_table_stride == 40
-    assert (kv.stride_batch, kv.stride_page, kv.stride_token, kv.stride_head) == (8 * 40 * 128, 128, 128, 40 * 128)
-    assert kv.dtype == nat.FP16 if hasattr(nat, "FP16") else kv.dtype == 0
+    table = torch.zeros(2, 40, dtype=torch.int32)
+    for make in (lambda: nat.kv_layout_rows(k, k.clone(), table), lambda: nat.kv_layout_contiguous(k, k.clone())):
+        with pytest.raises(nat.KascadeNativeError, match="CUDA"):
+            make()
