@@ -350,7 +350,10 @@ int kb200_prefill_budgets(int32_t* n_valid, int32_t* k_row, int batch, int num_k
  *   k_new/v_new [B, T, G, D] views: the rows to append (T = max_new)
  *   start_pos   [B] int32: cache length of each sequence before the append (position of its first new token)
  *   n_new       [B] int32 number of new tokens per sequence (<= max_new), or NULL (= max_new)
- *   kv          the cache (written): paged with a block table that already covers the new positions, or contiguous
+ *   kv          the cache (written): paged with a block table that already covers the new positions, or contiguous;
+ *               or an FP8 cache (dtype KB200_FP8_E4M3, k_scale / v_scale given by the caller, e.g. calibrated per
+ *               layer): a row is stored as value / scale of its page and KV head (fp32 division, saturating at
+ *               +-448, round to nearest even) - the bytes the decode entry points read back as byte x scale
  *   q_norm_gain / k_norm_gain  [D] in the same type, or NULL (no norm);  norm_eps
  *   inv_freq    [D/2] fp32 inverse frequencies of the model's rotary embedding (device memory), or NULL
  *               (no rotary);  rope_scale multiplies cos and sin (1 for the default rope type)

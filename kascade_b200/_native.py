@@ -278,6 +278,12 @@ def _fp8_scales(k_scale, v_scale, need_v: bool):
         raise KascadeNativeError("k_scale and v_scale must have the same shape and strides")
 
 
+def _holding(layout, *tensors):
+    """The layouts carry raw device addresses: keep the tensors alive as long as the layout object is."""
+    layout._keep = tuple(t for t in tensors if t is not None)
+    return layout
+
+
 def kv_layout_paged(k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], block_table: torch.Tensor,
                     k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None) -> KvLayout:
     """vLLM-style cache [num_pages, page_size, G, D] and block table [B, max_pages] int32.  An FP8 cache
@@ -289,18 +295,19 @@ def kv_layout_paged(k_cache: torch.Tensor, v_cache: Optional[torch.Tensor], bloc
             assert v_cache.shape == k_cache.shape and v_cache.stride() == k_cache.stride() and v_cache.dtype == k_cache.dtype
         _fp8_scales(k_scale, v_scale, v_cache is not None)
         assert k_scale.shape == (k_cache.shape[0], k_cache.shape[2])
-        return KvLayout(k_cache.data_ptr(), 0 if v_cache is None else v_cache.data_ptr(), 0, k_cache.stride(0),
-                        k_cache.stride(1), k_cache.stride(2), block_table.data_ptr(), block_table.stride(0),
-                        k_cache.shape[1], FP8_E4M3, k_scale.data_ptr(), 0 if v_scale is None else v_scale.data_ptr(),
-                        0, k_scale.stride(0), k_scale.stride(1))
+        return _holding(KvLayout(k_cache.data_ptr(), 0 if v_cache is None else v_cache.data_ptr(), 0, k_cache.stride(0),
+                                 k_cache.stride(1), k_cache.stride(2), block_table.data_ptr(), block_table.stride(0),
+                                 k_cache.shape[1], FP8_E4M3, k_scale.data_ptr(),
+                                 0 if v_scale is None else v_scale.data_ptr(), 0, k_scale.stride(0), k_scale.stride(1)),
+                        k_cache, v_cache, block_table, k_scale, v_scale)
     code = _half_code(k_cache, "k_cache")
     assert k_cache.dim() == 4 and k_cache.stride(3) == 1
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     if v_cache is not None:
         assert v_cache.shape == k_cache.shape and v_cache.stride() == k_cache.stride() and v_cache.dtype == k_cache.dtype
-    return KvLayout(k_cache.data_ptr(), 0 if v_cache is None else v_cache.data_ptr(), 0, k_cache.stride(0),
-                    k_cache.stride(1), k_cache.stride(2), block_table.data_ptr(), block_table.stride(0),
-                    k_cache.shape[1], code)
+    return _holding(KvLayout(k_cache.data_ptr(), 0 if v_cache is None else v_cache.data_ptr(), 0, k_cache.stride(0),
+                             k_cache.stride(1), k_cache.stride(2), block_table.data_ptr(), block_table.stride(0),
+                             k_cache.shape[1], code), k_cache, v_cache, block_table)
 
 
 def kv_layout_contiguous(k: torch.Tensor, v: Optional[torch.Tensor], page_size: int = 16,
@@ -313,15 +320,16 @@ def kv_layout_contiguous(k: torch.Tensor, v: Optional[torch.Tensor], page_size: 
             assert v.shape == k.shape and v.stride() == k.stride() and v.dtype == k.dtype
         _fp8_scales(k_scale, v_scale, v is not None)
         assert k_scale.dim() == 3 and k_scale.shape[:2] == k.shape[:2]
-        return KvLayout(k.data_ptr(), 0 if v is None else v.data_ptr(), k.stride(0), k.stride(2) * page_size,
-                        k.stride(2), k.stride(1), 0, 0, page_size, FP8_E4M3, k_scale.data_ptr(),
-                        0 if v_scale is None else v_scale.data_ptr(), k_scale.stride(0), k_scale.stride(2), k_scale.stride(1))
+        return _holding(KvLayout(k.data_ptr(), 0 if v is None else v.data_ptr(), k.stride(0), k.stride(2) * page_size,
+                                 k.stride(2), k.stride(1), 0, 0, page_size, FP8_E4M3, k_scale.data_ptr(),
+                                 0 if v_scale is None else v_scale.data_ptr(), k_scale.stride(0), k_scale.stride(2),
+                                 k_scale.stride(1)), k, v, k_scale, v_scale)
     code = _half_code(k, "k")
     assert k.dim() == 4 and k.stride(3) == 1
     if v is not None:
         assert v.shape == k.shape and v.stride() == k.stride() and v.dtype == k.dtype
-    return KvLayout(k.data_ptr(), 0 if v is None else v.data_ptr(), k.stride(0), k.stride(2) * page_size,
-                    k.stride(2), k.stride(1), 0, 0, page_size, code)
+    return _holding(KvLayout(k.data_ptr(), 0 if v is None else v.data_ptr(), k.stride(0), k.stride(2) * page_size,
+                             k.stride(2), k.stride(1), 0, 0, page_size, code), k, v)
 
 
 def kv_layout_rows(k: torch.Tensor, v: Optional[torch.Tensor], row_table: torch.Tensor) -> KvLayout:
@@ -333,8 +341,8 @@ def kv_layout_rows(k: torch.Tensor, v: Optional[torch.Tensor], row_table: torch.
     assert row_table.dtype == torch.int32 and row_table.dim() == 2 and row_table.stride(1) == 1
     if v is not None:
         assert v.shape == k.shape and v.stride() == k.stride() and v.dtype == k.dtype
-    return KvLayout(k.data_ptr(), 0 if v is None else v.data_ptr(), k.stride(0), k.stride(2), k.stride(2), k.stride(1),
-                    row_table.data_ptr(), row_table.stride(0), 1, code)
+    return _holding(KvLayout(k.data_ptr(), 0 if v is None else v.data_ptr(), k.stride(0), k.stride(2), k.stride(2),
+                             k.stride(1), row_table.data_ptr(), row_table.stride(0), 1, code), k, v, row_table)
 
 
 def decode_workspace(batch: int, heads: int, splits: int, device) -> torch.Tensor:

@@ -28,6 +28,8 @@ struct KvWriteParams {
   int64_t c_sb, c_sp, c_st, c_sh;                                     // cache strides (batch, page, token, head)
   const int32_t* block_table; int bt_stride; int page_shift, page_mask;
   const __half* q_gain; const __half* k_gain; float eps;              // RMS-norm gains [D] or null
+  // FP8 (e4m3) cache: a row is stored as value / scale of its (page, KV head); strides of the cache in bytes
+  const float* k_scale; const float* v_scale; int64_t s_sb, s_sp, s_sh;
   const float* inv_freq; float rope_scale;                            // [D/2] inverse frequencies or null (no rotary)
   int B, T, H, G;
 };
@@ -53,7 +55,23 @@ template <bool BF16> __device__ __forceinline__ typename Pair<BF16>::S from_f(fl
   else return __float2half_rn(a);
 }
 
-template <bool BF16>
+// eight values of the storage type (four pairs) -> eight e4m3 bytes of value / scale (fp32 division, saturating,
+// round to nearest even)
+template <typename H2>
+__device__ __forceinline__ uint2 quantize8(const H2* x, float scale) {
+  uint32_t w[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float2 a = to_f2(x[2 * i]), b = to_f2(x[2 * i + 1]);
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(lo) : "f"(a.y / scale), "f"(a.x / scale));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(hi) : "f"(b.y / scale), "f"(b.x / scale));
+    w[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+  }
+  return make_uint2(w[0], w[1]);
+}
+
+template <bool BF16, bool FP8>
 __global__ void __launch_bounds__(kKvWriteThreads) kv_write_kernel(const KvWriteParams p) {
   using H2 = typename Pair<BF16>::T;
   using H1 = typename Pair<BF16>::S;
@@ -130,6 +148,16 @@ __global__ void __launch_bounds__(kKvWriteThreads) kv_write_kernel(const KvWrite
     } else {
       const int page = pos >> p.page_shift, slot = pos & p.page_mask;
       const int64_t phys = p.block_table ? (int64_t)p.block_table[(int64_t)b * p.bt_stride + page] : page;
+      if (FP8) {
+        if (active) {
+          const float sc = (kind == 1 ? p.k_scale : p.v_scale)[b * p.s_sb + phys * p.s_sp + hh * p.s_sh];
+          uint8_t* d8 = reinterpret_cast<uint8_t*>(kind == 1 ? p.k_cache : p.v_cache) + b * p.c_sb + phys * p.c_sp +
+                        slot * p.c_st + hh * p.c_sh;
+          reinterpret_cast<uint2*>(d8)[c] = quantize8(lo, sc);              // bytes 8c .. 8c+7
+          reinterpret_cast<uint2*>(d8 + kD / 2)[c] = quantize8(hi, sc);     // bytes 64+8c .. 64+8c+7
+        }
+        continue;
+      }
       dst = (kind == 1 ? p.k_cache : p.v_cache) + b * p.c_sb + phys * p.c_sp + slot * p.c_st + hh * p.c_sh;
     }
     if (active) {
@@ -151,10 +179,12 @@ extern "C" int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const k
   KB_REQUIRE(k_new && k_new->ptr && v_new && v_new->ptr && start_pos && kv && kv->k && kv->v,
              "kv_write: null pointer");
   KB_REQUIRE(batch >= 0 && max_new >= 0 && num_kv_heads > 0 && num_q_heads >= 0, "kv_write: bad sizes");
+  const bool fp8 = kv->dtype == KB200_FP8_E4M3;
   KB_REQUIRE((k_new->dtype == KB200_FP16 || k_new->dtype == KB200_BF16) && v_new->dtype == k_new->dtype &&
-                 kv->dtype == k_new->dtype && (!q_in || !q_in->ptr || q_in->dtype == k_new->dtype),
+                 (fp8 || kv->dtype == k_new->dtype) && (!q_in || !q_in->ptr || q_in->dtype == k_new->dtype),
              "kv_write: q / k / v and the cache must all be fp16 or all bf16 (its arithmetic follows the Hugging Face "
-             "modules step by step in that type; gains are in the same type)");
+             "modules step by step in that type; gains are in the same type), or the cache FP8 (e4m3) with scales");
+  KB_REQUIRE(!fp8 || (kv->k_scale && kv->v_scale), "kv_write: an FP8 cache needs k_scale / v_scale");
   const bool bf16 = k_new->dtype == KB200_BF16;
   KB_REQUIRE(kv->page_size >= 1 && (kv->page_size & (kv->page_size - 1)) == 0,
              "kv_write: page_size must be a power of two (got %d)", kv->page_size);
@@ -170,6 +200,9 @@ extern "C" int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const k
                  aligned(kv->k, kv->stride_batch, kv->stride_page, kv->stride_token) &&
                  aligned(kv->v, kv->stride_head, 0, 0),
              "kv_write: pointers must be 16-byte aligned and strides multiples of 8 elements");
+  KB_REQUIRE(!fp8 || (kv->stride_batch % 16 == 0 && kv->stride_page % 16 == 0 && kv->stride_token % 16 == 0 &&
+                      kv->stride_head % 16 == 0),
+             "kv_write: strides of an FP8 cache must be multiples of 16 bytes");
   if (batch == 0 || max_new == 0) return 0;
   KvWriteParams p{};
   if (with_q) {
@@ -192,6 +225,9 @@ extern "C" int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const k
   while ((1 << shift) < kv->page_size) ++shift;
   p.page_shift = shift;
   p.page_mask = kv->page_size - 1;
+  p.k_scale = kv->k_scale;
+  p.v_scale = kv->v_scale;
+  p.s_sb = kv->scale_stride_batch; p.s_sp = kv->scale_stride_page; p.s_sh = kv->scale_stride_head;
   p.q_gain = static_cast<const __half*>(q_norm_gain);
   p.k_gain = static_cast<const __half*>(k_norm_gain);
   p.eps = norm_eps;
@@ -200,8 +236,11 @@ extern "C" int kb200_kv_write(const kb200_act_layout* q_in, void* q_out, const k
   p.B = batch; p.T = max_new; p.H = with_q ? num_q_heads : 0; p.G = num_kv_heads;
   const int64_t blocks = (int64_t)batch * max_new;                   // one CTA per (sequence, new token)
   KB_REQUIRE(blocks < (1ll << 31), "kv_write: too many tokens for one launch");
-  if (bf16) kv_write_kernel<true><<<(unsigned)blocks, kKvWriteThreads, 0, (cudaStream_t)stream>>>(p);
-  else kv_write_kernel<false><<<(unsigned)blocks, kKvWriteThreads, 0, (cudaStream_t)stream>>>(p);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bf16 && fp8) kv_write_kernel<true, true><<<(unsigned)blocks, kKvWriteThreads, 0, st>>>(p);
+  else if (bf16) kv_write_kernel<true, false><<<(unsigned)blocks, kKvWriteThreads, 0, st>>>(p);
+  else if (fp8) kv_write_kernel<false, true><<<(unsigned)blocks, kKvWriteThreads, 0, st>>>(p);
+  else kv_write_kernel<false, false><<<(unsigned)blocks, kKvWriteThreads, 0, st>>>(p);
   KB_CHECK_LAUNCH("kv_write_kernel");
   return 0;
 }

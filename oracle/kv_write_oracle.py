@@ -47,10 +47,19 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return (x * cos[:, :, None, :]) + (rotate_half(x) * sin[:, :, None, :])
 
 
+def quantize_e4m3(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """x [..., G, D] (fp16 values), scale [..., G] fp32 -> e4m3 bytes of x / scale: fp32 division, clamped to the
+    finite range of the format (+-448), rounded to nearest even."""
+    y = (x.float() / scale[..., None].float()).clamp(-448.0, 448.0)
+    return y.to(torch.float8_e4m3fn)
+
+
 def kv_write(q: Optional[torch.Tensor], k: torch.Tensor, v: torch.Tensor, start_pos, n_new, k_cache, v_cache,
-             block_table, page: int, q_gain=None, k_gain=None, eps: float = 1e-6, inv_freq=None, scale: float = 1.0):
-    """q [B,T,H,D] or None, k / v [B,T,G,D] fp16; caches [pages, page, G, D] are modified in place.
-    Returns the transformed q (or None)."""
+             block_table, page: int, q_gain=None, k_gain=None, eps: float = 1e-6, inv_freq=None, scale: float = 1.0,
+             k_scale=None, v_scale=None):
+    """q [B,T,H,D] or None, k / v [B,T,G,D] fp16 or bf16; caches [pages, page, G, D] are modified in place.
+    With k_scale / v_scale [pages, G] fp32 the caches are e4m3 (torch.float8_e4m3fn) and a row is stored as
+    value / scale of its page and KV head.  Returns the transformed q (or None)."""
     B, T = k.shape[:2]
     pos = torch.tensor(start_pos)[:, None] + torch.arange(T)[None, :]                   # [B, T]
     if k_gain is not None:
@@ -67,6 +76,10 @@ def kv_write(q: Optional[torch.Tensor], k: torch.Tensor, v: torch.Tensor, start_
         for t in range(n):
             p = int(pos[b, t])
             phys = int(block_table[b, p // page])
-            k_cache[phys, p % page] = k[b, t]
-            v_cache[phys, p % page] = v[b, t]
+            if k_scale is not None:
+                k_cache[phys, p % page] = quantize_e4m3(k[b, t], k_scale[phys])
+                v_cache[phys, p % page] = quantize_e4m3(v[b, t], v_scale[phys])
+            else:
+                k_cache[phys, p % page] = k[b, t]
+                v_cache[phys, p % page] = v[b, t]
     return q

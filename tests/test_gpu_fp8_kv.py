@@ -82,3 +82,52 @@ def test_fp8_cache_needs_scales_and_fp16_queries():
     rows = torch.zeros(1, 2, 16, dtype=torch.int32, device="cuda")
     with pytest.raises(nat.KascadeNativeError, match="fp16 q"):
         nat.decode_sparse_paged(q, kv, rows, None, 16, None, 0.1, out, None, None, 1)
+
+
+@pytest.mark.parametrize("with_norm", [False, True], ids=["llama", "qwen3_qknorm"])
+def test_kv_write_quantises_into_an_fp8_cache(with_norm):
+    """The append kernel with an FP8 cache: rotated (and normalised) rows are stored as value / scale of their page
+    and KV head, saturating, round to nearest even - against the oracle's torch restatement.  V rows are pure
+    quantisation of the inputs: bit-identical; K rows inherit the last-bit freedom of cos / sin."""
+    from kascade_b200 import _native as nat
+    from oracle.kv_write_oracle import kv_write as oracle_kv_write
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(31)
+    B, T, H, G, D, page = 2, 21, 8, 2, 128, 16
+    start, n_new = [5, 1000], [21, 9]
+    q = torch.randn(B, T, H, D, generator=g).half()
+    k = (2 * torch.randn(B, T, G, D, generator=g)).half()
+    v = (3 * torch.randn(B, T, G, D, generator=g)).half()
+    max_len = max(s + n for s, n in zip(start, n_new))
+    pps = -(-max_len // page)
+    n_pages = B * pps + 1
+    table = torch.randperm(n_pages, generator=g)[: B * pps].view(B, pps).to(torch.int32)
+    k8 = torch.zeros(n_pages, page, G, D, dtype=torch.float8_e4m3fn)
+    v8 = torch.zeros(n_pages, page, G, D, dtype=torch.float8_e4m3fn)
+    ks = (0.02 + 0.02 * torch.rand(n_pages, G, generator=g)).float()        # about amax / 448 of these rows
+    vs = (0.03 + 0.02 * torch.rand(n_pages, G, generator=g)).float()
+    ks[int(table[0, 0])] = 0.004                                            # two pages small enough to saturate
+    vs[int(table[1, 1000 // page])] = 0.004
+    inv_freq = 1.0 / (500000.0 ** (torch.arange(0, D, 2, dtype=torch.int64).float() / D))
+    q_gain = (1 + 0.1 * torch.randn(D, generator=g)).half() if with_norm else None
+    k_gain = (1 + 0.1 * torch.randn(D, generator=g)).half() if with_norm else None
+    ref_k, ref_v = k8.clone(), v8.clone()
+    oracle_kv_write(q, k, v, start, n_new, ref_k, ref_v, table, page, q_gain, k_gain, 1e-6, inv_freq, 1.0,
+                    k_scale=ks, v_scale=vs)
+    kd, vd, td = k8.to(dev), v8.to(dev), table.to(dev)
+    ks_d, vs_d = ks.to(dev), vs.to(dev)                   # (the layout holds raw pointers: the tensors must stay alive)
+    q_out = torch.empty(B, T, H, D, dtype=torch.float16, device=dev)
+    nat.kv_write(q.to(dev), q_out, k.to(dev), v.to(dev), torch.tensor(start, dtype=torch.int32, device=dev),
+                 torch.tensor(n_new, dtype=torch.int32, device=dev), nat.kv_layout_paged(kd, vd, td, ks_d, vs_d),
+                 None if q_gain is None else q_gain.to(dev), None if k_gain is None else k_gain.to(dev), 1e-6,
+                 inv_freq.to(dev), 1.0)
+    torch.cuda.synchronize()
+    assert torch.equal(vd.cpu().view(torch.uint8), ref_v.view(torch.uint8)), "V rows: pure quantisation, bit for bit"
+    got, want = kd.cpu().view(torch.uint8), ref_k.view(torch.uint8)
+    differ = got != want
+    assert float(differ.float().mean()) < 0.01, f"{float(differ.float().mean()):.3%} of the K bytes differ"
+    # where they differ it is by one step of the format
+    gf, wf = kd.cpu().float(), ref_k.float()
+    assert bool(((gf - wf).abs()[differ] <= 0.126 * wf.abs()[differ].clamp(min=2.0 ** -6)).all())
+    assert bool((wf.abs() == 448.0).any()) and bool((ref_v.float().abs() == 448.0).any()), \
+        "the case is meant to saturate somewhere"
