@@ -545,14 +545,15 @@ class EfficientKascadeStrategy(Strategy):
     @staticmethod
     def append_kv(key_new, value_new, key_cache, value_cache, block_table, start_pos, n_new=None, *, query=None,
                   q_norm_weight=None, k_norm_weight=None, norm_eps: float = 1e-6, inv_freq=None,
-                  rope_scale: float = 1.0):
+                  rope_scale: float = 1.0, k_scale=None, v_scale=None):
         """Prefill -> decode hand-off: write the new tokens' K / V rows (key_new / value_new [B,T,G,D] views,
         positions start_pos[b] + t) into the paged cache the decode kernels read, in one kernel; with
         `inv_freq` (the model's rotary table) and / or the norm weights the rows (and `query` [B,T,H,D], returned
-        transformed) are normalised and rotated on the way, as the Hugging Face module would have done.
+        transformed) are normalised and rotated on the way, as the Hugging Face module would have done; into an FP8
+        (e4m3) cache, with `k_scale` / `v_scale` [num_pages, G] fp32, the rows are stored as value / scale.
         The reference has no counterpart (it receives rotated tensors and copies them per call,
         strategies/EfficientKascadeStrategy.py:144-150)."""
-        kv = nat.kv_layout_paged(key_cache, value_cache, block_table)
+        kv = nat.kv_layout_paged(key_cache, value_cache, block_table, k_scale, v_scale)
         q_out = torch.empty_like(query, memory_format=torch.contiguous_format) if query is not None else None
         nat.kv_write(query, q_out, key_new, value_new, start_pos, n_new, kv, q_norm_weight, k_norm_weight, norm_eps,
                      inv_freq, rope_scale)
