@@ -373,7 +373,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n_c
       }
       if (lane == 0) { sh.warp_gt[warp] = my_gt_hi + g; sh.warp_eq[warp] = q; }
     } else {
-      // ---- 3. the sample misjudged the row: three histogram passes over the row itself -------------------
+      // ---- 3. the sample misjudged the row: four histogram passes over the row itself -------------------
       const int iters = (n4 + kTopkThreads - 1) / kTopkThreads;
       uint32_t prefix = 0, mask = 0, remaining = (uint32_t)k;
 #pragma unroll 1
